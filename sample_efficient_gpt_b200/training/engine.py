@@ -1,0 +1,264 @@
+"""Hand-scheduled forward + backward of the dense transformer (no autograd graph).
+
+One call to ``forward_backward`` runs the whole training micro-step as an explicit sequence of
+kernels: per block ``add+RMSNorm -> qkv GEMM -> RoPE/QK-norm/value-mix -> flash attention -> gate ->
+out GEMM -> add+RMSNorm -> up GEMM -> SwiGLU -> down GEMM``, then the final norm and the fused
+head-projection + cross-entropy (logits never stored), then the mirrored backward that writes
+parameter gradients straight into persistent fp32 buffers (``p.grad``).  Activations are bf16, the
+residual stream and all statistics fp32, weights are read from persistent bf16 shadows of the fp32
+masters that the optimizers refresh.  As soon as a block's gradients are final the engine calls
+``grad_ready(params)`` so that the data-parallel layer can start that bucket's reduction while the
+backward of earlier blocks is still running.  Blocks below ``num_grad_checkpoint_layers`` keep only
+their fp32 input and are recomputed in the backward sweep.
+
+The same schedule runs on CPU tensors through the PyTorch statements of each op, which is how the
+hand-derived backward is checked against autograd of the module path (models/transformer.py).
+Semantics follow the reference model (transformer/transformer.py:47-139, attention.py:176-267).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+from torch import Tensor
+
+from sample_efficient_gpt_b200 import ops
+from sample_efficient_gpt_b200.models.transformer import Transformer
+from sample_efficient_gpt_b200.training.loss import IGNORE_INDEX, LSE_SQUARE_SCALE, NATS_TO_BITS
+from sample_efficient_gpt_b200.utils.profiling import nvtx_range
+
+
+@dataclass
+class StepOutput:
+    loss: Tensor  # mean per-token loss (includes the 1e-6 * lse^2 term)
+    z_loss: Tensor
+    loss_bpb: Tensor | None
+    kurtosis: Tensor  # [n_layers]
+    loss_tok: Tensor | None = None
+
+
+def engine_supports(model: Transformer) -> bool:
+    blk = model.blocks[0]
+    return (not blk.is_moe) and blk.attn.gating in (False, "per-head")
+
+
+class FusedEngine:
+    def __init__(self, model: Transformer, act_dtype: torch.dtype = torch.bfloat16):
+        if not engine_supports(model):
+            raise ValueError("FusedEngine: dense FFN and gating in {False, 'per-head'} only")
+        self.model = model
+        self.lp = act_dtype
+        self.grad_ready: Callable[[list[torch.nn.Parameter]], None] | None = None
+        self.shadows: dict[Tensor, Tensor] = {}
+        self._matrix_params = [p for n, p in model.named_parameters() if p.ndim == 2 and "embedding" not in n]
+        for p in self._matrix_params:
+            self.shadows[p] = p.detach().to(act_dtype) if act_dtype != p.dtype else p.detach()
+        self._first_accum = True
+        at = model.blocks[0].attn
+        self.H, self.Hkv, self.hd = at.n_heads, at.n_kv_heads, at.head_dim
+        self._ones = torch.ones(1, dtype=torch.float32, device=model.embedding.weight.device)
+
+    # ------------------------------------------------------------------ helpers
+    def refresh_shadows(self):
+        """Re-cast every GEMM weight from its fp32 master (after a load or an external update)."""
+        if self.lp == torch.float32:
+            return
+        ps = list(self.shadows.keys())
+        torch._foreach_copy_([self.shadows[p] for p in ps], [p.detach() for p in ps])
+
+    def register_with(self, optimizers):
+        """Let the optimizers write the bf16 shadows in the same kernel that updates the masters."""
+        if self.lp == torch.float32:
+            return
+        for opt in optimizers:
+            if hasattr(opt, "lowp_shadows"):
+                for g in opt.param_groups:
+                    for p in g["params"]:
+                        if p in self.shadows:
+                            opt.lowp_shadows[p] = self.shadows[p]
+
+    def ensure_grads(self):
+        for p in self.model.parameters():
+            if p.requires_grad and p.grad is None:
+                p.grad = torch.zeros_like(p, dtype=torch.float32)
+
+    def _w(self, p: Tensor) -> Tensor:
+        return self.shadows[p]
+
+    def _acc(self, p: torch.nn.Parameter, value: Tensor):
+        if self._first_accum:
+            p.grad.copy_(value.reshape(p.grad.shape))
+        else:
+            p.grad.add_(value.reshape(p.grad.shape))
+
+    def _wgrad(self, p: torch.nn.Parameter, dy: Tensor, x: Tensor):
+        ops.wgrad_accumulate(p.grad, dy, x, self._first_accum)
+
+    # ------------------------------------------------------------------ one block
+    def _layer_fwd(self, i: int, res: Tensor, delta: Tensor | None, v1: Tensor | None, B: int, S: int, want_kurt=True):
+        blk = self.model.blocks[i]
+        at = blk.attn
+        H, Hkv, hd = self.H, self.Hkv, self.hd
+        T = B * S
+        scale = float(blk.ln1.position_scale)
+        x, n1, rstd1, kurt = ops.add_rmsnorm_fwd(res, delta, blk.ln1.gain, scale, blk.ln1.eps, self.lp, want_kurt)
+        qkv = ops.matmul_nt(n1, self._w(at.qkv.linear.weight))
+        z = ops.matmul_nt(n1, self._w(at.attn_gate.linear.weight)) if at.gating else None
+        qgain = at.sdpa_qknorm.gain if at.qknorm else self._ones
+        q, k, v = ops.qkv_post_fwd(
+            qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm
+        )
+        o, lse = ops.attention_fwd(q, k, v, True, 0)
+        g = ops.gate_fwd(o.view(T, H, hd), z) if at.gating else o.view(T, H * hd)
+        a = ops.matmul_nt(g, self._w(at.out.linear.weight))
+        y, n2, rstd2, _ = ops.add_rmsnorm_fwd(x, a, blk.ln2.gain, scale, blk.ln2.eps, self.lp, False)
+        u = ops.matmul_nt(n2, self._w(blk.ffn.up.linear.weight))
+        f = ops.swiglu_fwd(u)
+        m = ops.matmul_nt(f, self._w(blk.ffn.down.linear.weight))
+        saved = (x, n1, rstd1, qkv, z, q, k, v, o, lse, g, y, n2, rstd2, u, f)
+        return y, m, v, kurt, saved
+
+    def _layer_bwd(self, i, saved, v1, dres, dres_lp, dv1_acc, B, S):
+        blk = self.model.blocks[i]
+        at = blk.attn
+        H, Hkv, hd = self.H, self.Hkv, self.hd
+        T = B * S
+        x, n1, rstd1, qkv, z, q, k, v, o, lse, g, y, n2, rstd2, u, f = saved
+        scale = float(blk.ln1.position_scale)
+        w_down, w_up = blk.ffn.down.linear.weight, blk.ffn.up.linear.weight
+        w_out, w_qkv = at.out.linear.weight, at.qkv.linear.weight
+
+        df = ops.matmul_nn(dres_lp, self._w(w_down))
+        self._wgrad(w_down, dres_lp, f)
+        du = ops.swiglu_bwd(df, u)
+        dn2 = ops.matmul_nn(du, self._w(w_up))
+        self._wgrad(w_up, du, n2)
+        dy, dy_lp, dgain2 = ops.add_rmsnorm_bwd(dn2, dres, y, blk.ln2.gain, rstd2, scale, self.lp)
+        self._acc(blk.ln2.gain, dgain2)
+
+        dg = ops.matmul_nn(dy_lp, self._w(w_out))
+        self._wgrad(w_out, dy_lp, g)
+        if at.gating:
+            do, dz = ops.gate_bwd(dg, o.view(T, H, hd), z)
+        else:
+            do, dz = dg, None
+        dq, dk, dv = ops.attention_bwd(do.view(B, S, H, hd), q, k, v, o, lse, True, 0)
+        if i == 0 and dv1_acc is not None:
+            dv = dv.float() + dv1_acc
+        qgain = at.sdpa_qknorm.gain if at.qknorm else self._ones
+        dqkv, dv1, dqg, da1, da2, dvs = ops.qkv_post_bwd(
+            dq, dk, dv, qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm
+        )
+        if dv1 is not None:
+            dv1_acc = dv1 if dv1_acc is None else dv1_acc.add_(dv1)
+        if at.qknorm:
+            self._acc(at.sdpa_qknorm.gain, dqg)
+        if at.value_residual:
+            self._acc(at.alpha1, da1)
+            self._acc(at.alpha2, da2)
+            self._acc(at.scale, dvs)
+        dn1 = ops.matmul_nn(dqkv, self._w(w_qkv))
+        self._wgrad(w_qkv, dqkv, n1)
+        if at.gating:
+            w_gate = at.attn_gate.linear.weight
+            dn1.addmm_(dz, self._w(w_gate))
+            self._wgrad(w_gate, dz, n1)
+        dx, dx_lp, dgain1 = ops.add_rmsnorm_bwd(dn1, dy, x, blk.ln1.gain, rstd1, scale, self.lp)
+        self._acc(blk.ln1.gain, dgain1)
+        if self.grad_ready is not None:
+            self.grad_ready([p for p in blk.parameters() if p.requires_grad])
+        return dx, dx_lp, dv1_acc
+
+    # ------------------------------------------------------------------ whole model
+    @torch.no_grad()
+    def forward_backward(
+        self,
+        tokens: Tensor,
+        targets: Tensor,
+        loss_coef: float = 1.0,
+        byte_len: Tensor | None = None,
+        first_micro_step: bool = True,
+    ) -> StepOutput:
+        """Gradients of ``loss_coef * mean_tokens(loss)`` are written (first micro-step) or added to ``p.grad``."""
+        model = self.model
+        self.ensure_grads()
+        self._first_accum = first_micro_step
+        B, S = tokens.shape
+        T = B * S
+        L = model.n_layers
+        n_ckpt = min(model.num_grad_checkpoint_layers, L)
+        ids = tokens.reshape(-1).long()
+        with nvtx_range("forward"):
+            res = model.embedding.weight.detach()[ids].float()
+            delta, v1 = None, None
+            saved_all, v1_in, kurts = [], [], []
+            for i in range(L):
+                with nvtx_range(f"block {i}"):
+                    y, m, v, kurt, saved = self._layer_fwd(i, res, delta, v1, B, S)
+                v1_in.append(v1)
+                saved_all.append((saved[0],) if i < n_ckpt else saved)
+                if v1 is None:
+                    v1 = v
+                res, delta = y, m
+                kurts.append(kurt)
+            fn = model.final_norm
+            xf, hf, rstdf, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, float(fn.position_scale), fn.eps, self.lp, False)
+        head = model.lm_head.linear.weight
+        with nvtx_range("cross entropy"):
+            if first_micro_step:
+                head.grad.zero_()
+            loss_tok, z_tok, dh, _ = ops.linear_ce_fwd_bwd(
+                hf, self._w(head), targets.reshape(-1), LSE_SQUARE_SCALE, IGNORE_INDEX, loss_coef / T, model.output_mult, dw_out=head.grad
+            )
+        with nvtx_range("backward"):
+            dres, dres_lp, dgain_f = ops.add_rmsnorm_bwd(dh, None, xf, fn.gain, rstdf, float(fn.position_scale), self.lp)
+            self._acc(fn.gain, dgain_f)
+            if self.grad_ready is not None:
+                self.grad_ready([head, fn.gain])
+            dv1_acc = None
+            for i in reversed(range(L)):
+                saved = saved_all[i]
+                if len(saved) == 1:  # recompute this block from its fp32 input
+                    _, _, _, _, saved = self._layer_fwd(i, saved[0], None, v1_in[i], B, S, want_kurt=False)
+                saved_all[i] = None
+                with nvtx_range(f"block {i} bwd"):
+                    dres, dres_lp, dv1_acc = self._layer_bwd(i, saved, v1_in[i], dres, dres_lp, dv1_acc, B, S)
+                del saved
+            emb = model.embedding.weight
+            if first_micro_step:
+                emb.grad.zero_()
+            emb.grad.index_add_(0, ids, dres)
+            if self.grad_ready is not None:
+                self.grad_ready([emb])
+        bpb = None
+        if byte_len is not None:
+            bl = byte_len[targets.reshape(-1).clamp_min(0).long()]
+            bpb = (loss_tok * bl).sum() / bl.sum() * NATS_TO_BITS
+        return StepOutput(loss_tok.mean(), z_tok.mean(), bpb, torch.stack(kurts) / T, loss_tok)
+
+    @torch.no_grad()
+    def forward_loss(self, tokens: Tensor, targets: Tensor, byte_len: Tensor | None = None) -> StepOutput:
+        """Evaluation: the same kernel sequence without saving activations or producing gradients."""
+        model = self.model
+        B, S = tokens.shape
+        T = B * S
+        res = model.embedding.weight.detach()[tokens.reshape(-1).long()].float()
+        delta, v1, kurts = None, None, []
+        for i in range(model.n_layers):
+            res, delta, v, kurt, _ = self._layer_fwd(i, res, delta, v1, B, S)
+            if v1 is None:
+                v1 = v
+            kurts.append(kurt)
+        fn = model.final_norm
+        _, hf, _, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, float(fn.position_scale), fn.eps, self.lp, False)
+        loss_tok, z_tok, _, _ = ops.linear_ce_fwd_bwd(
+            hf, self._w(model.lm_head.linear.weight), targets.reshape(-1), LSE_SQUARE_SCALE, IGNORE_INDEX, 0.0,
+            model.output_mult, need_grad=False,
+        )
+        bpb = None
+        if byte_len is not None:
+            bl = byte_len[targets.reshape(-1).clamp_min(0).long()]
+            bpb = (loss_tok * bl).sum() / bl.sum() * NATS_TO_BITS
+        return StepOutput(loss_tok.mean(), z_tok.mean(), bpb, torch.stack(kurts) / T, loss_tok)
