@@ -1,0 +1,337 @@
+// Python bindings (pybind11 via torch/extension.h) for the sm_100a kernels.  Tensors are checked here
+// (device, dtype, contiguity, alignment-relevant sizes) and handed to the launchers as raw pointers on
+// the current CUDA stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <optional>
+#include <vector>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = std::optional<Tensor>;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+void check_lp(const Tensor& t, bool bf16, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == (bf16 ? at::kBFloat16 : at::kFloat), name, " has the wrong dtype");
+}
+void check_f32(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
+}
+const void* opt_ptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+// ------------------------------------------------------------------------------------------------ norm
+std::tuple<Tensor, Tensor, Tensor, OptTensor> add_rmsnorm_fwd(const Tensor& res, const OptTensor& delta, const Tensor& gain,
+                                                              double scale, double eps, bool bf16, bool want_kurt) {
+  check_f32(res, "res");
+  check_f32(gain, "gain");
+  TORCH_CHECK(res.dim() == 2, "res must be [T, d]");
+  const int T = res.size(0), d = res.size(1);
+  TORCH_CHECK(d % 4 == 0, "d must be a multiple of 4");
+  c10::cuda::CUDAGuard guard(res.device());
+  if (delta.has_value()) check_lp(*delta, bf16, "delta");
+  auto lp = res.options().dtype(bf16 ? at::kBFloat16 : at::kFloat);
+  Tensor x = delta.has_value() ? torch::empty_like(res) : res;
+  Tensor y = torch::empty({T, d}, lp);
+  Tensor rstd = torch::empty({T}, res.options());
+  OptTensor kurt;
+  if (want_kurt) kurt = torch::zeros({}, res.options());
+  seg::add_rmsnorm_fwd(res.data_ptr<float>(), opt_ptr(delta), gain.data_ptr<float>(),
+                       delta.has_value() ? x.data_ptr<float>() : nullptr, y.data_ptr(), rstd.data_ptr<float>(),
+                       want_kurt ? kurt->data_ptr<float>() : nullptr, T, d, (float)scale, (float)eps, bf16, cur_stream());
+  return {x, y, rstd, kurt};
+}
+
+std::tuple<Tensor, Tensor, Tensor> add_rmsnorm_bwd(const Tensor& dy, const OptTensor& dres_in, const Tensor& x, const Tensor& gain,
+                                                   const Tensor& rstd, double scale, bool bf16) {
+  check_lp(dy, bf16, "dy");
+  check_f32(x, "x");
+  check_f32(gain, "gain");
+  check_f32(rstd, "rstd");
+  if (dres_in.has_value()) check_f32(*dres_in, "dres_in");
+  const int T = x.size(0), d = x.size(1);
+  TORCH_CHECK(d % 4 == 0, "d must be a multiple of 4");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dres = torch::empty_like(x);
+  Tensor dres_lp = torch::empty_like(dy);
+  Tensor dgain = torch::empty({d}, x.options());
+  Tensor scratch = torch::empty({seg::add_rmsnorm_bwd_grid(T), d}, x.options());
+  seg::add_rmsnorm_bwd(dy.data_ptr(), dres_in.has_value() ? dres_in->data_ptr<float>() : nullptr, x.data_ptr<float>(),
+                       gain.data_ptr<float>(), rstd.data_ptr<float>(), dres.data_ptr<float>(), dres_lp.data_ptr(),
+                       dgain.data_ptr<float>(), scratch.data_ptr<float>(), T, d, (float)scale, bf16, cur_stream());
+  return {dres, dres_lp, dgain};
+}
+
+// ------------------------------------------------------------------------------------------------ elementwise
+Tensor swiglu_fwd(const Tensor& u) {
+  check_cuda(u, "u");
+  const bool bf16 = u.scalar_type() == at::kBFloat16;
+  check_lp(u, bf16, "u");
+  const int64_t T = u.size(0);
+  const int F = u.size(1) / 2;
+  TORCH_CHECK(F % 4 == 0, "ffn width must be a multiple of 4");
+  c10::cuda::CUDAGuard guard(u.device());
+  Tensor f = torch::empty({T, F}, u.options());
+  seg::swiglu_fwd(u.data_ptr(), f.data_ptr(), T, F, bf16, cur_stream());
+  return f;
+}
+
+Tensor swiglu_bwd(const Tensor& df, const Tensor& u) {
+  const bool bf16 = u.scalar_type() == at::kBFloat16;
+  check_lp(u, bf16, "u");
+  check_lp(df, bf16, "df");
+  const int64_t T = u.size(0);
+  const int F = u.size(1) / 2;
+  c10::cuda::CUDAGuard guard(u.device());
+  Tensor du = torch::empty_like(u);
+  seg::swiglu_bwd(df.data_ptr(), u.data_ptr(), du.data_ptr(), T, F, bf16, cur_stream());
+  return du;
+}
+
+void check_hd(int hd) { TORCH_CHECK(hd == 32 || hd == 64 || hd == 128, "head_dim must be 32, 64 or 128"); }
+
+Tensor gate_fwd(const Tensor& o, const Tensor& z) {
+  const bool bf16 = o.scalar_type() == at::kBFloat16;
+  check_lp(o, bf16, "o");
+  check_lp(z, bf16, "z");
+  TORCH_CHECK(o.dim() == 3, "o must be [T, H, hd]");
+  const int64_t T = o.size(0);
+  const int H = o.size(1), hd = o.size(2);
+  check_hd(hd);
+  c10::cuda::CUDAGuard guard(o.device());
+  Tensor g = torch::empty({T, (int64_t)H * hd}, o.options());
+  seg::gate_fwd(o.data_ptr(), z.data_ptr(), g.data_ptr(), T, H, hd, bf16, cur_stream());
+  return g;
+}
+
+std::tuple<Tensor, Tensor> gate_bwd(const Tensor& dg, const Tensor& o, const Tensor& z) {
+  const bool bf16 = o.scalar_type() == at::kBFloat16;
+  check_lp(o, bf16, "o");
+  check_lp(z, bf16, "z");
+  check_lp(dg, bf16, "dg");
+  const int64_t T = o.size(0);
+  const int H = o.size(1), hd = o.size(2);
+  check_hd(hd);
+  c10::cuda::CUDAGuard guard(o.device());
+  Tensor dout = torch::empty_like(o);
+  Tensor dz = torch::empty_like(z);
+  seg::gate_bwd(dg.data_ptr(), o.data_ptr(), z.data_ptr(), dout.data_ptr(), dz.data_ptr(), T, H, hd, bf16, cur_stream());
+  return {dout, dz};
+}
+
+// ------------------------------------------------------------------------------------------------ qkv post
+seg::QkvPostParams make_post(const Tensor& cos, const Tensor& sin, const Tensor& qgain, const Tensor& a1, const Tensor& a2,
+                             const Tensor& vs, int B, int S, int H, int Hkv, int hd, bool qknorm) {
+  check_f32(cos, "cos");
+  check_f32(sin, "sin");
+  check_f32(qgain, "qgain");
+  check_f32(a1, "alpha1");
+  check_f32(a2, "alpha2");
+  check_f32(vs, "vscale");
+  check_hd(hd);
+  TORCH_CHECK(cos.size(0) >= S && cos.size(1) == hd / 2, "rope table too small for this sequence / head_dim");
+  seg::QkvPostParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.hd = hd; p.qknorm = qknorm;
+  p.cos = cos.data_ptr<float>(); p.sin = sin.data_ptr<float>(); p.qgain = qgain.data_ptr<float>();
+  p.alpha1 = a1.data_ptr<float>(); p.alpha2 = a2.data_ptr<float>(); p.vscale = vs.data_ptr<float>();
+  return p;
+}
+
+std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTensor& v1, const Tensor& cos, const Tensor& sin,
+                                                const Tensor& qgain, const Tensor& a1, const Tensor& a2, const Tensor& vs, int B,
+                                                int S, int H, int Hkv, int hd, bool qknorm) {
+  const bool bf16 = qkv.scalar_type() == at::kBFloat16;
+  check_lp(qkv, bf16, "qkv");
+  TORCH_CHECK(qkv.size(0) == (int64_t)B * S && qkv.size(1) == (int64_t)(H + 2 * Hkv) * hd, "qkv has the wrong shape");
+  if (v1.has_value()) check_lp(*v1, bf16, "v1");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  auto p = make_post(cos, sin, qgain, a1, a2, vs, B, S, H, Hkv, hd, qknorm);
+  Tensor q = torch::empty({B, S, H, hd}, qkv.options());
+  Tensor k = torch::empty({B, S, Hkv, hd}, qkv.options());
+  Tensor v = torch::empty({B, S, Hkv, hd}, qkv.options());
+  seg::qkv_post_fwd(qkv.data_ptr(), opt_ptr(v1), q.data_ptr(), k.data_ptr(), v.data_ptr(), p, bf16, cur_stream());
+  return {q, k, v};
+}
+
+std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
+    const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& qkv, const OptTensor& v1, const Tensor& cos,
+    const Tensor& sin, const Tensor& qgain, const Tensor& a1, const Tensor& a2, const Tensor& vs, int B, int S, int H, int Hkv,
+    int hd, bool qknorm) {
+  const bool bf16 = qkv.scalar_type() == at::kBFloat16;
+  check_lp(qkv, bf16, "qkv");
+  check_lp(dq, bf16, "dq");
+  check_lp(dk, bf16, "dk");
+  check_cuda(dv, "dv");
+  const bool dv_f32 = dv.scalar_type() == at::kFloat;
+  TORCH_CHECK(dv_f32 || dv.scalar_type() == qkv.scalar_type(), "dv must be float32 or the activation dtype");
+  if (v1.has_value()) check_lp(*v1, bf16, "v1");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  auto p = make_post(cos, sin, qgain, a1, a2, vs, B, S, H, Hkv, hd, qknorm);
+  const int64_t T = (int64_t)B * S;
+  auto f32 = qkv.options().dtype(at::kFloat);
+  Tensor dqkv = torch::empty_like(qkv);
+  OptTensor dv1;
+  if (v1.has_value()) dv1 = torch::empty({B, S, Hkv, hd}, f32);
+  Tensor scalars = torch::empty({4}, f32);
+  Tensor partial = torch::empty({T, 4}, f32);
+  seg::qkv_post_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dv_f32, qkv.data_ptr(), opt_ptr(v1), dqkv.data_ptr(),
+                    dv1.has_value() ? dv1->data_ptr<float>() : nullptr, scalars.data_ptr<float>(), partial.data_ptr<float>(), p,
+                    bf16, cur_stream());
+  return {dqkv, dv1, scalars.slice(0, 0, 1), scalars.slice(0, 1, 2), scalars.slice(0, 2, 3), scalars.slice(0, 3, 4)};
+}
+
+// ------------------------------------------------------------------------------------------------ cross entropy
+void ce_chunk_fwd_bwd(Tensor logits, const Tensor& targets, Tensor loss, Tensor z, Tensor lse, double lse_square_scale,
+                      int64_t ignore_index, double grad_scale, double logit_scale, bool write_grad) {
+  check_lp(logits, true, "logits");
+  check_cuda(targets, "targets");
+  TORCH_CHECK(targets.scalar_type() == at::kLong, "targets must be int64");
+  check_f32(loss, "loss");
+  check_f32(z, "z");
+  check_f32(lse, "lse");
+  const int rows = logits.size(0), V = logits.size(1);
+  TORCH_CHECK(V % 8 == 0 && V <= 65536, "vocabulary must be a multiple of 8 and at most 65536");
+  TORCH_CHECK(loss.numel() == rows && z.numel() == rows && lse.numel() == rows && targets.numel() == rows, "row count mismatch");
+  c10::cuda::CUDAGuard guard(logits.device());
+  seg::ce_chunk_fwd_bwd(logits.data_ptr(), targets.data_ptr<int64_t>(), loss.data_ptr<float>(), z.data_ptr<float>(),
+                        lse.data_ptr<float>(), rows, V, (float)lse_square_scale, ignore_index, (float)grad_scale,
+                        (float)logit_scale, write_grad, cur_stream());
+}
+
+// ------------------------------------------------------------------------------------------------ multi-tensor
+constexpr int kChunkElems = 64 * 1024;
+
+struct TensorTable {
+  Tensor ptrs;      // int64 [n_lists, n_tensors] device
+  Tensor sizes;     // int64 [n_tensors]
+  Tensor chunk_t;   // int32 [n_chunks]
+  Tensor chunk_off; // int64 [n_chunks]
+  int n_chunks = 0;
+  int n_tensors = 0;
+};
+
+// Tables are cached by the pointer values they hold: a training run builds each one once.
+const TensorTable& get_table(const std::vector<std::vector<Tensor>>& lists) {
+  static std::map<std::vector<int64_t>, TensorTable> cache;
+  const size_t n = lists[0].size();
+  std::vector<int64_t> key;
+  key.reserve(lists.size() * n + 1);
+  key.push_back((int64_t)lists.size());
+  for (const auto& l : lists) {
+    TORCH_CHECK(l.size() == n, "tensor lists must have equal length");
+    for (const auto& t : l) key.push_back(t.numel() ? (int64_t)(uintptr_t)t.data_ptr() : 0);
+  }
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 64) cache.clear();
+  TensorTable tb;
+  tb.n_tensors = (int)n;
+  auto dev = lists[0][0].device();
+  Tensor ptrs = torch::empty({(int64_t)lists.size(), (int64_t)n}, torch::dtype(torch::kInt64).pinned_memory(true));
+  Tensor sizes = torch::empty({(int64_t)n}, torch::dtype(torch::kInt64).pinned_memory(true));
+  std::vector<int32_t> ct;
+  std::vector<int64_t> co;
+  for (size_t i = 0; i < n; ++i) {
+    const int64_t ne = lists[0][i].numel();
+    sizes.data_ptr<int64_t>()[i] = ne;
+    for (size_t l = 0; l < lists.size(); ++l) ptrs.data_ptr<int64_t>()[l * n + i] = key[1 + l * n + i];
+    for (int64_t o = 0; o < ne; o += kChunkElems) {
+      ct.push_back((int32_t)i);
+      co.push_back(o);
+    }
+  }
+  tb.n_chunks = (int)ct.size();
+  Tensor cth = torch::empty({(int64_t)ct.size()}, torch::dtype(torch::kInt32).pinned_memory(true));
+  Tensor coh = torch::empty({(int64_t)co.size()}, torch::dtype(torch::kInt64).pinned_memory(true));
+  std::memcpy(cth.data_ptr(), ct.data(), ct.size() * sizeof(int32_t));
+  std::memcpy(coh.data_ptr(), co.data(), co.size() * sizeof(int64_t));
+  tb.ptrs = ptrs.to(dev);
+  tb.sizes = sizes.to(dev);
+  tb.chunk_t = cth.to(dev);
+  tb.chunk_off = coh.to(dev);
+  return cache.emplace(std::move(key), std::move(tb)).first->second;
+}
+
+void check_list(const std::vector<Tensor>& l, at::ScalarType st, const char* name, const std::vector<Tensor>* like = nullptr) {
+  for (size_t i = 0; i < l.size(); ++i) {
+    if (l[i].numel() == 0) continue;
+    check_cuda(l[i], name);
+    TORCH_CHECK(l[i].scalar_type() == st, name, " has the wrong dtype");
+    if (like) TORCH_CHECK(l[i].numel() == (*like)[i].numel(), name, " size mismatch");
+  }
+}
+
+void adamw(std::vector<Tensor> ps, std::vector<Tensor> gs, std::vector<Tensor> ms, std::vector<Tensor> vs,
+           std::vector<Tensor> shadows, double lr, double wd, double b1, double b2, double eps, double step_size) {
+  if (ps.empty()) return;
+  check_list(ps, at::kFloat, "params");
+  check_list(gs, at::kFloat, "grads", &ps);
+  check_list(ms, at::kFloat, "m", &ps);
+  check_list(vs, at::kFloat, "v", &ps);
+  check_list(shadows, at::kBFloat16, "shadows", &ps);
+  c10::cuda::CUDAGuard guard(ps[0].device());
+  const auto& tb = get_table({ps, gs, ms, vs, shadows});
+  int64_t* base = tb.ptrs.data_ptr<int64_t>();
+  const int n = tb.n_tensors;
+  seg::adamw_multi((float**)(base), (const float**)(base + n), (float**)(base + 2 * n), (float**)(base + 3 * n),
+                   (void**)(base + 4 * n), tb.sizes.data_ptr<int64_t>(), tb.chunk_t.data_ptr<int32_t>(),
+                   tb.chunk_off.data_ptr<int64_t>(), tb.n_chunks, kChunkElems, (float)lr, (float)wd, (float)b1, (float)b2,
+                   (float)eps, (float)step_size, cur_stream());
+}
+
+void ema(std::vector<Tensor> shadow, std::vector<Tensor> srcs, double decay) {
+  if (shadow.empty()) return;
+  check_list(shadow, at::kFloat, "ema");
+  check_list(srcs, at::kFloat, "src", &shadow);
+  c10::cuda::CUDAGuard guard(shadow[0].device());
+  const auto& tb = get_table({shadow, srcs});
+  int64_t* base = tb.ptrs.data_ptr<int64_t>();
+  const int n = tb.n_tensors;
+  seg::ema_multi((float**)base, (const float**)(base + n), tb.sizes.data_ptr<int64_t>(), tb.chunk_t.data_ptr<int32_t>(),
+                 tb.chunk_off.data_ptr<int64_t>(), tb.n_chunks, kChunkElems, (float)decay, cur_stream());
+}
+
+void cast_bf16(std::vector<Tensor> dsts, std::vector<Tensor> srcs) {
+  if (dsts.empty()) return;
+  check_list(dsts, at::kBFloat16, "dst");
+  check_list(srcs, at::kFloat, "src", &dsts);
+  c10::cuda::CUDAGuard guard(dsts[0].device());
+  const auto& tb = get_table({dsts, srcs});
+  int64_t* base = tb.ptrs.data_ptr<int64_t>();
+  const int n = tb.n_tensors;
+  seg::cast_multi((void**)base, (const float**)(base + n), tb.sizes.data_ptr<int64_t>(), tb.chunk_t.data_ptr<int32_t>(),
+                  tb.chunk_off.data_ptr<int64_t>(), tb.n_chunks, kChunkElems, cur_stream());
+}
+
+}  // namespace
+
+void register_gemm(pybind11::module_& m);  // gemm_bindings.cpp
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "sm_100a kernels of sample_efficient_gpt_b200";
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("add_rmsnorm_bwd", &add_rmsnorm_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("gate_fwd", &gate_fwd);
+  m.def("gate_bwd", &gate_bwd);
+  m.def("qkv_post_fwd", &qkv_post_fwd);
+  m.def("qkv_post_bwd", &qkv_post_bwd);
+  m.def("ce_chunk_fwd_bwd", &ce_chunk_fwd_bwd);
+  m.def("adamw", &adamw);
+  m.def("ema", &ema);
+  m.def("cast_bf16", &cast_bf16);
+  register_gemm(m);
+}

@@ -1,0 +1,129 @@
+// SwiGLU on the packed [gate | up] projection and the per-head output gate, forward and backward.
+//   swiglu: f = silu(a) * b with a = u[:, :F], b = u[:, F:]          (transformer/core.py:86-89 of the reference)
+//           da = df * b * (s + a s (1 - s)), db = df * a * s,  s = sigmoid(a)
+//   gate  : g[t,h,:] = 2 sigmoid(z[t,h]) * o[t,h,:]                   (transformer/attention.py:249-255)
+//           do = 2 s dg ;  dz = 2 s (1 - s) sum_d dg * o
+// Pure streaming kernels: 4 elements per thread per access, every tensor touched once.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace seg {
+
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ u, T* __restrict__ f, int64_t rows, int F) {
+  const int f4 = F >> 2;
+  const int64_t total = rows * f4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / f4;
+    const int c = (int)(i - r * f4) * 4;
+    const float4 a = load4<T>(u + r * 2 * F + c), b = load4<T>(u + r * 2 * F + F + c);
+    store4<T>(f + r * F + c, make_float4(a.x * sigmoidf_(a.x) * b.x, a.y * sigmoidf_(a.y) * b.y, a.z * sigmoidf_(a.z) * b.z,
+                                          a.w * sigmoidf_(a.w) * b.w));
+  }
+}
+
+__device__ __forceinline__ void swiglu_grad(float a, float b, float df, float& da, float& db) {
+  const float s = sigmoidf_(a);
+  da = df * b * (s + a * s * (1.f - s));
+  db = df * a * s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const T* __restrict__ df, const T* __restrict__ u, T* __restrict__ du,
+                                                       int64_t rows, int F) {
+  const int f4 = F >> 2;
+  const int64_t total = rows * f4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / f4;
+    const int c = (int)(i - r * f4) * 4;
+    const float4 a = load4<T>(u + r * 2 * F + c), b = load4<T>(u + r * 2 * F + F + c), g = load4<T>(df + r * F + c);
+    float4 da, db;
+    swiglu_grad(a.x, b.x, g.x, da.x, db.x);
+    swiglu_grad(a.y, b.y, g.y, da.y, db.y);
+    swiglu_grad(a.z, b.z, g.z, da.z, db.z);
+    swiglu_grad(a.w, b.w, g.w, da.w, db.w);
+    store4<T>(du + r * 2 * F + c, da);
+    store4<T>(du + r * 2 * F + F + c, db);
+  }
+}
+
+static int stream_grid(int64_t work_items, int block) {
+  int64_t g = (work_items + block - 1) / block;
+  const int64_t cap = 148 * 16;
+  return (int)(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+void swiglu_fwd(const void* u, void* f, int64_t T, int F, bool bf16, cudaStream_t st) {
+  const int grid = stream_grid(T * (F / 4), 256);
+  if (bf16)
+    swiglu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)f, T, F);
+  else
+    swiglu_fwd_kernel<float><<<grid, 256, 0, st>>>((const float*)u, (float*)f, T, F);
+}
+
+void swiglu_bwd(const void* df, const void* u, void* du, int64_t T, int F, bool bf16, cudaStream_t st) {
+  const int grid = stream_grid(T * (F / 4), 256);
+  if (bf16)
+    swiglu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)df, (const __nv_bfloat16*)u, (__nv_bfloat16*)du, T, F);
+  else
+    swiglu_bwd_kernel<float><<<grid, 256, 0, st>>>((const float*)df, (const float*)u, (float*)du, T, F);
+}
+
+// One group of hd/4 threads per (token, head); hd/4 is 16 (hd 64) or 32 (hd 128), so a warp holds 2 or 1 heads.
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ o, const T* __restrict__ z, T* __restrict__ g,
+                                                     int64_t n_heads_total) {
+  constexpr int TPH = HD / 4;
+  const int64_t total = n_heads_total * TPH;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t head = i / TPH;
+    const float s = 2.f * sigmoidf_(to_f<T>(z[head]));
+    const float4 v = load4<T>(o + i * 4);
+    store4<T>(g + i * 4, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
+  }
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dg, const T* __restrict__ o, const T* __restrict__ z,
+                                                     T* __restrict__ dout, T* __restrict__ dz, int64_t n_heads_total) {
+  constexpr int TPH = HD / 4;
+  const int64_t total = n_heads_total * TPH;  // multiple of TPH; blockDim is a multiple of 32 >= TPH
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t rounds = (total + stride - 1) / stride;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  for (int64_t it = 0; it < rounds; ++it, i += stride) {
+    const bool live = i < total;
+    const int64_t head = live ? i / TPH : 0;
+    float sg = 0.f, dot = 0.f;
+    if (live) {
+      sg = sigmoidf_(to_f<T>(z[head]));
+      const float4 a = load4<T>(dg + i * 4), b = load4<T>(o + i * 4);
+      const float s2 = 2.f * sg;
+      store4<T>(dout + i * 4, make_float4(a.x * s2, a.y * s2, a.z * s2, a.w * s2));
+      dot = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+#pragma unroll
+    for (int off = TPH / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    if (live && (i % TPH) == 0) dz[head] = from_f<T>(2.f * sg * (1.f - sg) * dot);
+  }
+}
+
+void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, bool bf16, cudaStream_t st) {
+  const int64_t nh = T * H;
+  const int grid = stream_grid(nh * (hd / 4), 256);
+#define SEG_GATE(TY, HD) gate_fwd_kernel<TY, HD><<<grid, 256, 0, st>>>((const TY*)o, (const TY*)z, (TY*)g, nh)
+  if (bf16) { if (hd == 64) SEG_GATE(__nv_bfloat16, 64); else if (hd == 128) SEG_GATE(__nv_bfloat16, 128); else SEG_GATE(__nv_bfloat16, 32); }
+  else { if (hd == 64) SEG_GATE(float, 64); else if (hd == 128) SEG_GATE(float, 128); else SEG_GATE(float, 32); }
+#undef SEG_GATE
+}
+
+void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st) {
+  const int64_t nh = T * H;
+  const int grid = stream_grid(nh * (hd / 4), 256);
+#define SEG_GATE(TY, HD) gate_bwd_kernel<TY, HD><<<grid, 256, 0, st>>>((const TY*)dg, (const TY*)o, (const TY*)z, (TY*)dout, (TY*)dz, nh)
+  if (bf16) { if (hd == 64) SEG_GATE(__nv_bfloat16, 64); else if (hd == 128) SEG_GATE(__nv_bfloat16, 128); else SEG_GATE(__nv_bfloat16, 32); }
+  else { if (hd == 64) SEG_GATE(float, 64); else if (hd == 128) SEG_GATE(float, 128); else SEG_GATE(float, 32); }
+#undef SEG_GATE
+}
+
+}  // namespace seg

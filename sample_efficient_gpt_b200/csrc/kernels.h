@@ -1,0 +1,57 @@
+// Host-callable launchers of the sm_100a kernels (raw pointers + stream; no framework types).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace seg {
+
+// ---- norm.cu
+constexpr int kNormBwdMaxGrid = 148 * 4;  // CTAs of the backward kernel == rows of its dgain scratch
+void add_rmsnorm_fwd(const float* res, const void* delta, const float* gain, float* x_out, void* y, float* rstd, float* kurt,
+                     int T, int d, float scale, float eps, bool bf16, cudaStream_t st);
+int add_rmsnorm_bwd_grid(int T);
+// scratch: fp32 [add_rmsnorm_bwd_grid(T), d]
+void add_rmsnorm_bwd(const void* dy, const float* dres_in, const float* x, const float* gain, const float* rstd, float* dres,
+                     void* dres_lp, float* dgain, float* scratch, int T, int d, float scale, bool bf16, cudaStream_t st);
+
+// ---- elementwise.cu
+void swiglu_fwd(const void* u, void* f, int64_t T, int F, bool bf16, cudaStream_t st);
+void swiglu_bwd(const void* df, const void* u, void* du, int64_t T, int F, bool bf16, cudaStream_t st);
+void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, bool bf16, cudaStream_t st);
+void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st);
+
+// ---- qkv_post.cu
+struct QkvPostParams {
+  int B, S, H, Hkv, hd;
+  bool qknorm;
+  const float* cos;  // [>=S, hd/2]
+  const float* sin;
+  const float* qgain;   // [1]
+  const float* alpha1;  // [1]
+  const float* alpha2;  // [1]
+  const float* vscale;  // [1]
+};
+void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st);
+// dv_is_f32: dv is fp32 (first block, after the v1 gradients were added); dv1_out fp32 [T,Hkv,hd] or nullptr;
+// scalars: fp32[4] = {dqgain, dalpha1, dalpha2, dvscale}; partial: scratch fp32 [T, 4].
+void qkv_post_bwd(const void* dq, const void* dk, const void* dv, bool dv_is_f32, const void* qkv, const void* v1, void* dqkv,
+                  float* dv1_out, float* scalars, float* partial, const QkvPostParams& p, bool bf16, cudaStream_t st);
+
+// ---- cross_entropy.cu
+// In place over a chunk of logits [rows, V] (bf16): writes per-row loss, z and lse, and overwrites the
+// logits with grad_scale * (softmax * (1 + 2 s lse) - onehot) (zero rows for ignored targets) when
+// write_grad.  logit_scale multiplies the raw logits first (and the gradient once more).
+void ce_chunk_fwd_bwd(void* logits, const int64_t* targets, float* loss, float* z, float* lse, int rows, int V,
+                      float lse_square_scale, int64_t ignore_index, float grad_scale, float logit_scale, bool write_grad,
+                      cudaStream_t st);
+
+// ---- multi_tensor.cu
+void adamw_multi(float** p, const float** g, float** m, float** v, void** shadow, const int64_t* sizes, const int32_t* chunk_tensor,
+                 const int64_t* chunk_offset, int n_chunks, int chunk_elems, float lr, float wd, float b1, float b2, float eps,
+                 float step_size, cudaStream_t st);
+void ema_multi(float** ema, const float** src, const int64_t* sizes, const int32_t* chunk_tensor, const int64_t* chunk_offset,
+               int n_chunks, int chunk_elems, float decay, cudaStream_t st);
+void cast_multi(void** dst_bf16, const float** src, const int64_t* sizes, const int32_t* chunk_tensor, const int64_t* chunk_offset,
+                int n_chunks, int chunk_elems, cudaStream_t st);
+
+}  // namespace seg

@@ -169,13 +169,13 @@ def wgrad_accumulate(main_grad: Tensor, dy: Tensor, x: Tensor, first: bool):
 
 # ----------------------------------------------------------------------------- cross entropy
 def linear_ce_fwd_bwd(h, w, targets, lse_square_scale, ignore_index, grad_scale, logit_scale=1.0, dw_out=None, need_grad=True):
-    if h.is_cuda and has_kernel("ce_chunk_fwd_bwd"):
+    if h.is_cuda and h.dtype == torch.bfloat16 and has_kernel("ce_chunk_fwd_bwd"):
         from sample_efficient_gpt_b200.ops import cross_entropy as ce_impl
 
         return ce_impl.linear_ce_fwd_bwd(
             h, w, targets, lse_square_scale, ignore_index, grad_scale, logit_scale, dw_out=dw_out, need_grad=need_grad
         )
-    if h.is_cuda:
+    if h.is_cuda and h.dtype == torch.bfloat16:
         _use_cuda(h, "ce_chunk_fwd_bwd")  # raises unless fallback is allowed
     return ref.linear_ce_fwd_bwd(
         h, w, targets, lse_square_scale, ignore_index, grad_scale, logit_scale, dw_out=dw_out, need_grad=need_grad

@@ -1,0 +1,63 @@
+"""Causal GQA attention on CUDA tensors: forward returning (O, ctx) and backward from ctx.
+
+Preferred implementation: this package's tcgen05 flash-attention kernels (``fa_fwd`` / ``fa_bwd`` in the
+extension) when they are built and support the shape.  Otherwise the library path: PyTorch's fused SDPA
+(flash / cuDNN backend, native GQA), differentiated through a private autograd tape so that the caller
+needs no autograd graph of its own.  ``SEGPT_ATTN_IMPL=library|native`` forces one of the two.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from sample_efficient_gpt_b200 import ops
+
+
+class _Tape:
+    """What the library path keeps for its backward: detached leaves and the taped output."""
+
+    __slots__ = ("q", "k", "v", "out")
+
+    def __init__(self, q, k, v, out):
+        self.q, self.k, self.v, self.out = q, k, v, out
+
+
+def _native_ok(q: Tensor, k: Tensor, q_start: int) -> bool:
+    impl = os.environ.get("SEGPT_ATTN_IMPL", "auto")
+    if impl == "library" or not ops.has_kernel("fa_fwd"):
+        if impl == "native":
+            raise RuntimeError("SEGPT_ATTN_IMPL=native but the flash-attention kernels are not built")
+        return False
+    hd = q.size(-1)
+    return q.dtype == torch.bfloat16 and hd in (64, 128) and q_start == 0 and q.size(1) == k.size(1) and q.size(1) % 128 == 0
+
+
+def forward(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, q_start: int = 0):
+    """q [B,S,H,hd], k/v [B,S,Hkv,hd] -> (O [B,S,H,hd], ctx)."""
+    if _native_ok(q, k, q_start):
+        ops._count()
+        o, lse = ops.ext().fa_fwd(q, k, v, causal)
+        return o, lse
+    with torch.enable_grad():
+        ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+        qt, kt, vt = ql.transpose(1, 2), kl.transpose(1, 2), vl.transpose(1, 2)
+        if q_start == 0 and q.size(1) == k.size(1):
+            o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal, enable_gqa=True)
+        else:
+            qi = q_start + torch.arange(q.size(1), device=q.device)
+            kj = torch.arange(k.size(1), device=q.device)
+            o = F.scaled_dot_product_attention(qt, kt, vt, attn_mask=kj[None, :] <= qi[:, None], enable_gqa=True)
+        o = o.transpose(1, 2).contiguous()
+    return o.detach(), _Tape(ql, kl, vl, o)
+
+
+def backward(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, ctx, causal: bool = True, q_start: int = 0):
+    if isinstance(ctx, _Tape):
+        dq, dk, dv = torch.autograd.grad(ctx.out, (ctx.q, ctx.k, ctx.v), do.reshape(ctx.out.shape))
+        return dq, dk, dv
+    ops._count(2)
+    return ops.ext().fa_bwd(do.contiguous(), q, k, v, o, ctx, causal)

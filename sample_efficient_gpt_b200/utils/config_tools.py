@@ -16,6 +16,7 @@ from __future__ import annotations
 import dataclasses
 import importlib
 import json
+import re
 from datetime import datetime
 from pathlib import Path
 from typing import Any
@@ -187,7 +188,8 @@ def render_template(template: str, cfg, extra: dict[str, Any] | None = None) -> 
     values["time"] = now.strftime("%H%M")
     if extra:
         values.update(extra)
-    return template.format_map(values)
+    # dotted keys ("{optim.lr}") are looked up whole, not as attribute access on "optim"
+    return re.sub(r"\{([^{}]+)\}", lambda m: str(values[m.group(1)]), template)
 
 
 def wandb_run_name(cfg: Config, extra: dict[str, Any] | None = None) -> str:
