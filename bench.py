@@ -308,10 +308,15 @@ def run_reference(args):
         tmp = Path(obj[0])
     yaml_path = ref_root / "sample_efficient_gpt" / "configs" / "imu1_base.yaml"
     cfg = load_config_from_yaml(yaml_path, "stable")
+    # The reference keeps about 176 GB of activations at 16 x 2048 tokens per GPU and runs out of memory on a
+    # 180 GB B200, so its arm runs the same 16 sequences per GPU and optimizer step as two accumulated
+    # micro-batches of 8 (SEGPT_REF_MICRO_BATCH=16 tries the single micro-batch).
+    ref_mb = int(os.environ.get("SEGPT_REF_MICRO_BATCH", "8"))
+    ga = MICRO_BATCH // ref_mb
     cfg = apply_overrides(cfg, {
         "data.train_path": str(tmp / "train"), "data.validation_path": str(tmp / "val.npy"),
-        "data.tokenizer_path": str(tmp / "tok"), "data.batch_size": MICRO_BATCH * world, "data.context_length": SEQ,
-        "trainer.save_dir": str(tmp / "ckpt"), "trainer.load_from": None, "trainer.gradient_accumulation_steps": 1,
+        "data.tokenizer_path": str(tmp / "tok"), "data.batch_size": ref_mb * world, "data.context_length": SEQ,
+        "trainer.save_dir": str(tmp / "ckpt"), "trainer.load_from": None, "trainer.gradient_accumulation_steps": ga,
         "trainer.log_every": 10**9, "optim.lr": float(cfg.optim.lr), "optim.muon_lr": float(cfg.optim.muon_lr),
         "optim.zero_lr_steps": 0,
     })
@@ -320,10 +325,12 @@ def run_reference(args):
     sink = []
 
     def step(_i, read_loss=False):
-        inputs, targets = trainer.train_dataset.get_batch(bs)
-        inputs, targets = inputs.to(cfg.trainer.device), targets.to(cfg.trainer.device)
-        log = trainer.train_step(inputs, targets)
-        trainer.iteration += 1
+        """One optimizer step = ``ga`` reference iterations (its train loop body, training/trainer.py:623-628)."""
+        for _ in range(ga):
+            inputs, targets = trainer.train_dataset.get_batch(bs)
+            inputs, targets = inputs.to(cfg.trainer.device), targets.to(cfg.trainer.device)
+            log = trainer.train_step(inputs, targets)
+            trainer.iteration += 1
         if read_loss:
             sink.append(float(log["train_loss"]))
 
@@ -337,8 +344,10 @@ def run_reference(args):
     if not args.no_e2e:
         ms_e2e = timed_loop(lambda i: step(i, True), args.steps, world)
     emit(args, world, rank, ms_dev, ms_e2e, 0, clocks, "reference",
-         {"comm": "nccl" if world > 1 else "none", "compile": True,
-          "note": "reference Trainer.train_step; batches come from its own loader (host->device every step) in both phases"},
+         {"comm": "nccl" if world > 1 else "none", "compile": True, "micro_batch": ref_mb, "grad_accum": ga,
+          "note": "reference Trainer.train_step; 16 sequences per GPU and optimizer step as grad_accum micro-batches "
+                  "(a single 16 x 2048 micro-batch exceeds 180 GB in the reference); batches come from its own loader "
+                  "(host->device every iteration) in both phases"},
          2 * MICRO_BATCH * SEQ * 4, 4)
     if world > 1:
         dist.destroy_process_group()

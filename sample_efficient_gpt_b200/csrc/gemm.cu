@@ -1,0 +1,385 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   D[b] = alpha * A[b] * B[b]^T(or B[b]) + beta * C[b]        fp32 accumulation in tensor memory
+//
+// Operands are described by 3-D TMA tensor maps (inner, outer, batch) built on the host:
+//   K-major operand  : memory [rows, K]  (contraction index contiguous)  -> box {64, rows_per_tile}
+//   MN-major operand : memory [K, rows]  (row index contiguous)          -> boxes {64, 64}, one per 64 rows
+// so that x @ W^T, dy @ W and dy^T @ x all read their inputs in place (no transposes are materialised).
+//
+// Structure (one CTA per SM, 192 threads):
+//   warp 0   : TMA producer.  One elected lane walks the tiles of this CTA and the K blocks of each tile, waits
+//              for a free stage (empty barrier) and issues the loads of the A and B tiles for that stage
+//              (128-byte swizzle), completing on the stage's full barrier.
+//   warp 1   : MMA issuer.  One elected lane waits for a stage, issues BK/16 tcgen05.mma instructions
+//              (128 x BN x 16, accumulator in TMEM) and commits them to the stage's empty barrier; after the last
+//              K block it commits to the accumulator's full barrier.  Two accumulators (2 x BN columns of TMEM)
+//              let the next tile's mainloop overlap this tile's epilogue.
+//   warps 2-5: epilogue.  Each warp owns the 32 TMEM lanes of its sub-partition (warp % 4), reads the accumulator
+//              with tcgen05.ld 32 columns at a time, applies alpha / beta*C and stores bf16 or fp32 rows.
+// Every mbarrier wait is bounded (sm100.cuh): on expiry the CTA raises an abort flag, all roles unwind, TMEM is
+// freed and a status word reports the failure to the host.
+//
+// The reference runs these products through cuBLAS (nn.Linear, torch.addmm) and Triton
+// (training/optimizers/muon_triton.py:58-252, ns_line_1 / ns_line_2).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "sm100.cuh"
+
+namespace seg {
+
+using namespace sm100;
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+struct GemmParams {
+  int M, N, K, batch;
+  float alpha, beta;
+  const void* C;  // optional addend, same layout and dtype as D
+  void* D;
+  int64_t ldd;       // row stride of D and C in elements
+  int64_t batch_stride_d;
+  int* status;
+  int symmetric;  // 1: D is symmetric (A == B, square): only tiles with n_tile >= m_tile are computed and mirrored
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk32(OutT* drow, const OutT* crow, const uint32_t* acc, int ncols, float alpha, float beta,
+                                              bool vec_ok);
+
+template <>
+__device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* drow, const __nv_bfloat16* crow, const uint32_t* acc,
+                                                              int ncols, float alpha, float beta, bool vec_ok) {
+  if (vec_ok && ncols == 32) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = alpha * __uint_as_float(acc[j * 8 + e]);
+      if (crow != nullptr) {
+        float c[8];
+        unpack8(reinterpret_cast<const bf16x8*>(crow)[j], c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += beta * c[e];
+      }
+      reinterpret_cast<bf16x8*>(drow)[j] = pack8(f);
+    }
+  } else {
+    for (int e = 0; e < ncols; ++e) {
+      float f = alpha * __uint_as_float(acc[e]);
+      if (crow != nullptr) f += beta * __bfloat162float(crow[e]);
+      drow[e] = __float2bfloat16_rn(f);
+    }
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_chunk32<float>(float* drow, const float* crow, const uint32_t* acc, int ncols, float alpha,
+                                                      float beta, bool vec_ok) {
+  if (vec_ok && ncols == 32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 f = make_float4(alpha * __uint_as_float(acc[j * 4]), alpha * __uint_as_float(acc[j * 4 + 1]),
+                             alpha * __uint_as_float(acc[j * 4 + 2]), alpha * __uint_as_float(acc[j * 4 + 3]));
+      if (crow != nullptr) {
+        const float4 c = reinterpret_cast<const float4*>(crow)[j];
+        f.x += beta * c.x; f.y += beta * c.y; f.z += beta * c.z; f.w += beta * c.w;
+      }
+      reinterpret_cast<float4*>(drow)[j] = f;
+    }
+  } else {
+    for (int e = 0; e < ncols; ++e) {
+      float f = alpha * __uint_as_float(acc[e]);
+      if (crow != nullptr) f += beta * crow[e];
+      drow[e] = f;
+    }
+  }
+}
+
+// Tile enumeration shared by the three roles: tile t -> (batch, m_tile, n_tile), n fastest.
+struct TileCoord {
+  int b, m, n;
+};
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles) {
+  TileCoord c;
+  c.n = t % n_tiles;
+  const int r = t / n_tiles;
+  c.m = r % m_tiles;
+  c.b = r / m_tiles;
+  return c;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int kStages = S::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* bar_area = smem + kStages * S::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* acc_full = empty_bar + kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles * p.batch;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+  const AbortState ab{cta_abort, p.status};
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 0) {
+    __syncwarp();  // lane 0 initialised the barriers above; the allocation needs the whole warp converged
+    tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int it = 0;  // running stage counter across tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+        if (p.symmetric && tc.n < tc.m) continue;  // below the diagonal: written by the mirror of its twin tile
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, ab, 1)) { ok = false; break; }
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          mbar_expect_tx(fb, S::kStageBytes);
+          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j) tma_load_3d(sa + j * (64 * kBK * 2), &map_a, fb, tc.m * kBM + j * 64, kb * kBK, tc.b);
+          } else {
+            tma_load_3d(sa, &map_a, fb, kb * kBK, tc.m * kBM, tc.b);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * (64 * kBK * 2), &map_b, fb, tc.n * BN + j * 64, kb * kBK, tc.b);
+          } else {
+            tma_load_3d(sb, &map_b, fb, kb * kBK, tc.n * BN, tc.b);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+      int it = 0, local_tile = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+        if (p.symmetric && tc.n < tc.m) continue;
+        const int acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_ph ^ 1, ab, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, ab, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // K-major: 16 elements of K are 32 bytes inside the 128-byte swizzled row.
+            // MN-major: 16 K-rows of 128 bytes = two 1024-byte groups.
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 64 * kBK * 2, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 64 * kBK * 2, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(smem_u32(&acc_full[acc]));
+        ++local_tile;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int sub = warp & 3;  // TMEM sub-partition of this warp: lanes [32*sub, 32*sub+32)
+    OutT* D = reinterpret_cast<OutT*>(p.D);
+    const OutT* C = reinterpret_cast<const OutT*>(p.C);
+    const bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+                        (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
+    int local_tile = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+      if (p.symmetric && tc.n < tc.m) continue;
+      const int acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tc.m * kBM + sub * 32 + lane;
+      const int64_t boff = (int64_t)tc.b * p.batch_stride_d;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * BN + c0, v);
+        tmem_ld_wait();
+        const int col = tc.n * BN + c0;
+        if (row < p.M && col < p.N) {
+          const int ncols = (p.N - col) < 32 ? (p.N - col) : 32;
+          OutT* drow = D + boff + (int64_t)row * p.ldd + col;
+          const OutT* crow = C ? C + boff + (int64_t)row * p.ldd + col : nullptr;
+          store_chunk32<OutT>(drow, crow, v, ncols, p.alpha, p.beta, vec_ok);
+          if (p.symmetric && tc.n > tc.m) {
+            // mirror: D[col+e, row] = D[row, col+e] (symmetric tiles are square, so the twin tile below the
+            // diagonal is never computed).  C, if given, is symmetric too, so the mirrored value is the same.
+            for (int e = 0; e < ncols; ++e) {
+              float f = p.alpha * __uint_as_float(v[e]);
+              if (crow != nullptr) f += p.beta * to_f<OutT>(crow[e]);
+              D[boff + (int64_t)(col + e) * p.ldd + row] = from_f<OutT>(f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+      ++local_tile;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown (also reached after an abort)
+  if (*cta_abort != 0) {
+    // give loads that may still be in flight time to land before the CTA's shared memory is released
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 3-D bf16 tensor map {inner, outer, batch} with a {64, box_outer, 1} box and 128-byte swizzle.
+int make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t outer_stride_elems,
+                         uint64_t batch_stride_elems, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {outer_stride_elems * 2, (batch > 1 ? batch_stride_elems : outer_stride_elems * outer) * 2};
+  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t st) {
+  using S = GemmSmem<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles * p.batch;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  kern<<<grid, kGemmThreads, S::kTotal, st>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
+              int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
+              float beta, bool symmetric, int* status, int sm_count, cudaStream_t st) {
+  // N tile: 256 unless the problem is narrow or the symmetric mirror needs square tiles
+  const int BN = (symmetric || N <= 128) ? 128 : 256;
+  CUtensorMap ma, mb;
+  int r;
+  if (a_mn_major)  // memory [K, M]
+    r = make_tensor_map_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)batch, (uint64_t)lda, (uint64_t)bsa, 64);
+  else  // memory [M, K]
+    r = make_tensor_map_bf16(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, (uint64_t)lda, (uint64_t)bsa, kBM);
+  if (r != 0) return 100 + r;
+  if (b_mn_major)  // memory [K, N]
+    r = make_tensor_map_bf16(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, 64);
+  else  // memory [N, K]
+    r = make_tensor_map_bf16(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, (uint32_t)BN);
+  if (r != 0) return 200 + r;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.alpha = alpha; p.beta = beta;
+  p.C = C; p.D = D; p.ldd = ldd; p.batch_stride_d = bsd;
+  p.status = status;
+  p.symmetric = symmetric ? 1 : 0;
+#define SEG_GEMM(BNv, AM, BM_)                                                                      \
+  (out_f32 ? launch_gemm<BNv, AM, BM_, float>(ma, mb, p, sm_count, st)                              \
+           : launch_gemm<BNv, AM, BM_, __nv_bfloat16>(ma, mb, p, sm_count, st))
+  if (BN == 256) {
+    if (!a_mn_major && !b_mn_major) return SEG_GEMM(256, false, false);
+    if (!a_mn_major && b_mn_major) return SEG_GEMM(256, false, true);
+    if (a_mn_major && b_mn_major) return SEG_GEMM(256, true, true);
+    return SEG_GEMM(256, true, false);
+  }
+  if (!a_mn_major && !b_mn_major) return SEG_GEMM(128, false, false);
+  if (!a_mn_major && b_mn_major) return SEG_GEMM(128, false, true);
+  if (a_mn_major && b_mn_major) return SEG_GEMM(128, true, true);
+  return SEG_GEMM(128, true, false);
+#undef SEG_GEMM
+}
+
+}  // namespace seg

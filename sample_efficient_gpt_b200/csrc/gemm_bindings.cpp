@@ -1,5 +1,100 @@
-// Bindings of the tcgen05 GEMM family (filled in by gemm.cu); kept in a separate translation unit so that the
-// element-wise kernels can be rebuilt without touching it.
+// Bindings of the tcgen05 GEMM (gemm.cu).  Operands may be 2-D or batched 3-D bf16 tensors whose last dimension is
+// contiguous; the bindings derive leading dimensions and batch strides and check the 16-byte alignment TMA needs.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
-void register_gemm(pybind11::module_& m) { (void)m; }
+#include <map>
+#include <optional>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+struct DeviceState {
+  Tensor status;  // int32[1], stays 0 unless a bounded wait gave up
+  int sm_count = 0;
+};
+
+DeviceState& device_state(const c10::Device& dev) {
+  static std::map<int, DeviceState> states;
+  auto it = states.find(dev.index());
+  if (it == states.end()) {
+    DeviceState st;
+    st.status = torch::zeros({1}, torch::dtype(torch::kInt32).device(dev));
+    st.sm_count = at::cuda::getDeviceProperties(dev.index())->multiProcessorCount;
+    it = states.emplace(dev.index(), std::move(st)).first;
+  }
+  return it->second;
+}
+
+void check_operand(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, " must be a CUDA bf16 tensor");
+  TORCH_CHECK(t.dim() == 2 || t.dim() == 3, name, " must be 2-D or 3-D");
+  TORCH_CHECK(t.stride(-1) == 1, name, ": last dimension must be contiguous");
+  TORCH_CHECK(t.stride(-2) % 8 == 0, name, ": row stride must be a multiple of 8 elements (16 bytes)");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, ": base must be 16-byte aligned");
+  if (t.dim() == 3) TORCH_CHECK(t.stride(0) % 8 == 0, name, ": batch stride must be a multiple of 8 elements");
+}
+
+// D = alpha * A op(B) + beta * C
+Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, std::optional<Tensor> out, bool out_f32, bool a_mn,
+            bool b_mn, double alpha, double beta, bool symmetric) {
+  check_operand(a, "a");
+  check_operand(b, "b");
+  TORCH_CHECK(a.dim() == b.dim(), "a and b must have the same rank");
+  const int batch = a.dim() == 3 ? (int)a.size(0) : 1;
+  if (a.dim() == 3) TORCH_CHECK(b.size(0) == batch, "batch mismatch");
+  const int M = (int)(a_mn ? a.size(-1) : a.size(-2));
+  const int K = (int)(a_mn ? a.size(-2) : a.size(-1));
+  const int N = (int)(b_mn ? b.size(-1) : b.size(-2));
+  const int Kb = (int)(b_mn ? b.size(-2) : b.size(-1));
+  TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  if (symmetric) TORCH_CHECK(M == N, "symmetric output must be square");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto opts = a.options().dtype(out_f32 ? at::kFloat : at::kBFloat16);
+  Tensor d;
+  if (out.has_value()) {
+    d = *out;
+    TORCH_CHECK(d.is_cuda() && d.scalar_type() == (out_f32 ? at::kFloat : at::kBFloat16), "out has the wrong dtype");
+    TORCH_CHECK(d.stride(-1) == 1 && d.size(-2) == M && d.size(-1) == N, "out has the wrong shape");
+  } else {
+    d = a.dim() == 3 ? torch::empty({batch, M, N}, opts) : torch::empty({M, N}, opts);
+  }
+  const void* cptr = nullptr;
+  if (c.has_value()) {
+    TORCH_CHECK(c->scalar_type() == d.scalar_type() && c->sizes() == d.sizes() && c->strides() == d.strides(),
+                "c must match the output's dtype, shape and strides");
+    cptr = c->data_ptr();
+  }
+  auto& st = device_state(a.device());
+  const int64_t bsa = a.dim() == 3 ? a.stride(0) : 0, bsb = b.dim() == 3 ? b.stride(0) : 0, bsd = d.dim() == 3 ? d.stride(0) : 0;
+  const int rc = seg::gemm_bf16(a.data_ptr(), b.data_ptr(), cptr, d.data_ptr(), M, N, K, batch, a.stride(-2), b.stride(-2),
+                                d.stride(-2), bsa, bsb, bsd, a_mn, b_mn, out_f32, (float)alpha, (float)beta, symmetric,
+                                st.status.data_ptr<int>(), st.sm_count, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
+  return d;
+}
+
+// Host read of the status word (synchronises): 0 = every wait completed.
+int64_t gemm_status(int64_t device_index) {
+  auto& st = device_state(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
+  return st.status.item<int>();
+}
+
+void gemm_reset_status(int64_t device_index) {
+  auto& st = device_state(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
+  st.status.zero_();
+}
+
+}  // namespace
+
+void register_gemm(pybind11::module_& m) {
+  m.def("gemm", &gemm, pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("c") = std::nullopt, pybind11::arg("out") = std::nullopt,
+        pybind11::arg("out_f32") = false, pybind11::arg("a_mn") = false, pybind11::arg("b_mn") = false, pybind11::arg("alpha") = 1.0,
+        pybind11::arg("beta") = 0.0, pybind11::arg("symmetric") = false);
+  m.def("gemm_status", &gemm_status);
+  m.def("gemm_reset_status", &gemm_reset_status);
+}

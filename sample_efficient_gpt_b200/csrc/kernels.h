@@ -54,4 +54,15 @@ void ema_multi(float** ema, const float** src, const int64_t* sizes, const int32
 void cast_multi(void** dst_bf16, const float** src, const int64_t* sizes, const int32_t* chunk_tensor, const int64_t* chunk_offset,
                 int n_chunks, int chunk_elems, cudaStream_t st);
 
+// ---- gemm.cu (tcgen05 / TMEM / TMA)
+// D[b] = alpha * A[b] * op(B[b]) + beta * C[b], bf16 inputs, fp32 accumulation, D and C bf16 or fp32.
+//   a_mn_major = false: A is [M, K] row-major (lda = row stride);  true: A is stored [K, M].
+//   b_mn_major = false: B is [N, K] row-major (the product is A * B^T); true: B is stored [K, N].
+//   symmetric: A == B and D square: only tiles on or above the diagonal are computed, the rest is mirrored.
+// Strides are in elements; bases and row strides must be 16-byte aligned.  Returns 0 when the launch was issued.
+// `status` is a device int that stays 0 unless a bounded wait inside the kernel gave up.
+int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
+              int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
+              float beta, bool symmetric, int* status, int sm_count, cudaStream_t st);
+
 }  // namespace seg

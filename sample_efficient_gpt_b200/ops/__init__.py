@@ -45,6 +45,11 @@ def has_kernel(name: str) -> bool:
     return e is not None and name not in _DISABLED and hasattr(e, name)
 
 
+def kernel_enabled(feature: str) -> bool:
+    """Features that choose between this package's kernel and a library call (``SEGPT_DISABLE_KERNELS=ns_gemm``)."""
+    return feature not in _DISABLED
+
+
 def _use_cuda(t: Tensor, name: str) -> bool:
     if not t.is_cuda:
         return False

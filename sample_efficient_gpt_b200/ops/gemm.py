@@ -1,0 +1,54 @@
+"""Python face of the tcgen05 GEMM (csrc/gemm.cu): ``D = alpha * A op(B) + beta * C`` on bf16 operands.
+
+``mm_nt(x, w)`` = x @ w^T, ``mm_nn(x, w)`` = x @ w, ``mm_tn(a, b)`` = a^T @ b; all read their operands in place
+(the kernel takes K-major and MN-major tiles), accept a leading batch dimension and accumulate in fp32.
+``usable(t...)`` tells whether the tensors meet the TMA alignment rules (contiguous last dimension, row and
+batch strides multiples of 8 elements, 16-byte aligned base); callers fall back to the library GEMM otherwise.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from sample_efficient_gpt_b200 import ops
+
+
+def usable(*tensors: Tensor) -> bool:
+    if not ops.has_kernel("gemm"):
+        return False
+    for t in tensors:
+        if t is None:
+            continue
+        if not (t.is_cuda and t.dim() in (2, 3) and t.stride(-1) == 1 and t.stride(-2) % 8 == 0 and t.data_ptr() % 16 == 0):
+            return False
+        if t.dim() == 3 and t.stride(0) % 8 != 0:
+            return False
+    return True
+
+
+def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, symmetric=False) -> Tensor:
+    ops._count()
+    return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric)
+
+
+def mm_nt(x: Tensor, w: Tensor, **kw) -> Tensor:
+    """x [.., M, K] @ w [.., N, K]^T."""
+    return gemm(x, w, **kw)
+
+
+def mm_nn(x: Tensor, w: Tensor, **kw) -> Tensor:
+    """x [.., M, K] @ w [.., K, N]."""
+    return gemm(x, w, b_mn=True, **kw)
+
+
+def mm_tn(a: Tensor, b: Tensor, **kw) -> Tensor:
+    """a [.., K, M]^T @ b [.., K, N] (weight gradient: dy^T @ x)."""
+    return gemm(a, b, a_mn=True, b_mn=True, **kw)
+
+
+def status(device_index: int | None = None) -> int:
+    """0 unless a bounded wait inside a GEMM kernel gave up (synchronises the device)."""
+    if device_index is None:
+        device_index = torch.cuda.current_device()
+    return int(ops.ext().gemm_status(device_index))

@@ -36,7 +36,7 @@ def newton_schulz(G: Tensor, epsilon: float = 1e-7, coeffs=POLAR_EXPRESS_COEFFS,
     if G.is_cuda and dtype == torch.bfloat16:
         from sample_efficient_gpt_b200 import ops
 
-        if ops.has_kernel("ns_gemm"):
+        if ops.has_kernel("gemm") and ops.kernel_enabled("ns_gemm"):
             return ops.newton_schulz_cuda(G, epsilon, coeffs)
     X = G.to(dtype)
     transposed = G.size(-2) > G.size(-1)

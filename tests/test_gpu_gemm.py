@@ -1,0 +1,109 @@
+"""tcgen05 GEMM against an fp32 matmul of the same bf16 operands; ordered from one tile upwards.
+
+Every case first checks the kernel's status word: a bounded wait that gave up is reported there instead of hanging.
+"""
+
+import pytest
+import torch
+
+from sample_efficient_gpt_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _g():
+    from sample_efficient_gpt_b200.ops import gemm as G
+
+    assert ops.has_kernel("gemm"), f"extension not built: {ops.ext_error()!r}"
+    return G
+
+
+def _check(d, want, name, tol=2e-2):
+    G = _g()
+    torch.cuda.synchronize()
+    st = G.status()
+    assert st == 0, f"{name}: kernel status {st} (a bounded wait gave up)"
+    err = (d.float() - want).abs().max().item()
+    scale = want.abs().max().item() + 1e-6
+    assert err <= tol * scale, f"{name}: max err {err} vs scale {scale}"
+
+
+def _rand(*shape):
+    return (torch.randn(*shape, device=DEV) * 0.5).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (128, 256, 128), (256, 512, 512), (200, 136, 72), (1000, 1152, 1152)])
+def test_nt(M, N, K):
+    G = _g()
+    torch.manual_seed(0)
+    a, b = _rand(M, K), _rand(N, K)
+    _check(G.mm_nt(a, b), a.float() @ b.float().t(), f"nt {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 320, 192), (520, 1152, 384)])
+def test_nn_and_tn(M, N, K):
+    G = _g()
+    torch.manual_seed(1)
+    a, w = _rand(M, K), _rand(K, N)
+    _check(G.mm_nn(a, w), a.float() @ w.float(), f"nn {M}x{N}x{K}")
+    at, bt = _rand(K, M), _rand(K, N)
+    _check(G.mm_tn(at, bt), at.float().t() @ bt.float(), f"tn {M}x{N}x{K}")
+
+
+def test_epilogue_batch_f32_and_strides():
+    G = _g()
+    torch.manual_seed(2)
+    a, b = _rand(3, 256, 192), _rand(3, 384, 192)
+    c = _rand(3, 256, 384)
+    want = 0.5 * torch.bmm(a.float(), b.float().mT) - 1.5 * c.float()
+    _check(G.gemm(a, b, c=c, alpha=0.5, beta=-1.5), want, "batched alpha/beta")
+    cf = torch.randn(256, 384, device=DEV)
+    d = G.gemm(a[0], b[0], c=cf, out=cf.clone(), out_f32=True, alpha=1.0, beta=1.0)
+    _check(d, a[0].float() @ b[0].float().t() + cf, "fp32 accumulate", tol=1e-3)
+    big = _rand(300, 512)
+    view = big[:, 128:320]  # row stride 512, offset 128: still 16-byte aligned
+    _check(G.mm_nt(view, b[1]), view.float() @ b[1].float().t(), "strided A")
+
+
+def test_symmetric():
+    G = _g()
+    torch.manual_seed(3)
+    x = _rand(2, 384, 640)
+    a = G.gemm(x, x, symmetric=True)
+    _check(a, torch.bmm(x.float(), x.float().mT), "x x^T symmetric")
+    assert torch.equal(a, a.mT.contiguous())
+    bb = G.gemm(a, a, c=a, alpha=0.3, beta=-0.7, symmetric=True)
+    _check(bb, 0.3 * torch.bmm(a.float(), a.float()) - 0.7 * a.float(), "b A + c A A")
+
+
+def test_newton_schulz_on_gemm_matches_library_path():
+    from sample_efficient_gpt_b200.optim.newton_schulz import POLAR_EXPRESS_COEFFS
+    from sample_efficient_gpt_b200.ops.newton_schulz import newton_schulz
+
+    torch.manual_seed(4)
+    for shape in [(4, 256, 512), (3, 512, 256), (1152, 1152)]:
+        Gm = torch.randn(*shape, device=DEV)
+        X = newton_schulz(Gm, 1e-7, POLAR_EXPRESS_COEFFS)
+        Xb = Gm.to(torch.bfloat16)
+        tr = Xb.size(-2) > Xb.size(-1)
+        Y = Xb.mT if tr else Xb
+        Y = Y / (Y.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+        for a, b, c in POLAR_EXPRESS_COEFFS:
+            A = (Y.float() @ Y.float().mT).to(torch.bfloat16)
+            B = (b * A.float() + c * (A.float() @ A.float())).to(torch.bfloat16)
+            Y = (a * Y.float() + B.float() @ Y.float()).to(torch.bfloat16)
+        Y = Y.mT if tr else Y
+        _check(X, Y.float(), f"NS {shape}", tol=6e-2)
+        s = torch.linalg.svdvals(X.float().reshape(-1, *X.shape[-2:])[0])
+        assert s.max() < 1.3 and s.min() > 0.4
+
+
+def test_large_shapes_and_speed():
+    G = _g()
+    torch.manual_seed(5)
+    a, w = _rand(8192, 1152), _rand(6144, 1152)
+    _check(G.mm_nt(a, w), a.float() @ w.float().t(), "8192x6144x1152")
+    dy = _rand(8192, 3072)
+    x = _rand(8192, 1152)
+    _check(G.mm_tn(dy, x, out_f32=True), dy.float().t() @ x.float(), "wgrad 3072x1152x8192", tol=1e-2)
