@@ -112,10 +112,12 @@ class Muon(torch.optim.Optimizer):
 
     def state_dict(self):
         sd = super().state_dict()
-        for st in sd["state"].values():
-            for k, v in list(st.items()):
-                if torch.is_tensor(v) and v._base is not None:
-                    st[k] = v.clone()  # a view would drag the whole stacked storage into the file
+        # The per-parameter dicts returned by torch are the live ones: build copies instead of editing them, and
+        # clone views so that a file does not drag the whole stacked storage along.
+        sd["state"] = {
+            k: {kk: (vv.clone() if torch.is_tensor(vv) and vv._base is not None else vv) for kk, vv in st.items()}
+            for k, st in sd["state"].items()
+        }
         return sd
 
     def load_state_dict(self, state_dict):

@@ -111,6 +111,8 @@ class Trainer:
         self.act_dtype = torch.bfloat16 if tc.dtype == "bfloat16" else torch.float32
         self.iteration = 0
         self.run_id = None
+        self.engine: FusedEngine | None = None
+        self.optimizers = None
         self.wandb = wandb
         if wandb is None and tc.metrics_jsonl and self.rank == self.target_log_rank:
             self.wandb = M.JsonlSink(tc.metrics_jsonl)
@@ -148,9 +150,7 @@ class Trainer:
             if specials:
                 self.id2byte_len[torch.tensor(specials, device=self.device)] = 0
 
-        self.engine: FusedEngine | None = None
         self.use_engine = engine_supports(self.model) and os.environ.get("SEGPT_ENGINE", "1") == "1"
-        self.optimizers = None
         self.ema: WeightEMA | None = None
         if load_components == "all":
             self._init_optimizers()
