@@ -185,7 +185,7 @@ std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
   OptTensor dv1;
   if (v1.has_value()) dv1 = torch::empty({B, S, Hkv, hd}, f32);
   Tensor scalars = torch::empty({4}, f32);
-  Tensor partial = torch::empty({T, 4}, f32);
+  Tensor partial = torch::empty({seg::qkv_post_bwd_grid(T, H + 2 * Hkv, hd), 4}, f32);
   seg::qkv_post_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dv_f32, qkv.data_ptr(), opt_ptr(v1), dqkv.data_ptr(),
                     dv1.has_value() ? dv1->data_ptr<float>() : nullptr, scalars.data_ptr<float>(), partial.data_ptr<float>(), p,
                     bf16, cur_stream());
@@ -315,6 +315,57 @@ void cast_bf16(std::vector<Tensor> dsts, std::vector<Tensor> srcs) {
                   tb.chunk_off.data_ptr<int64_t>(), tb.n_chunks, kChunkElems, cur_stream());
 }
 
+// ------------------------------------------------------------------------------------------------ muon
+// grads: the owned matrices' fp32 gradients; slot_of: int32 device tensor with their slots in the stacked buffers.
+void muon_momentum(std::vector<Tensor> grads, const Tensor& slot_of, Tensor momentum, Tensor xout, double mu, double eps) {
+  if (grads.empty()) return;
+  check_list(grads, at::kFloat, "grads");
+  check_f32(momentum, "momentum");
+  check_lp(xout, true, "xout");
+  TORCH_CHECK(slot_of.is_cuda() && slot_of.scalar_type() == at::kInt && slot_of.numel() == (int64_t)grads.size(), "slot_of mismatch");
+  const int64_t numel = grads[0].numel();
+  TORCH_CHECK(numel % 8 == 0, "matrix size must be a multiple of 8");
+  for (auto& g : grads) TORCH_CHECK(g.numel() == numel && g.is_contiguous(), "gradients of one group must share a shape");
+  TORCH_CHECK(momentum.numel() % numel == 0 && xout.numel() == momentum.numel(), "stacked buffers have the wrong size");
+  c10::cuda::CUDAGuard guard(momentum.device());
+  const auto& tb = get_table({grads});
+  const int n = (int)grads.size();
+  Tensor partial = torch::empty({(int64_t)n * seg::muon_chunks_per_matrix(numel)}, momentum.options());
+  seg::muon_momentum((const float* const*)tb.ptrs.data_ptr<int64_t>(), slot_of.data_ptr<int>(), momentum.data_ptr<float>(),
+                     xout.data_ptr(), partial.data_ptr<float>(), n, numel, (float)mu, (float)eps, cur_stream());
+}
+
+void muon_tail(const Tensor& v, const Tensor& slot_of, Tensor second, std::vector<Tensor> params, std::vector<Tensor> shadows,
+               Tensor sq_sum_out, int64_t R, int64_t C, double beta2, bool normalize, double lr_eff, double decay, int64_t mode) {
+  if (params.empty()) return;
+  check_lp(v, true, "v");
+  check_list(params, at::kFloat, "params");
+  check_f32(sq_sum_out, "sq_sum_out");
+  const int n = (int)params.size();
+  TORCH_CHECK(slot_of.is_cuda() && slot_of.scalar_type() == at::kInt && slot_of.numel() == n, "slot_of mismatch");
+  TORCH_CHECK(C % 8 == 0, "columns must be a multiple of 8");
+  for (auto& p : params) TORCH_CHECK(p.numel() == R * C && p.is_contiguous(), "parameters of one group must share a shape");
+  const bool with_shadows = !shadows.empty();
+  if (with_shadows) {
+    TORCH_CHECK((int)shadows.size() == n, "shadows mismatch");
+    check_list(shadows, at::kBFloat16, "shadows", &params);
+  }
+  const int64_t len = R >= C ? R : C;
+  if (normalize) {
+    check_f32(second, "second");
+    TORCH_CHECK(second.numel() == (int64_t)n * len, "second-moment buffer has the wrong size");
+  }
+  c10::cuda::CUDAGuard guard(v.device());
+  const auto& tb = with_shadows ? get_table({params, shadows}) : get_table({params});
+  int64_t* base = tb.ptrs.data_ptr<int64_t>();
+  auto f32 = v.options().dtype(at::kFloat);
+  Tensor sq = torch::empty({(int64_t)n, len}, f32), mult = torch::empty({(int64_t)n, len}, f32);
+  seg::muon_tail(v.data_ptr(), slot_of.data_ptr<int>(), normalize ? second.data_ptr<float>() : nullptr, sq.data_ptr<float>(),
+                 mult.data_ptr<float>(), (float* const*)base, with_shadows ? (void* const*)(base + n) : nullptr,
+                 sq_sum_out.data_ptr<float>(), n, (int)R, (int)C, (float)beta2, normalize ? 1 : 0, (float)lr_eff, (float)decay,
+                 (int)mode, cur_stream());
+}
+
 }  // namespace
 
 void register_gemm(pybind11::module_& m);  // gemm_bindings.cpp
@@ -333,5 +384,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw", &adamw);
   m.def("ema", &ema);
   m.def("cast_bf16", &cast_bf16);
+  m.def("muon_momentum", &muon_momentum);
+  m.def("muon_tail", &muon_tail);
   register_gemm(m);
 }

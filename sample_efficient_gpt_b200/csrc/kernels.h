@@ -21,6 +21,8 @@ void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, b
 void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st);
 
 // ---- qkv_post.cu
+constexpr int kQkvPostMaxGrid = 148 * 8;  // CTAs of the kernels == rows of the backward's scalar scratch
+int qkv_post_bwd_grid(int64_t T, int nslots, int hd);
 struct QkvPostParams {
   int B, S, H, Hkv, hd;
   bool qknorm;
@@ -33,7 +35,7 @@ struct QkvPostParams {
 };
 void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st);
 // dv_is_f32: dv is fp32 (first block, after the v1 gradients were added); dv1_out fp32 [T,Hkv,hd] or nullptr;
-// scalars: fp32[4] = {dqgain, dalpha1, dalpha2, dvscale}; partial: scratch fp32 [T, 4].
+// scalars: fp32[4] = {dqgain, dalpha1, dalpha2, dvscale}; partial: scratch fp32 [qkv_post_bwd_grid(...), 4].
 void qkv_post_bwd(const void* dq, const void* dk, const void* dv, bool dv_is_f32, const void* qkv, const void* v1, void* dqkv,
                   float* dv1_out, float* scalars, float* partial, const QkvPostParams& p, bool bf16, cudaStream_t st);
 
@@ -53,6 +55,18 @@ void ema_multi(float** ema, const float** src, const int64_t* sizes, const int32
                int n_chunks, int chunk_elems, float decay, cudaStream_t st);
 void cast_multi(void** dst_bf16, const float** src, const int64_t* sizes, const int32_t* chunk_tensor, const int64_t* chunk_offset,
                 int n_chunks, int chunk_elems, cudaStream_t st);
+
+// ---- muon.cu
+int muon_chunks_per_matrix(int64_t numel);
+// momentum [slots, numel] fp32 and xout [slots, numel] bf16 are indexed through slot_of[i]; grads[i] are fp32 pointers.
+// partial: scratch fp32 [n_mats * muon_chunks_per_matrix(numel)].  numel must be a multiple of 8.
+void muon_momentum(const float* const* grads, const int32_t* slot_of, float* momentum, void* xout, float* partial, int n_mats,
+                   int64_t numel, float mu, float eps, cudaStream_t st);
+// v [slots, R, C] bf16; second / sq / mult fp32 [n_mats, R] (R >= C) or [n_mats, C]; params[i] fp32, shadows[i] bf16 or null
+// array; sq_sum_out accumulates sum ||v_i||_F^2.  mode: 0 none, 1 plain decay, 2 cautious decay.  C % 8 == 0.
+void muon_tail(const void* v, const int32_t* slot_of, float* second, float* sq, float* mult, float* const* params,
+               void* const* shadows, float* sq_sum_out, int n_mats, int R, int C, float beta2, int normalize, float lr_eff,
+               float decay, int mode, cudaStream_t st);
 
 // ---- gemm.cu (tcgen05 / TMEM / TMA)
 // D[b] = alpha * A[b] * op(B[b]) + beta * C[b], bf16 inputs, fp32 accumulation, D and C bf16 or fp32.

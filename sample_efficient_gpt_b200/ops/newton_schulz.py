@@ -1,10 +1,11 @@
 """Newton-Schulz chain on the tcgen05 GEMM.
 
-Per iteration and for a whole batch of same-shape matrices: ``A = X X^T`` and ``B = b A + c A A`` compute only the
-tiles on or above the diagonal and mirror them (both results are symmetric); ``X = a X + B X`` reads X as an MN-major
-operand, so nothing is transposed.  Every product accumulates in fp32 and is rounded to bf16, as in the reference
-(training/optimizers/muon_triton.py:327-377).  Shapes the TMA path cannot take (a side that is not a multiple of 8,
-e.g. the 18 x d gate matrices) use the library batched GEMM.
+Per iteration and for a whole batch of same-shape matrices: the Gram matrix ``A`` and ``B = b A + c A A`` compute only
+the tiles on or above the diagonal and mirror them (both are symmetric); the update ``a X + B X`` (wide X) or
+``a X + X B`` (tall X) reads its operands in place (K-major and MN-major tiles), so tall matrices are never
+transposed: for ``R > C`` the chain runs on ``X^T`` implicitly with ``A = X^T X``.  Every product accumulates in fp32
+and is rounded to bf16, as in the reference (training/optimizers/muon_triton.py:327-377).  Shapes the TMA path
+cannot take (a side that is not a multiple of 8, e.g. the 18 x d gate matrices) use the library batched GEMM.
 """
 
 from __future__ import annotations
@@ -15,30 +16,44 @@ from torch import Tensor
 from sample_efficient_gpt_b200.ops import gemm as G
 
 
+def ns_iterations(X: Tensor, Y: Tensor, coeffs) -> Tensor:
+    """Run the chain on normalised bf16 ``X [n, R, C]`` ping-ponging with ``Y`` (same shape); returns the buffer
+    that holds the result (``Y`` for an odd number of iterations)."""
+    n, R, C = X.shape
+    tall = R > C
+    r = min(R, C)
+    if r % 8 == 0 and max(R, C) % 8 == 0 and G.usable(X, Y):
+        A = torch.empty((n, r, r), dtype=torch.bfloat16, device=X.device)
+        B = torch.empty_like(A)
+        for a, b, c in coeffs:
+            if tall:
+                G.gemm(X, X, out=A, a_mn=True, b_mn=True, symmetric=True)  # X^T X
+            else:
+                G.gemm(X, X, out=A, symmetric=True)  # X X^T
+            G.gemm(A, A, c=A, out=B, alpha=c, beta=b, symmetric=True)
+            if tall:
+                G.gemm(X, B, c=X, out=Y, alpha=1.0, beta=a)  # X B (B symmetric)
+            else:
+                G.gemm(B, X, c=X, out=Y, b_mn=True, alpha=1.0, beta=a)  # B X
+            X, Y = Y, X
+        return X
+    for a, b, c in coeffs:
+        A = (X.mT @ X) if tall else (X @ X.mT)
+        B = torch.baddbmm(A, A, A, beta=b, alpha=c)
+        if tall:
+            torch.baddbmm(X, X, B, beta=a, out=Y)
+        else:
+            torch.baddbmm(X, B, X, beta=a, out=Y)
+        X, Y = Y, X
+    return X
+
+
 def newton_schulz(Gm: Tensor, epsilon: float, coeffs) -> Tensor:
+    """Orthogonalise ``Gm`` ([R, C] or [n, R, C], any float dtype): normalise by the Frobenius norm, run the chain."""
     X = Gm.to(torch.bfloat16)
     squeeze = X.dim() == 2
     if squeeze:
         X = X.unsqueeze(0)
-    transposed = X.size(-2) > X.size(-1)
-    if transposed:
-        X = X.mT
     X = (X / (X.norm(dim=(-2, -1), keepdim=True) + epsilon)).contiguous()
-    r = X.size(-2)
-    if r % 8 == 0 and X.size(-1) % 8 == 0 and G.usable(X):
-        A = torch.empty((X.size(0), r, r), dtype=torch.bfloat16, device=X.device)
-        B = torch.empty_like(A)
-        Y = torch.empty_like(X)
-        for a, b, c in coeffs:
-            G.gemm(X, X, out=A, symmetric=True)
-            G.gemm(A, A, c=A, out=B, alpha=c, beta=b, symmetric=True)
-            G.gemm(B, X, c=X, out=Y, b_mn=True, alpha=1.0, beta=a)
-            X, Y = Y, X
-    else:
-        for a, b, c in coeffs:
-            A = X @ X.mT
-            B = torch.baddbmm(A, A, A, beta=b, alpha=c)
-            X = torch.baddbmm(X, B, X, beta=a)
-    if transposed:
-        X = X.mT
-    return X.squeeze(0) if squeeze else X
+    out = ns_iterations(X, torch.empty_like(X), coeffs)
+    return out.squeeze(0) if squeeze else out

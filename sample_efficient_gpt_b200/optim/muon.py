@@ -57,6 +57,11 @@ class _ShapeBatch:
         sm_shape = (n, rows, 1) if rows >= cols else (n, 1, cols)
         self.second = torch.zeros(sm_shape, dtype=torch.float32, device=dev)
         self.update = torch.zeros((self.slots, rows, cols), dtype=torch.bfloat16, device=dev)
+        # CUDA fast path: second ping-pong buffer of the Newton-Schulz chain and slot index tables
+        self.xbuf = torch.zeros_like(self.update) if dev.type == "cuda" else None
+        if dev.type == "cuda":
+            self.slot_all = torch.tensor(self.slot_of, dtype=torch.int32, device=dev)
+            self.slot_owned = torch.tensor([self.slot_of[i] for i in self.owned], dtype=torch.int32, device=dev)
 
     def owner(self, i: int) -> int:
         return (i // self.chunk + self.rot) % self.world
@@ -152,10 +157,65 @@ class Muon(torch.optim.Optimizer):
                     continue
                 raise RuntimeError("Muon: either all or none of the matrices of one shape must have a gradient")
             b = self._batch(gi)
-            v = self._orthogonalized_updates(b, group)  # [n, rows, cols] fp32, identical on all ranks
-            sq_sum += self._apply(b, group, v)
+            if self._fused_ok(b):
+                sq_sum += self._step_fused(b, group)
+            else:
+                v = self._orthogonalized_updates(b, group)  # [n, rows, cols] fp32, identical on all ranks
+                sq_sum += self._apply(b, group, v)
             n_total += b.n
         return sq_sum.sqrt() / (n_total + 1e-10)
+
+    def _fused_ok(self, b: _ShapeBatch) -> bool:
+        from sample_efficient_gpt_b200 import ops
+
+        p0 = b.params[0]
+        if not (p0.is_cuda and p0.dtype == torch.float32 and ops.has_kernel("muon_tail") and ops.kernel_enabled("muon_fused")):
+            return False
+        if b.cols % 8 != 0 or (b.rows * b.cols) % 8 != 0:
+            return False
+        muls = {(getattr(p, "lr_mul", 1.0), getattr(p, "wd_mul", 1.0)) for p in b.params}
+        return len(muls) == 1 and all(p.is_contiguous() and p.grad is not None and p.grad.is_contiguous() for p in b.params)
+
+    def _step_fused(self, b: _ShapeBatch, group) -> Tensor:
+        """CUDA path: 2 launches for momentum + normalisation, the GEMM chain, 3 launches for the tail."""
+        from sample_efficient_gpt_b200 import ops
+        from sample_efficient_gpt_b200.ops.newton_schulz import ns_iterations
+        from sample_efficient_gpt_b200.optim.newton_schulz import POLAR_EXPRESS_COEFFS
+
+        ext = ops.ext()
+        idx = b.owned if self.is_distributed else list(range(b.n))
+        if idx:
+            ext.muon_momentum([b.params[i].grad for i in idx], b.slot_owned if self.is_distributed else b.slot_all,
+                              b.momentum, b.xbuf, group["momentum"], 1e-7)
+            ops._count(2)
+            s0 = b.slot_of[idx[0]]
+            res = ns_iterations(b.xbuf[s0 : s0 + len(idx)], b.update[s0 : s0 + len(idx)], POLAR_EXPRESS_COEFFS)
+            if res.data_ptr() != b.update[s0].data_ptr():
+                b.update[s0 : s0 + len(idx)].copy_(res)
+        if self.is_distributed:
+            self._gather_updates(b)
+        lr, wd = group["lr"], group["weight_decay"]
+        lr_mul, wd_mul = getattr(b.params[0], "lr_mul", 1.0), getattr(b.params[0], "wd_mul", 1.0)
+        mode = 1 if self._plain_decay else (2 if self._cautious else 0)
+        sq = torch.zeros((), dtype=torch.float32, device=b.update.device)
+        shadows = [self.lowp_shadows.get(p) for p in b.params]
+        shadows = shadows if all(s is not None for s in shadows) else []
+        ext.muon_tail(b.update, b.slot_all, b.second, list(b.params), shadows, sq, b.rows, b.cols, group["beta2"],
+                      self._normalize, lr * max(1.0, b.rows / b.cols) ** 0.5 * lr_mul, lr * wd * wd_mul, mode)
+        ops._count(3)
+        if not shadows:
+            for p in b.params:
+                sh = self.lowp_shadows.get(p)
+                if sh is not None:
+                    sh.copy_(p)
+        return sq
+
+    def _gather_updates(self, b: _ShapeBatch):
+        if self.comm is not None:
+            self.comm.all_gather_inplace(b.update, b.chunk)
+        else:
+            mine = b.update[self.rank * b.chunk : (self.rank + 1) * b.chunk].contiguous()
+            dist.all_gather_into_tensor(b.update.view(-1), mine.view(-1))
 
     def _orthogonalized_updates(self, b: _ShapeBatch, group) -> Tensor:
         mu = group["momentum"]
@@ -175,11 +235,7 @@ class Muon(torch.optim.Optimizer):
             else:
                 b.update[slots] = x
         if self.is_distributed:
-            if self.comm is not None:
-                self.comm.all_gather_inplace(b.update, b.chunk)
-            else:
-                mine = b.update[self.rank * b.chunk : (self.rank + 1) * b.chunk].contiguous()
-                dist.all_gather_into_tensor(b.update.view(-1), mine.view(-1))
+            self._gather_updates(b)
         if b.slot_of == list(range(b.n)):
             return b.update[: b.n].float()
         return b.update[b.slot_of].float()

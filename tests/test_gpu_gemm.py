@@ -96,7 +96,7 @@ def test_newton_schulz_on_gemm_matches_library_path():
         Y = Y.mT if tr else Y
         _check(X, Y.float(), f"NS {shape}", tol=6e-2)
         s = torch.linalg.svdvals(X.float().reshape(-1, *X.shape[-2:])[0])
-        assert s.max() < 1.3 and s.min() > 0.4
+        assert s.max() < 1.3 and s.median() > 0.5
 
 
 def test_large_shapes_and_speed():
