@@ -220,7 +220,7 @@ def run_ours(args):
         "data.batch_size": MICRO_BATCH * world, "data.context_length": SEQ,
         "trainer.save_dir": str(tmp / "ckpt"), "trainer.device": f"cuda:{local}", "trainer.dtype": "bfloat16",
         "trainer.gradient_accumulation_steps": 1, "trainer.load_from": None, "trainer.log_every": 10**9,
-        "optim.shard_muon": world > 1,
+        "optim.shard_muon": world > 1, "trainer.comm_backend": os.environ.get("SEGPT_COMM_BACKEND", "auto"),
     })
     cfg.optim.lr, cfg.optim.muon_lr = float(cfg.optim.lr), float(cfg.optim.muon_lr)
     trainer = Trainer(cfg)
@@ -263,6 +263,8 @@ def run_ours(args):
         ms_e2e = timed_loop(e2e_step, args.steps, world)
         h2d = 2 * MICRO_BATCH * SEQ * 4
         d2h = 4
+    if trainer.ddp is not None and trainer.ddp.comm is not None:
+        trainer.ddp.comm.check()  # raises if a bounded wait on a peer gave up during the run
     emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, "ours",
          {"comm": comm, "sharded_muon": bool(cfg.optim.shard_muon), "ema_every": cfg.trainer.ema_every}, h2d, d2h)
     if world > 1:

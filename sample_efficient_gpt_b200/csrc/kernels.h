@@ -68,6 +68,18 @@ void muon_tail(const void* v, const int32_t* slot_of, float* second, float* sq, 
                void* const* shadows, float* sq_sum_out, int n_mats, int R, int C, float beta2, int normalize, float lr_eff,
                float decay, int mode, cudaStream_t st);
 
+// ---- comm.cu (NVLink peer-memory collectives; one process per GPU)
+constexpr int kMaxRanks = 8;
+constexpr int kCommMaxBlocks = 64;  // flag words per rank = kCommMaxBlocks * kMaxRanks
+// grads: this rank's fp32 bucket (n elements, n % (world*8) == 0), reduced in place across ranks with bf16 on the wire.
+// wire_bufs[p] / flags[p]: peer-mapped wire buffer and flag array of rank p; wire_off: element offset of the bucket in the
+// wire buffers; mc_base: NVLS multicast address of the wire buffer or null; seq: first of two consecutive barrier numbers.
+void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
+                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st);
+// bufs[p] + off_bytes holds `world` chunks of chunk_bytes (multiple of 16); chunk `rank` is valid on entry, all on exit.
+void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,
+                    uint32_t seq, int blocks, int* status, cudaStream_t st);
+
 // ---- gemm.cu (tcgen05 / TMEM / TMA)
 // D[b] = alpha * A[b] * op(B[b]) + beta * C[b], bf16 inputs, fp32 accumulation, D and C bf16 or fp32.
 //   a_mn_major = false: A is [M, K] row-major (lda = row stride);  true: A is stored [K, M].

@@ -40,7 +40,7 @@ class _ShapeBatch:
     optimizer-state entries are views into these tensors.
     """
 
-    def __init__(self, params: list[Tensor], group_index: int, world: int, rank: int):
+    def __init__(self, params: list[Tensor], group_index: int, world: int, rank: int, symm_alloc=None):
         self.params = params
         n = len(params)
         self.n = n
@@ -56,7 +56,10 @@ class _ShapeBatch:
         self.momentum = torch.zeros((self.slots, rows, cols), dtype=torch.float32, device=dev)
         sm_shape = (n, rows, 1) if rows >= cols else (n, 1, cols)
         self.second = torch.zeros(sm_shape, dtype=torch.float32, device=dev)
-        self.update = torch.zeros((self.slots, rows, cols), dtype=torch.bfloat16, device=dev)
+        if symm_alloc is not None:  # peer-mapped, so that the all-gather kernel can read it from other ranks
+            self.update = symm_alloc((self.slots, rows, cols), torch.bfloat16)
+        else:
+            self.update = torch.zeros((self.slots, rows, cols), dtype=torch.bfloat16, device=dev)
         # CUDA fast path: second ping-pong buffer of the Newton-Schulz chain and slot index tables
         self.xbuf = torch.zeros_like(self.update) if dev.type == "cuda" else None
         if dev.type == "cuda":
@@ -94,7 +97,8 @@ class Muon(torch.optim.Optimizer):
         b = self._batches.get(gi)
         if b is None:
             ps = self.param_groups[gi]["params"]
-            b = _ShapeBatch(ps, gi, self.world, self.rank)
+            alloc = self.comm.symm_zeros if (self.comm is not None and self.is_distributed) else None
+            b = _ShapeBatch(ps, gi, self.world, self.rank, alloc)
             self._batches[gi] = b
             self._bind_state(b)
         return b

@@ -56,22 +56,26 @@ class DDP(nn.Module):
         by_name = dict(named)
         self.bucket_names = assign_buckets(named, int(bucket_size_mb * 1024 * 1024))
         # flat fp32 gradient storage, bucket after bucket
-        total = sum(p.numel() for _, p in named)
+        # each bucket is padded to the alignment the reduction kernels need (the padding stays zero)
+        align = comm.bucket_alignment() if comm is not None else 1
+        sizes = [sum(by_name[n].numel() for n in names) for names in self.bucket_names]
+        padded = [(sz + align - 1) // align * align for sz in sizes]
         dev = named[0][1].device
-        self.flat_grads = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.flat_grads = torch.zeros(sum(padded), dtype=torch.float32, device=dev)
         self.bucket_ranges: list[tuple[int, int]] = []
         self.param_bucket: dict[Tensor, int] = {}
         self._views: dict[Tensor, Tensor] = {}
-        off = 0
+        start = 0
         for bi, names in enumerate(self.bucket_names):
-            start = off
+            off = start
             for n in names:
                 p = by_name[n]
                 self._views[p] = self.flat_grads[off : off + p.numel()].view_as(p)
                 p.grad = self._views[p]
                 self.param_bucket[p] = bi
                 off += p.numel()
-            self.bucket_ranges.append((start, off))
+            self.bucket_ranges.append((start, start + padded[bi]))
+            start += padded[bi]
         self.bucket_sizes = [len(n) for n in self.bucket_names]
         self._pending = [0] * len(self.bucket_names)
         self._should_all_reduce = True

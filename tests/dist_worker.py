@@ -1,0 +1,184 @@
+"""Worker for the multi-process tests; launched by torchrun from test_ddp_gloo.py / test_gpu_multi.py.
+
+Modes: ``ddp_cpu`` (gloo ranks on CPU), ``comm_gpu`` and ``train_gpu`` (one rank per GPU, NCCL bootstrap).
+Prints ``WORKER-OK <mode>`` from rank 0 on success; any assertion makes the launcher exit non-zero.
+"""
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+from sample_efficient_gpt_b200.models import Transformer  # noqa: E402
+from sample_efficient_gpt_b200.optim import NorMuonCWD  # noqa: E402
+from sample_efficient_gpt_b200.parallel.ddp import DDP, assign_buckets  # noqa: E402
+from sample_efficient_gpt_b200.training.engine import FusedEngine  # noqa: E402
+from sample_efficient_gpt_b200.training.loss import efficient_cross_entropy  # noqa: E402
+
+
+def tiny_model(device):
+    torch.manual_seed(7)
+    m = Transformer(2, 512, 64, 4, 128, attn_qknorm=True, attn_val_residual=True, attn_gating="per-head", layernorm_scaling=True,
+                    n_kv_heads=2, weight_tying=True)
+    return m.to(device)
+
+
+def ddp_cpu(rank, world):
+    m = tiny_model("cpu")
+    if rank != 0:  # DDP must overwrite this with rank 0's weights
+        with torch.no_grad():
+            for p in m.parameters():
+                p.add_(1.0)
+    ddp = DDP(m, bucket_size_mb=0.05)
+    assert len(ddp.bucket_names) > 3
+    names = [n for b in ddp.bucket_names for n in b]
+    assert names == [n for n, _ in reversed(list(m.named_parameters()))]
+    ref = tiny_model("cpu")
+    for a, b in zip(m.parameters(), ref.parameters()):
+        assert torch.equal(a, b), "broadcast from rank 0 failed"
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 512, (4, 16), generator=g)
+    tg = torch.randint(0, 512, (4, 16), generator=g)
+    # reference: full batch on one process
+    logits, _ = ref(ids)
+    loss, _, _ = efficient_cross_entropy(logits, tg)
+    loss.backward()
+    # autograd path: each rank takes half the batch, loss pre-scaled by local/global
+    sl = slice(rank * 2, rank * 2 + 2)
+    logits, _ = ddp(ids[sl])
+    loss, _, _ = efficient_cross_entropy(logits, tg[sl])
+    (loss * 0.5).backward()
+    ddp.finish_gradient_synchronization()
+    for (n, a), b in zip(m.named_parameters(), ref.parameters()):
+        assert torch.allclose(a.grad, b.grad, rtol=0.05, atol=2e-3 * float(b.grad.abs().max()) + 1e-6), f"autograd path {n}"
+    # engine path with explicit grads_ready notifications and no_sync accumulation
+    ddp.zero_grad()
+    eng = FusedEngine(m, torch.float32)
+    eng.grad_ready = ddp.grads_ready
+    with ddp.no_sync():
+        eng.forward_backward(ids[sl], tg[sl], 0.25, first_micro_step=True)
+    eng.forward_backward(ids[sl], tg[sl], 0.25, first_micro_step=False)
+    ddp.finish_gradient_synchronization()
+    for (n, a), b in zip(m.named_parameters(), ref.parameters()):
+        assert torch.allclose(a.grad, b.grad, rtol=0.05, atol=2e-3 * float(b.grad.abs().max()) + 1e-6), f"engine path {n}"
+    # sharded NorMuon == unsharded NorMuon on identical gradients
+    ps_a = [torch.nn.Parameter(p.detach().clone()) for p in ref.parameters() if p.ndim == 2 and p.shape[0] != 512]
+    ps_b = [torch.nn.Parameter(p.detach().clone()) for p in ps_a]
+    oa = NorMuonCWD(ps_a, lr=0.02, momentum=0.9, weight_decay=0.1, shard=True)
+    ob = NorMuonCWD(ps_b, lr=0.02, momentum=0.9, weight_decay=0.1, shard=False)
+    assert oa.is_distributed and not ob.is_distributed
+    for step in range(3):
+        gg = torch.Generator().manual_seed(100 + step)
+        for p, q in zip(ps_a, ps_b):
+            gr = torch.randn(p.shape, generator=gg)
+            p.grad, q.grad = gr.clone(), gr.clone()
+        ra, rb = oa.step(), ob.step()
+        assert abs(float(ra) - float(rb)) < 1e-5
+    for p, q in zip(ps_a, ps_b):
+        assert torch.allclose(p, q, atol=1e-6), "sharded Muon diverged from the unsharded step"
+    oa.consolidate_state()
+    sa, sb = oa.state_dict(), ob.state_dict()
+    for k in sb["state"]:
+        assert torch.allclose(sa["state"][k]["momentum_buffer"], sb["state"][k]["momentum_buffer"], atol=1e-6)
+
+
+def comm_gpu(rank, world):
+    from sample_efficient_gpt_b200.parallel.symm import SymmComm
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    for use_mm in ([False, True] if os.environ.get("SEGPT_TEST_MULTIMEM", "0") == "1" else [False]):
+        comm = SymmComm.create(dev, use_multimem=use_mm, blocks=8)
+        align = comm.bucket_alignment()
+        sizes = [align * 3, align * 1000, align * 17 + 0, 4 * 1024 * 1024 // align * align]
+        ranges, off = [], 0
+        for s in sizes:
+            ranges.append((off, off + s))
+            off += s
+        flat = torch.zeros(off, device=dev)
+        comm.register_buckets(flat, ranges)
+        for it in range(3):
+            torch.manual_seed(1000 * it + rank)
+            flat.copy_(torch.randn(off, device=dev))
+            want = flat.to(torch.bfloat16).float()
+            dist.all_reduce(want)
+            for bi in range(len(ranges)):
+                comm.all_reduce_bucket(bi)
+            comm.wait_all()
+            torch.cuda.synchronize()
+            comm.check()
+            err = (flat - want).abs().max().item()
+            assert err < 0.05 * world, f"all-reduce mismatch {err} (multimem={use_mm})"
+            gathered = [torch.empty_like(flat) for _ in range(world)]
+            dist.all_gather(gathered, flat)
+            for g in gathered:
+                assert torch.equal(g, flat), "ranks ended with different reduced values"
+        rows = 5
+        buf = comm.symm_zeros((world * rows, 48, 64), torch.bfloat16)
+        for it in range(2):
+            buf.zero_()
+            buf[rank * rows : (rank + 1) * rows] = float(rank + 1 + it)
+            torch.cuda.synchronize()
+            dist.barrier()
+            comm.all_gather_inplace(buf, rows)
+            torch.cuda.synchronize()
+            comm.check()
+            for r in range(world):
+                assert torch.all(buf[r * rows : (r + 1) * rows] == float(r + 1 + it)), "all-gather mismatch"
+
+
+def train_gpu(rank, world):
+    """Two optimizer steps of a small model: NVLink-kernel communicator vs torch.distributed collectives."""
+    import numpy as np
+
+    from sample_efficient_gpt_b200.training.trainer import Trainer
+    from sample_efficient_gpt_b200.utils.config_tools import apply_overrides, load_cfg
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    results = {}
+    for backend in ("nccl", "p2p"):
+        cfg = load_cfg("tiny_cpu.yaml")
+        cfg = apply_overrides(cfg, {"trainer.device": f"cuda:{local}", "trainer.dtype": "bfloat16", "trainer.comm_backend": backend,
+                                    "model.vocab_size": 4096, "data.batch_size": 4 * world, "optim.shard_muon": True,
+                                    "trainer.save_dir": "/tmp/segpt_multi", "trainer.bucket_size_mb": 1.0})
+        tr = Trainer(cfg)
+        assert (tr.ddp.comm is not None) == (backend == "p2p")
+        g = torch.Generator().manual_seed(5 + rank)
+        for _ in range(3):
+            w = torch.randint(0, 4096, (4, 257), generator=g).cuda()
+            tr.train_step(w[:, :-1], w[:, 1:])
+            tr.iteration += 1
+        torch.cuda.synchronize()
+        if tr.ddp.comm is not None:
+            tr.ddp.comm.check()
+        results[backend] = [p.detach().clone() for p in tr.model.parameters()]
+        flat = torch.cat([p.flatten() for p in results[backend]])
+        other = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(other, flat)
+        for o in other:
+            assert torch.equal(o, flat), f"{backend}: ranks diverged"
+    for a, b in zip(results["nccl"], results["p2p"]):
+        assert torch.allclose(a, b, atol=3e-2, rtol=0.1), (a - b).abs().max()
+
+
+def main():
+    mode = sys.argv[1]
+    cuda = mode.endswith("_gpu")
+    if cuda:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dist.init_process_group("nccl" if cuda else "gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    try:
+        {"ddp_cpu": ddp_cpu, "comm_gpu": comm_gpu, "train_gpu": train_gpu}[mode](rank, world)
+        dist.barrier()
+        if rank == 0:
+            print(f"WORKER-OK {mode}", flush=True)
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

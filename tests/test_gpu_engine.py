@@ -41,6 +41,9 @@ def test_engine_bf16_close_to_fp32_autograd(ckpt):
     assert torch.allclose(out.kurtosis, kurt.float(), rtol=0.05, atol=0.05)
     for n, p in m.named_parameters():
         g, r = p.grad.float(), ref[n].float()
+        if g.numel() == 1:  # scalar gradients are sums of many bf16-rounded terms of both signs: absolute slack
+            assert (g - r).abs().item() < 0.1 * r.abs().item() + 5e-3, f"{n}: {g.item()} vs {r.item()}"
+            continue
         cos = torch.nn.functional.cosine_similarity(g.flatten(), r.flatten(), dim=0)
         assert cos > 0.98, f"{n}: cosine {cos}"
         assert (g.norm() / (r.norm() + 1e-12) - 1).abs() < 0.1, n
