@@ -18,9 +18,12 @@ using OptTensor = std::optional<Tensor>;
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+// The kernels use 16-byte vector accesses: a tensor that starts off such a boundary (a view at an odd offset)
+// is rejected here instead of faulting on the device.
 void check_cuda(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.numel() == 0 || reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " must start on a 16-byte boundary");
 }
 void check_lp(const Tensor& t, bool bf16, const char* name) {
   check_cuda(t, name);
@@ -264,10 +267,13 @@ const TensorTable& get_table(const std::vector<std::vector<Tensor>>& lists) {
   return cache.emplace(std::move(key), std::move(tb)).first->second;
 }
 
-void check_list(const std::vector<Tensor>& l, at::ScalarType st, const char* name, const std::vector<Tensor>* like = nullptr) {
+void check_list(const std::vector<Tensor>& l, at::ScalarType st, const char* name, const std::vector<Tensor>* like = nullptr,
+                bool need_aligned = false) {
   for (size_t i = 0; i < l.size(); ++i) {
     if (l[i].numel() == 0) continue;
-    check_cuda(l[i], name);
+    TORCH_CHECK(l[i].is_cuda() && l[i].is_contiguous(), name, " must be contiguous CUDA tensors");
+    if (need_aligned)
+      TORCH_CHECK(reinterpret_cast<uintptr_t>(l[i].data_ptr()) % 16 == 0, name, " must start on 16-byte boundaries");
     TORCH_CHECK(l[i].scalar_type() == st, name, " has the wrong dtype");
     if (like) TORCH_CHECK(l[i].numel() == (*like)[i].numel(), name, " size mismatch");
   }
@@ -319,7 +325,7 @@ void cast_bf16(std::vector<Tensor> dsts, std::vector<Tensor> srcs) {
 // grads: the owned matrices' fp32 gradients; slot_of: int32 device tensor with their slots in the stacked buffers.
 void muon_momentum(std::vector<Tensor> grads, const Tensor& slot_of, Tensor momentum, Tensor xout, double mu, double eps) {
   if (grads.empty()) return;
-  check_list(grads, at::kFloat, "grads");
+  check_list(grads, at::kFloat, "grads", nullptr, true);
   check_f32(momentum, "momentum");
   check_lp(xout, true, "xout");
   TORCH_CHECK(slot_of.is_cuda() && slot_of.scalar_type() == at::kInt && slot_of.numel() == (int64_t)grads.size(), "slot_of mismatch");
@@ -339,7 +345,7 @@ void muon_tail(const Tensor& v, const Tensor& slot_of, Tensor second, std::vecto
                Tensor sq_sum_out, int64_t R, int64_t C, double beta2, bool normalize, double lr_eff, double decay, int64_t mode) {
   if (params.empty()) return;
   check_lp(v, true, "v");
-  check_list(params, at::kFloat, "params");
+  check_list(params, at::kFloat, "params", nullptr, true);
   check_f32(sq_sum_out, "sq_sum_out");
   const int n = (int)params.size();
   TORCH_CHECK(slot_of.is_cuda() && slot_of.scalar_type() == at::kInt && slot_of.numel() == n, "slot_of mismatch");
@@ -348,7 +354,7 @@ void muon_tail(const Tensor& v, const Tensor& slot_of, Tensor second, std::vecto
   const bool with_shadows = !shadows.empty();
   if (with_shadows) {
     TORCH_CHECK((int)shadows.size() == n, "shadows mismatch");
-    check_list(shadows, at::kBFloat16, "shadows", &params);
+    check_list(shadows, at::kBFloat16, "shadows", &params, true);
   }
   const int64_t len = R >= C ? R : C;
   if (normalize) {

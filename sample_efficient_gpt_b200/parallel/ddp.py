@@ -56,26 +56,32 @@ class DDP(nn.Module):
         by_name = dict(named)
         self.bucket_names = assign_buckets(named, int(bucket_size_mb * 1024 * 1024))
         # flat fp32 gradient storage, bucket after bucket
-        # each bucket is padded to the alignment the reduction kernels need (the padding stays zero)
-        align = comm.bucket_alignment() if comm is not None else 1
-        sizes = [sum(by_name[n].numel() for n in names) for names in self.bucket_names]
-        padded = [(sz + align - 1) // align * align for sz in sizes]
+        # Every gradient view starts on a 256-byte boundary (the kernels read gradients with 16-byte vector
+        # accesses) and every bucket is padded to the length the reduction kernels need; padding stays zero.
+        palign = 64
+        align = max(comm.bucket_alignment() if comm is not None else 1, palign)
+        align = (align + palign - 1) // palign * palign
         dev = named[0][1].device
-        self.flat_grads = torch.zeros(sum(padded), dtype=torch.float32, device=dev)
+        layout, start = [], 0
+        for names in self.bucket_names:
+            off, offs = start, []
+            for n in names:
+                offs.append(off)
+                off = (off + by_name[n].numel() + palign - 1) // palign * palign
+            end = start + (off - start + align - 1) // align * align
+            layout.append((start, end, offs))
+            start = end
+        self.flat_grads = torch.zeros(start, dtype=torch.float32, device=dev)
         self.bucket_ranges: list[tuple[int, int]] = []
         self.param_bucket: dict[Tensor, int] = {}
         self._views: dict[Tensor, Tensor] = {}
-        start = 0
-        for bi, names in enumerate(self.bucket_names):
-            off = start
-            for n in names:
+        for bi, (names, (b_start, b_end, offs)) in enumerate(zip(self.bucket_names, layout)):
+            for n, off in zip(names, offs):
                 p = by_name[n]
                 self._views[p] = self.flat_grads[off : off + p.numel()].view_as(p)
                 p.grad = self._views[p]
                 self.param_bucket[p] = bi
-                off += p.numel()
-            self.bucket_ranges.append((start, start + padded[bi]))
-            start += padded[bi]
+            self.bucket_ranges.append((b_start, b_end))
         self.bucket_sizes = [len(n) for n in self.bucket_names]
         self._pending = [0] * len(self.bucket_names)
         self._should_all_reduce = True
