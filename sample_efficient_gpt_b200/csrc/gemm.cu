@@ -7,7 +7,7 @@
 //   MN-major operand : memory [K, rows]  (row index contiguous)          -> boxes {64, 64}, one per 64 rows
 // so that x @ W^T, dy @ W and dy^T @ x all read their inputs in place (no transposes are materialised).
 //
-// Structure (one CTA per SM, 192 threads):
+// Structure (one CTA per SM, 320 threads):
 //   warp 0   : TMA producer.  One elected lane walks the tiles of this CTA and the K blocks of each tile, waits
 //              for a free stage (empty barrier) and issues the loads of the A and B tiles for that stage
 //              (128-byte swizzle), completing on the stage's full barrier.
@@ -15,8 +15,9 @@
 //              (128 x BN x 16, accumulator in TMEM) and commits them to the stage's empty barrier; after the last
 //              K block it commits to the accumulator's full barrier.  Two accumulators (2 x BN columns of TMEM)
 //              let the next tile's mainloop overlap this tile's epilogue.
-//   warps 2-5: epilogue.  Each warp owns the 32 TMEM lanes of its sub-partition (warp % 4), reads the accumulator
-//              with tcgen05.ld 32 columns at a time, applies alpha / beta*C and stores bf16 or fp32 rows.
+//   warps 2-9: epilogue.  Each warp owns the 32 TMEM lanes of its sub-partition (warp % 4) and one half of the
+//              columns, reads the accumulator with tcgen05.ld 32 columns at a time, applies alpha / beta*C (C fetched
+//              one chunk ahead) and stores bf16 or fp32 rows - to this GPU and, optionally, to peer GPUs' buffers.
 // Every mbarrier wait is bounded (sm100.cuh): on expiry the CTA raises an abort flag, all roles unwind, TMEM is
 // freed and a status word reports the failure to the host.
 //
@@ -34,7 +35,7 @@ using namespace sm100;
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
 template <int BN>
 struct GemmSmem {
@@ -54,60 +55,69 @@ struct GemmParams {
   int64_t ldd;       // row stride of D and C in elements
   int64_t batch_stride_d;
   int* status;
-  int symmetric;  // 1: D is symmetric (A == B, square): only tiles with n_tile >= m_tile are computed and mirrored
+  int symmetric;  // 1: D is symmetric (A == B, square): tiles wholly below the diagonal are skipped and mirrored
+  void* D_extra[7];  // further destinations with D's layout (peer-mapped buffers of other ranks): every tile is
+  int n_extra;       // stored to all of them, which turns the epilogue into the all-gather of the result
 };
 
+// Raw addend values of one 32-column row chunk, fetched ahead of use.
 template <typename OutT>
-__device__ __forceinline__ void store_chunk32(OutT* drow, const OutT* crow, const uint32_t* acc, int ncols, float alpha, float beta,
-                                              bool vec_ok);
-
+struct CRegs;
 template <>
-__device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* drow, const __nv_bfloat16* crow, const uint32_t* acc,
-                                                              int ncols, float alpha, float beta, bool vec_ok) {
-  if (vec_ok && ncols == 32) {
+struct CRegs<__nv_bfloat16> {
+  uint4 r[4];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = reinterpret_cast<const uint4*>(p)[j];
+  }
+  // v[e] (float bits) += beta * c[e]
+  __device__ __forceinline__ void add_scaled(uint32_t* v, float beta) const {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float f[8];
+      float c[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(&r[j]), c);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = alpha * __uint_as_float(acc[j * 8 + e]);
-      if (crow != nullptr) {
-        float c[8];
-        unpack8(reinterpret_cast<const bf16x8*>(crow)[j], c);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] += beta * c[e];
-      }
-      reinterpret_cast<bf16x8*>(drow)[j] = pack8(f);
-    }
-  } else {
-    for (int e = 0; e < ncols; ++e) {
-      float f = alpha * __uint_as_float(acc[e]);
-      if (crow != nullptr) f += beta * __bfloat162float(crow[e]);
-      drow[e] = __float2bfloat16_rn(f);
+      for (int e = 0; e < 8; ++e) v[j * 8 + e] = __float_as_uint(__uint_as_float(v[j * 8 + e]) + beta * c[e]);
     }
   }
-}
-
+};
 template <>
-__device__ __forceinline__ void store_chunk32<float>(float* drow, const float* crow, const uint32_t* acc, int ncols, float alpha,
-                                                      float beta, bool vec_ok) {
-  if (vec_ok && ncols == 32) {
+struct CRegs<float> {
+  float4 r[8];
+  __device__ __forceinline__ void load(const float* p) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = reinterpret_cast<const float4*>(p)[j];
+  }
+  __device__ __forceinline__ void add_scaled(uint32_t* v, float beta) const {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float4 f = make_float4(alpha * __uint_as_float(acc[j * 4]), alpha * __uint_as_float(acc[j * 4 + 1]),
-                             alpha * __uint_as_float(acc[j * 4 + 2]), alpha * __uint_as_float(acc[j * 4 + 3]));
-      if (crow != nullptr) {
-        const float4 c = reinterpret_cast<const float4*>(crow)[j];
-        f.x += beta * c.x; f.y += beta * c.y; f.z += beta * c.z; f.w += beta * c.w;
-      }
-      reinterpret_cast<float4*>(drow)[j] = f;
-    }
-  } else {
-    for (int e = 0; e < ncols; ++e) {
-      float f = alpha * __uint_as_float(acc[e]);
-      if (crow != nullptr) f += beta * crow[e];
-      drow[e] = f;
+      v[j * 4 + 0] = __float_as_uint(__uint_as_float(v[j * 4 + 0]) + beta * r[j].x);
+      v[j * 4 + 1] = __float_as_uint(__uint_as_float(v[j * 4 + 1]) + beta * r[j].y);
+      v[j * 4 + 2] = __float_as_uint(__uint_as_float(v[j * 4 + 2]) + beta * r[j].z);
+      v[j * 4 + 3] = __float_as_uint(__uint_as_float(v[j * 4 + 3]) + beta * r[j].w);
     }
   }
+};
+
+// Store 32 final values (float bits in v) of one row chunk with 16-byte accesses.
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* drow, const uint32_t* v);
+template <>
+__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* drow, const uint32_t* v) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j * 8 + e]);
+    reinterpret_cast<bf16x8*>(drow)[j] = pack8(f);
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32<float>(float* drow, const uint32_t* v) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    reinterpret_cast<float4*>(drow)[j] = make_float4(__uint_as_float(v[j * 4]), __uint_as_float(v[j * 4 + 1]),
+                                                     __uint_as_float(v[j * 4 + 2]), __uint_as_float(v[j * 4 + 3]));
 }
 
 // Tile enumeration shared by the three roles: tile t -> (batch, m_tile, n_tile), n fastest.
@@ -152,7 +162,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&acc_empty[a]), 8);  // one arrival per epilogue warp
     }
     fence_barrier_init();
     prefetch_tensormap(&map_a);
@@ -175,7 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
-        if (p.symmetric && tc.n < tc.m) continue;  // below the diagonal: written by the mirror of its twin tile
+        if (p.symmetric && (tc.n + 1) * BN <= tc.m * kBM) continue;  // wholly below the diagonal: mirrored from its twin
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -208,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
-        if (p.symmetric && tc.n < tc.m) continue;
+        if (p.symmetric && (tc.n + 1) * BN <= tc.m * kBM) continue;
         const int acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_ph ^ 1, ab, 2)) { ok = false; break; }
@@ -237,41 +247,85 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
-    const int sub = warp & 3;  // TMEM sub-partition of this warp: lanes [32*sub, 32*sub+32)
+    // ------------------------------------------------------------------ epilogue (8 warps)
+    // Warps 2-5 take the left half of the accumulator's columns, warps 6-9 the right half; warp % 4 selects the
+    // TMEM sub-partition (32 lanes = 32 rows).  The addend C of the next 32-column chunk is fetched while the
+    // current chunk is converted and stored, so its memory latency is paid once per tile, not once per chunk.
+    const int sub = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kHalfCols = BN / 2;
+    constexpr int kChunks = kHalfCols / 32;
     OutT* D = reinterpret_cast<OutT*>(p.D);
     const OutT* C = reinterpret_cast<const OutT*>(p.C);
-    const bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
-                        (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
+    bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+                  (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
+    for (int d = 0; d < p.n_extra; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_extra[d]) & 15) == 0);
     int local_tile = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
-      if (p.symmetric && tc.n < tc.m) continue;
+      if (p.symmetric && (tc.n + 1) * BN <= tc.m * kBM) continue;
       const int acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 4)) { ok = false; break; }
       tc_fence_after();
       const int row = tc.m * kBM + sub * 32 + lane;
+      const bool row_ok = row < p.M;
       const int64_t boff = (int64_t)tc.b * p.batch_stride_d;
+      const int64_t roff = boff + (int64_t)row * p.ldd;
+      CRegs<OutT> cnext;
+      bool have_next = false;
+      {
+        const int col = tc.n * BN + half * kHalfCols;
+        if (C != nullptr && vec_ok && row_ok && col + 32 <= p.N) {
+          cnext.load(C + roff + col);
+          have_next = true;
+        }
+      }
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int ci = 0; ci < kChunks; ++ci) {
+        const int c0 = half * kHalfCols + ci * 32;
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * BN + c0, v);
-        tmem_ld_wait();
+        const CRegs<OutT> ccur = cnext;
+        const bool have_cur = have_next;
+        have_next = false;
         const int col = tc.n * BN + c0;
-        if (row < p.M && col < p.N) {
+        if (ci + 1 < kChunks && C != nullptr && vec_ok && row_ok && col + 64 <= p.N) {
+          cnext.load(C + roff + col + 32);
+          have_next = true;
+        }
+        tmem_ld_wait();
+        if (row_ok && col < p.N) {
           const int ncols = (p.N - col) < 32 ? (p.N - col) : 32;
-          OutT* drow = D + boff + (int64_t)row * p.ldd + col;
-          const OutT* crow = C ? C + boff + (int64_t)row * p.ldd + col : nullptr;
-          store_chunk32<OutT>(drow, crow, v, ncols, p.alpha, p.beta, vec_ok);
-          if (p.symmetric && tc.n > tc.m) {
-            // mirror: D[col+e, row] = D[row, col+e] (symmetric tiles are square, so the twin tile below the
-            // diagonal is never computed).  C, if given, is symmetric too, so the mirrored value is the same.
+          // the twin tile (rows of this chunk's columns, columns of this row) is skipped by the symmetric schedule
+          const bool mirror = p.symmetric && ((row / BN) + 1) * BN <= (col / kBM) * kBM;
+          if (vec_ok && ncols == 32 && (C == nullptr || have_cur)) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(p.alpha * __uint_as_float(v[e]));
+            if (C != nullptr) ccur.add_scaled(v, p.beta);
+            store_row32<OutT>(D + roff + col, v);
+            for (int d = 0; d < p.n_extra; ++d) store_row32<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + roff + col, v);
+            if (mirror) {
+              for (int e = 0; e < 32; ++e) {
+                const OutT val = from_f<OutT>(__uint_as_float(v[e]));
+                const int64_t moff = boff + (int64_t)(col + e) * p.ldd + row;
+                D[moff] = val;
+                for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+              }
+            }
+          } else {
             for (int e = 0; e < ncols; ++e) {
               float f = p.alpha * __uint_as_float(v[e]);
-              if (crow != nullptr) f += p.beta * to_f<OutT>(crow[e]);
-              D[boff + (int64_t)(col + e) * p.ldd + row] = from_f<OutT>(f);
+              if (C != nullptr) f += p.beta * to_f<OutT>(C[roff + col + e]);
+              const OutT val = from_f<OutT>(f);
+              D[roff + col + e] = val;
+              for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[roff + col + e] = val;
+              if (mirror) {
+                const int64_t moff = boff + (int64_t)(col + e) * p.ldd + row;
+                D[moff] = val;
+                for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+              }
             }
           }
         }
@@ -345,9 +399,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 
 int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
-              float beta, bool symmetric, int* status, int sm_count, cudaStream_t st) {
-  // N tile: 256 unless the problem is narrow or the symmetric mirror needs square tiles
-  const int BN = (symmetric || N <= 128) ? 128 : 256;
+              float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st) {
+  const int BN = (N <= 128) ? 128 : 256;
   CUtensorMap ma, mb;
   int r;
   if (a_mn_major)  // memory [K, M]
@@ -366,6 +419,8 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.C = C; p.D = D; p.ldd = ldd; p.batch_stride_d = bsd;
   p.status = status;
   p.symmetric = symmetric ? 1 : 0;
+  p.n_extra = n_extra < 0 ? 0 : (n_extra > 7 ? 7 : n_extra);
+  for (int i = 0; i < 7; ++i) p.D_extra[i] = i < p.n_extra ? d_extra[i] : nullptr;
 #define SEG_GEMM(BNv, AM, BM_)                                                                      \
   (out_f32 ? launch_gemm<BNv, AM, BM_, float>(ma, mb, p, sm_count, st)                              \
            : launch_gemm<BNv, AM, BM_, __nv_bfloat16>(ma, mb, p, sm_count, st))

@@ -85,10 +85,11 @@ void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes
 //   a_mn_major = false: A is [M, K] row-major (lda = row stride);  true: A is stored [K, M].
 //   b_mn_major = false: B is [N, K] row-major (the product is A * B^T); true: B is stored [K, N].
 //   symmetric: A == B and D square: only tiles on or above the diagonal are computed, the rest is mirrored.
+// d_extra[0..n_extra): up to 7 further destination buffers with D's layout (peer memory of other ranks).
 // Strides are in elements; bases and row strides must be 16-byte aligned.  Returns 0 when the launch was issued.
 // `status` is a device int that stays 0 unless a bounded wait inside the kernel gave up.
 int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
-              float beta, bool symmetric, int* status, int sm_count, cudaStream_t st);
+              float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st);
 
 }  // namespace seg

@@ -27,9 +27,12 @@ def usable(*tensors: Tensor) -> bool:
     return True
 
 
-def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, symmetric=False) -> Tensor:
+def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, symmetric=False,
+         extra_dst: list[int] | None = None) -> Tensor:
+    """``extra_dst``: device addresses of up to 7 more buffers with the output's layout (peer memory of other ranks);
+    every output tile is stored to all of them from the epilogue."""
     ops._count()
-    return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric)
+    return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric, extra_dst or [])
 
 
 def mm_nt(x: Tensor, w: Tensor, **kw) -> Tensor:

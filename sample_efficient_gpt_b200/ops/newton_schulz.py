@@ -16,27 +16,35 @@ from torch import Tensor
 from sample_efficient_gpt_b200.ops import gemm as G
 
 
-def ns_iterations(X: Tensor, Y: Tensor, coeffs) -> Tensor:
+def ns_iterations(X: Tensor, Y: Tensor, coeffs, final_extra_dst=None) -> Tensor:
     """Run the chain on normalised bf16 ``X [n, R, C]`` ping-ponging with ``Y`` (same shape); returns the buffer
-    that holds the result (``Y`` for an odd number of iterations)."""
+    that holds the result (``Y`` for an odd number of iterations).
+
+    ``final_extra_dst(buffer) -> list[int]``: peer addresses that mirror the buffer receiving the last iteration's
+    output; the last GEMM then stores every tile to those as well (the all-gather of the result happens in its
+    epilogue).  Returns ``(result, True)`` instead of ``result`` when that happened."""
     n, R, C = X.shape
     tall = R > C
     r = min(R, C)
     if r % 8 == 0 and max(R, C) % 8 == 0 and G.usable(X, Y):
         A = torch.empty((n, r, r), dtype=torch.bfloat16, device=X.device)
         B = torch.empty_like(A)
-        for a, b, c in coeffs:
+        last = len(coeffs) - 1
+        pushed = False
+        for it, (a, b, c) in enumerate(coeffs):
             if tall:
                 G.gemm(X, X, out=A, a_mn=True, b_mn=True, symmetric=True)  # X^T X
             else:
                 G.gemm(X, X, out=A, symmetric=True)  # X X^T
             G.gemm(A, A, c=A, out=B, alpha=c, beta=b, symmetric=True)
+            extra = final_extra_dst(Y) if (it == last and final_extra_dst is not None) else None
+            pushed = pushed or bool(extra)
             if tall:
-                G.gemm(X, B, c=X, out=Y, alpha=1.0, beta=a)  # X B (B symmetric)
+                G.gemm(X, B, c=X, out=Y, alpha=1.0, beta=a, extra_dst=extra)  # X B (B symmetric)
             else:
-                G.gemm(B, X, c=X, out=Y, b_mn=True, alpha=1.0, beta=a)  # B X
+                G.gemm(B, X, c=X, out=Y, b_mn=True, alpha=1.0, beta=a, extra_dst=extra)  # B X
             X, Y = Y, X
-        return X
+        return (X, True) if final_extra_dst is not None and pushed else X
     for a, b, c in coeffs:
         A = (X.mT @ X) if tall else (X @ X.mT)
         B = torch.baddbmm(A, A, A, beta=b, alpha=c)

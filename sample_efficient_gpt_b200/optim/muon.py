@@ -193,11 +193,23 @@ class Muon(torch.optim.Optimizer):
                               b.momentum, b.xbuf, group["momentum"], 1e-7)
             ops._count(2)
             s0 = b.slot_of[idx[0]]
-            res = ns_iterations(b.xbuf[s0 : s0 + len(idx)], b.update[s0 : s0 + len(idx)], POLAR_EXPRESS_COEFFS)
-            if res.data_ptr() != b.update[s0].data_ptr():
-                b.update[s0 : s0 + len(idx)].copy_(res)
+            dst = b.update[s0 : s0 + len(idx)]
+            push = None
+            if self.is_distributed and self.comm is not None and hasattr(self.comm, "peer_addresses"):
+                # the last Newton-Schulz GEMM stores its tiles into every rank's update buffer
+                push = lambda buf: self.comm.peer_addresses(buf) if buf.data_ptr() == dst.data_ptr() else None  # noqa: E731
+            res = ns_iterations(b.xbuf[s0 : s0 + len(idx)], dst, POLAR_EXPRESS_COEFFS, final_extra_dst=push)
+            pushed = isinstance(res, tuple)
+            res = res[0] if pushed else res
+            if res.data_ptr() != dst.data_ptr():
+                dst.copy_(res)
+        else:
+            pushed = self.is_distributed and self.comm is not None and hasattr(self.comm, "peer_addresses")
         if self.is_distributed:
-            self._gather_updates(b)
+            if pushed and self._all_ranks_push(b):
+                self.comm.barrier()  # every rank's tiles have landed everywhere
+            else:
+                self._gather_updates(b)
         lr, wd = group["lr"], group["weight_decay"]
         lr_mul, wd_mul = getattr(b.params[0], "lr_mul", 1.0), getattr(b.params[0], "wd_mul", 1.0)
         mode = 1 if self._plain_decay else (2 if self._cautious else 0)
@@ -213,6 +225,13 @@ class Muon(torch.optim.Optimizer):
                 if sh is not None:
                     sh.copy_(p)
         return sq
+
+    def _all_ranks_push(self, b: _ShapeBatch) -> bool:
+        """The in-epilogue all-gather is used only when every rank takes it for this shape (same decision everywhere)."""
+        r = min(b.rows, b.cols)
+        return r % 8 == 0 and max(b.rows, b.cols) % 8 == 0 and all(
+            any(b.owner(i) == rk for i in range(b.n)) for rk in range(self.world)
+        )
 
     def _gather_updates(self, b: _ShapeBatch):
         if self.comm is not None:

@@ -123,6 +123,17 @@ class SymmComm:
         ops._count()
         self.seq += 2
 
+    def peer_addresses(self, t: Tensor) -> list[int]:
+        """Addresses of the other ranks' copies of ``t`` (a view of a ``symm_zeros`` buffer)."""
+        hdl, off = self._handle_of(t)
+        return [int(p) + off for r, p in enumerate(hdl.buffer_ptrs) if r != self.rank]
+
+    def barrier(self):
+        """Device-side barrier across ranks on the current stream (a zero-byte all-gather)."""
+        ops.ext().comm_allgather(self.flag_ptrs, self.flag_ptrs, 0, 0, self.rank, self.seq, 1, self.status)
+        ops._count()
+        self.seq += 2
+
     def check(self):
         """Host read (synchronises): raises when a kernel gave up waiting for a peer."""
         code = int(self.status.item())
