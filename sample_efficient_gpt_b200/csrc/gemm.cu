@@ -44,7 +44,8 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kStagingBytes = 8 * 32 * 32 * 4;  // one 32x32 fp32 transposition tile per epilogue warp
+  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 struct GemmParams {
@@ -59,66 +60,6 @@ struct GemmParams {
   void* D_extra[7];  // further destinations with D's layout (peer-mapped buffers of other ranks): every tile is
   int n_extra;       // stored to all of them, which turns the epilogue into the all-gather of the result
 };
-
-// Raw addend values of one 32-column row chunk, fetched ahead of use.
-template <typename OutT>
-struct CRegs;
-template <>
-struct CRegs<__nv_bfloat16> {
-  uint4 r[4];
-  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r[j] = reinterpret_cast<const uint4*>(p)[j];
-  }
-  // v[e] (float bits) += beta * c[e]
-  __device__ __forceinline__ void add_scaled(uint32_t* v, float beta) const {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float c[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(&r[j]), c);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[j * 8 + e] = __float_as_uint(__uint_as_float(v[j * 8 + e]) + beta * c[e]);
-    }
-  }
-};
-template <>
-struct CRegs<float> {
-  float4 r[8];
-  __device__ __forceinline__ void load(const float* p) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) r[j] = reinterpret_cast<const float4*>(p)[j];
-  }
-  __device__ __forceinline__ void add_scaled(uint32_t* v, float beta) const {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      v[j * 4 + 0] = __float_as_uint(__uint_as_float(v[j * 4 + 0]) + beta * r[j].x);
-      v[j * 4 + 1] = __float_as_uint(__uint_as_float(v[j * 4 + 1]) + beta * r[j].y);
-      v[j * 4 + 2] = __float_as_uint(__uint_as_float(v[j * 4 + 2]) + beta * r[j].z);
-      v[j * 4 + 3] = __float_as_uint(__uint_as_float(v[j * 4 + 3]) + beta * r[j].w);
-    }
-  }
-};
-
-// Store 32 final values (float bits in v) of one row chunk with 16-byte accesses.
-template <typename OutT>
-__device__ __forceinline__ void store_row32(OutT* drow, const uint32_t* v);
-template <>
-__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* drow, const uint32_t* v) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float f[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j * 8 + e]);
-    reinterpret_cast<bf16x8*>(drow)[j] = pack8(f);
-  }
-}
-template <>
-__device__ __forceinline__ void store_row32<float>(float* drow, const uint32_t* v) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    reinterpret_cast<float4*>(drow)[j] = make_float4(__uint_as_float(v[j * 4]), __uint_as_float(v[j * 4 + 1]),
-                                                     __uint_as_float(v[j * 4 + 2]), __uint_as_float(v[j * 4 + 3]));
-}
 
 // Tile enumeration shared by the three roles: tile t -> (batch, m_tile, n_tile), n fastest.
 struct TileCoord {
@@ -140,7 +81,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* bar_area = smem + kStages * S::kStageBytes;
+  uint8_t* stage_area = smem + kStages * S::kStageBytes;
+  uint8_t* bar_area = stage_area + S::kStagingBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* acc_full = empty_bar + kStages;
@@ -249,12 +191,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else {
     // ------------------------------------------------------------------ epilogue (8 warps)
     // Warps 2-5 take the left half of the accumulator's columns, warps 6-9 the right half; warp % 4 selects the
-    // TMEM sub-partition (32 lanes = 32 rows).  The addend C of the next 32-column chunk is fetched while the
-    // current chunk is converted and stored, so its memory latency is paid once per tile, not once per chunk.
+    // TMEM sub-partition (32 lanes = 32 rows).  tcgen05.ld hands every lane one row of a 32-column chunk; the chunk
+    // is transposed through a private, XOR-swizzled 4 KB staging tile so that global accesses are coalesced: in the
+    // store phase 8 consecutive lanes cover one row (4 fp32 values each), 4 rows per instruction, full sectors.
+    // The addend C is read in that same layout, one chunk ahead of its use.
     const int sub = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int ep = warp - 2;
+    const int half = ep >> 2;
     constexpr int kHalfCols = BN / 2;
     constexpr int kChunks = kHalfCols / 32;
+    float* stage = reinterpret_cast<float*>(stage_area) + ep * (32 * 32);
+    const int q = lane & 7, rsub = lane >> 3;  // store phase: this lane holds columns [4q, 4q+4) of rows rsub + 4i
     OutT* D = reinterpret_cast<OutT*>(p.D);
     const OutT* C = reinterpret_cast<const OutT*>(p.C);
     bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
@@ -269,65 +216,105 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 4)) { ok = false; break; }
       tc_fence_after();
-      const int row = tc.m * kBM + sub * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row0 = tc.m * kBM + sub * 32;  // first row of this warp's 32-row band
       const int64_t boff = (int64_t)tc.b * p.batch_stride_d;
-      const int64_t roff = boff + (int64_t)row * p.ldd;
-      CRegs<OutT> cnext;
+      float4 cnext[8];
       bool have_next = false;
+      auto fetch_c = [&](int col, float4* dst) {  // coalesced read of C[row0 + rsub + 4i, col + 4q .. +4)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = row0 + rsub + 4 * i;
+          dst[i] = (r < p.M) ? load4<OutT>(C + boff + (int64_t)r * p.ldd + col + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      };
       {
         const int col = tc.n * BN + half * kHalfCols;
-        if (C != nullptr && vec_ok && row_ok && col + 32 <= p.N) {
-          cnext.load(C + roff + col);
+        if (C != nullptr && vec_ok && col + 32 <= p.N) {
+          fetch_c(col, cnext);
           have_next = true;
         }
       }
 #pragma unroll 1
       for (int ci = 0; ci < kChunks; ++ci) {
         const int c0 = half * kHalfCols + ci * 32;
+        const int col = tc.n * BN + c0;
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * BN + c0, v);
-        const CRegs<OutT> ccur = cnext;
+        float4 ccur[8];
         const bool have_cur = have_next;
+        if (have_cur) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ccur[i] = cnext[i];
+        }
         have_next = false;
-        const int col = tc.n * BN + c0;
-        if (ci + 1 < kChunks && C != nullptr && vec_ok && row_ok && col + 64 <= p.N) {
-          cnext.load(C + roff + col + 32);
+        if (ci + 1 < kChunks && C != nullptr && vec_ok && col + 64 <= p.N) {
+          fetch_c(col + 32, cnext);
           have_next = true;
         }
         tmem_ld_wait();
-        if (row_ok && col < p.N) {
+        if (col < p.N) {  // warp-uniform
           const int ncols = (p.N - col) < 32 ? (p.N - col) : 32;
-          // the twin tile (rows of this chunk's columns, columns of this row) is skipped by the symmetric schedule
-          const bool mirror = p.symmetric && ((row / BN) + 1) * BN <= (col / kBM) * kBM;
-          if (vec_ok && ncols == 32 && (C == nullptr || have_cur)) {
+          const bool fast = vec_ok && ncols == 32 && (C == nullptr || have_cur);
+          // 1. row-per-lane registers -> staging tile (piece j of row `lane` lives at slot j ^ (lane & 7))
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(p.alpha * __uint_as_float(v[e]));
-            if (C != nullptr) ccur.add_scaled(v, p.beta);
-            store_row32<OutT>(D + roff + col, v);
-            for (int d = 0; d < p.n_extra; ++d) store_row32<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + roff + col, v);
-            if (mirror) {
-              for (int e = 0; e < 32; ++e) {
-                const OutT val = from_f<OutT>(__uint_as_float(v[e]));
-                const int64_t moff = boff + (int64_t)(col + e) * p.ldd + row;
-                D[moff] = val;
-                for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+          for (int j = 0; j < 8; ++j)
+            reinterpret_cast<float4*>(stage + lane * 32)[j ^ (lane & 7)] =
+                make_float4(p.alpha * __uint_as_float(v[4 * j]), p.alpha * __uint_as_float(v[4 * j + 1]),
+                            p.alpha * __uint_as_float(v[4 * j + 2]), p.alpha * __uint_as_float(v[4 * j + 3]));
+          __syncwarp();
+          // 2. transposed read, addend, coalesced stores
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = rsub + 4 * i, r = row0 + rl;
+            float4 f = reinterpret_cast<const float4*>(stage + rl * 32)[q ^ (rl & 7)];
+            if (r < p.M) {
+              const int64_t off = boff + (int64_t)r * p.ldd + col + 4 * q;
+              if (fast) {
+                if (C != nullptr) {
+                  f.x += p.beta * ccur[i].x; f.y += p.beta * ccur[i].y; f.z += p.beta * ccur[i].z; f.w += p.beta * ccur[i].w;
+                }
+                store4<OutT>(D + off, f);
+                for (int d = 0; d < p.n_extra; ++d) store4<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + off, f);
+              } else {
+                const float fv[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (4 * q + e < ncols) {
+                    float val = fv[e];
+                    if (C != nullptr) val += p.beta * to_f<OutT>(C[off + e]);
+                    D[off + e] = from_f<OutT>(val);
+                    for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[off + e] = from_f<OutT>(val);
+                    if (e == 0) f.x = val; else if (e == 1) f.y = val; else if (e == 2) f.z = val; else f.w = val;
+                  }
+                }
               }
             }
-          } else {
-            for (int e = 0; e < ncols; ++e) {
-              float f = p.alpha * __uint_as_float(v[e]);
-              if (C != nullptr) f += p.beta * to_f<OutT>(C[roff + col + e]);
-              const OutT val = from_f<OutT>(f);
-              D[roff + col + e] = val;
-              for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[roff + col + e] = val;
-              if (mirror) {
-                const int64_t moff = boff + (int64_t)(col + e) * p.ldd + row;
-                D[moff] = val;
-                for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+            // keep the final values in the staging tile for the mirror pass
+            if (p.symmetric) reinterpret_cast<float4*>(stage + rl * 32)[q ^ (rl & 7)] = f;
+          }
+          // 3. symmetric outputs: the twin tile (this chunk's columns as rows) is skipped by the schedule, so its
+          //    elements are written from here, column by column, with consecutive lanes on consecutive addresses
+          const int row = row0 + lane;
+          const bool mirror = p.symmetric && ((row0 / BN) + 1) * BN <= (col / kBM) * kBM;
+          if (mirror) {
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 f = reinterpret_cast<const float4*>(stage + lane * 32)[j ^ (lane & 7)];
+              const float fv[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int cc = 4 * j + e;
+                if (row < p.M && cc < ncols) {
+                  const OutT val = from_f<OutT>(fv[e]);
+                  const int64_t moff = boff + (int64_t)(col + cc) * p.ldd + row;
+                  D[moff] = val;
+                  for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+                }
               }
             }
           }
+          __syncwarp();  // the staging tile is rewritten by the next chunk
         }
       }
       tc_fence_before();
