@@ -1,0 +1,303 @@
+// Causal flash-attention forward for sm_100a on tcgen05 tensor cores, native GQA, head_dim 64, bf16.
+//
+//   S = Q K^T / sqrt(hd) (causal), P = softmax(S), O = P V, LSE = log sum exp(S)      per (batch, query head)
+// q [B,S,H,hd], k/v [B,S,Hkv,hd] (token-major, as written by the qkv post-processing kernel), o like q, lse [B,H,S].
+//
+// One CTA per (128-query tile, batch, head); two CTAs share an SM (256 TMEM columns and ~100 KB of shared memory
+// each), so one CTA's tensor-core work overlaps the other's softmax.  Roles (192 threads):
+//   warp 0  : TMA producer - Q tile once, then K/V tiles (128 keys) into a 2-stage ring (4-D tensor maps, 128-byte
+//             swizzle, no multicast).
+//   warp 1  : MMA issuer - S(j) = Q K_j^T into TMEM (128x128 fp32), and, once the softmax warps have written P(j) to
+//             shared memory, PV(j) = P(j) V_j into a second TMEM accumulator (128x64 fp32).  V is consumed in place as
+//             an MN-major operand, K as a K-major one.
+//   warps 2-5: softmax - every thread owns one query row: reads S with tcgen05.ld, online max/sum in the exp2 domain,
+//             writes P as bf16 into the swizzled operand layout, and accumulates O in registers
+//             (O = O*alpha + PV(j-1), one tile behind, so the PV product overlaps the next tile's first pass).
+// The reference uses PyTorch SDPA on repeated K/V heads (transformer/attention.py:207-236) or a Triton kernel
+// (transformer/ops/triton_flash_attn.py:12-101).
+// Every mbarrier wait is bounded; on expiry the CTA unwinds, frees TMEM and sets the status word.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "sm100.cuh"
+
+namespace seg {
+
+using namespace sm100;
+
+constexpr int kAQ = 128;   // queries per CTA
+constexpr int kAK = 128;   // keys per tile
+constexpr int kAHD = 64;   // head dim
+constexpr int kAttnThreads = 192;
+constexpr int kTileBytes = kAK * kAHD * 2;  // 16 KB: one Q, K or V tile
+constexpr int kPBytes = kAQ * kAK * 2;      // 32 KB: P as two 64-column swizzle atoms
+constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * 2 * kTileBytes /*K,V x 2 stages*/ + kPBytes + 128;  // two CTAs per SM
+
+struct AttnParams {
+  int B, S, H, Hkv;
+  float scale_log2;  // log2(e) / sqrt(hd)
+  __nv_bfloat16* o;
+  float* lse;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base: refuse instead of computing garbage
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 10);
+    return;
+  }
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + kTileBytes;            // stage s: K at s*32K, V at s*32K + 16K
+  uint8_t* sP = sKV + 4 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_empty = bars + 6;
+  uint64_t* p_full = bars + 7;
+  uint64_t* pv_full = bars + 8;
+  uint64_t* pv_empty = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = p.S / kAQ;
+  const int qt = n_qt - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int kvh = h / (p.H / p.Hkv);
+  const int n_tiles = qt + 1;  // causal: key tiles 0..qt
+  const AbortState ab{cta_abort, p.status};
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    mbar_init(smem_u32(q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&kv_full[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), 1);
+    }
+    mbar_init(smem_u32(s_full), 1);
+    mbar_init(smem_u32(s_empty), 4);
+    mbar_init(smem_u32(p_full), 4);
+    mbar_init(smem_u32(pv_full), 1);
+    mbar_init(smem_u32(pv_empty), 4);
+    fence_barrier_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;         // columns [0,128): S
+  const uint32_t tmem_pv = tmem_base + 128;  // columns [128,192): P V
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(smem_u32(q_full), kTileBytes);
+      tma_load_4d(smem_u32(sQ), &map_q, smem_u32(q_full), 0, h, qt * kAQ, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1, ab, 11)) break;
+        const uint32_t fb = smem_u32(&kv_full[st]);
+        mbar_expect_tx(fb, 2 * kTileBytes);
+        tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes), &map_k, fb, 0, kvh, j * kAK, b);
+        tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes + kTileBytes), &map_v, fb, 0, kvh, j * kAK, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(kAQ, kAK, false, false);   // Q (K-major) x K (K-major)
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kAQ, kAHD, false, true);  // P (K-major) x V (MN-major)
+      bool ok = mbar_wait(smem_u32(q_full), 0, ab, 12);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t sk = smem_u32(sKV + st * 2 * kTileBytes), sv = sk + kTileBytes;
+        if (!mbar_wait(smem_u32(&kv_full[st]), (j >> 1) & 1, ab, 13)) break;
+        if (j > 0 && !mbar_wait(smem_u32(s_empty), (j - 1) & 1, ab, 14)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kAHD / 16; ++k)
+          umma_bf16(tmem_s, make_smem_desc(smem_u32(sQ) + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s, k > 0);
+        umma_commit(smem_u32(s_full));
+        if (!mbar_wait(smem_u32(p_full), j & 1, ab, 15)) break;
+        if (j > 0 && !mbar_wait(smem_u32(pv_empty), (j - 1) & 1, ab, 16)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kAK / 16; ++k)
+          umma_bf16(tmem_pv, make_smem_desc(smem_u32(sP) + (k >> 2) * (kAQ * 128) + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(sv + k * 2048, kTileBytes, 1024), idesc_pv, k > 0);
+        umma_commit(smem_u32(pv_full));
+        umma_commit(smem_u32(&kv_empty[st]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax warps: one query row per thread
+    const int sub = warp & 3;
+    const int r = sub * 32 + lane;  // row inside the tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+    float o_acc[kAHD];
+#pragma unroll
+    for (int i = 0; i < kAHD; ++i) o_acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(smem_u32(s_full), j & 1, ab, 17)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (j == qt);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kAK / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float x = __uint_as_float(v[e]);
+          if (!diag || (c * 32 + e) <= r) mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float alpha = exp2f(m - m_new);  // 0 on the first tile (m = -inf)
+      if (j > 0) {  // fold in P V of the previous tile (it is relative to the old maximum)
+        if (!mbar_wait(smem_u32(pv_full), (j - 1) & 1, ab, 18)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < kAHD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_pv + lane_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o_acc[c * 32 + e] += __uint_as_float(v[e]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(pv_empty));
+      }
+#pragma unroll
+      for (int i = 0; i < kAHD; ++i) o_acc[i] *= alpha;
+      l *= alpha;
+      // pass 2: probabilities -> bf16 operand tile (row r, 16-byte chunk c16 stored at c16 ^ (r & 7) inside its atom)
+#pragma unroll 1
+      for (int c = 0; c < kAK / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float x = __uint_as_float(v[e]) * p.scale_log2 - m_new;
+          const float pe = (!diag || (c * 32 + e) <= r) ? exp2f(x) : 0.f;
+          pr[e] = pe;
+          l += pe;
+        }
+        uint8_t* atom = sP + (c >> 1) * (kAQ * 128) + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int c16 = (c & 1) * 4 + q4;
+          *reinterpret_cast<bf16x8*>(atom + ((c16 ^ (r & 7)) << 4)) = pack8(pr + q4 * 8);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();  // make the P tile visible to the tensor core's shared-memory reads
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(s_empty));
+        mbar_arrive(smem_u32(p_full));
+      }
+      m = m_new;
+    }
+    if (ok && mbar_wait(smem_u32(pv_full), (n_tiles - 1) & 1, ab, 19)) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+      const int row = qt * kAQ + r;
+      __nv_bfloat16* orow = p.o + (((size_t)b * p.S + row) * p.H + h) * kAHD;
+#pragma unroll
+      for (int c = 0; c < kAHD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_pv + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) f[e] = (o_acc[c * 32 + e] + __uint_as_float(v[e])) * inv;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(orow + c * 32)[q4] = pack8(f + q4 * 8);
+      }
+      p.lse[((size_t)b * p.H + h) * p.S + row] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  if (*cta_abort != 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
+}
+
+// 4-D bf16 tensor map over [B, S, heads, hd] with a {64, 1, 128, 1} box and 128-byte swizzle.
+typedef CUresult (*EncodeTiledFn4)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_map_bshd(CUtensorMap* map, const void* base, int B, int S, int heads, int hd) {
+  static EncodeTiledFn4 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return -1;
+    fn = reinterpret_cast<EncodeTiledFn4>(ptr);
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)heads * hd * 2, (cuuint64_t)S * heads * hd * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, int Hkv, int hd, int* status,
+             cudaStream_t st) {
+  if (hd != kAHD || S % kAQ != 0 || H % Hkv != 0) return -10;
+  CUtensorMap mq, mk, mv;
+  int r = make_map_bshd(&mq, q, B, S, H, hd);
+  if (r == 0) r = make_map_bshd(&mk, k, B, S, Hkv, hd);
+  if (r == 0) r = make_map_bshd(&mv, v, B, S, Hkv, hd);
+  if (r != 0) return 100 + r;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) return -2;
+    configured = true;
+  }
+  AttnParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.status = status;
+  dim3 grid(S / kAQ, B * H);
+  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(mq, mk, mv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace seg

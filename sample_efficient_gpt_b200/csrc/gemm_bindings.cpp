@@ -94,6 +94,25 @@ void gemm_reset_status(int64_t device_index) {
   st.status.zero_();
 }
 
+// Causal GQA flash attention forward on the tcgen05 kernel: returns (o, lse).
+std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
+  TORCH_CHECK(causal, "only causal attention is implemented");
+  for (const Tensor* t : {&q, &k, &v}) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->dim() == 4, "q/k/v must be contiguous CUDA bf16 [B,S,H,hd]");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "q/k/v must be 16-byte aligned");
+  }
+  const int B = q.size(0), S = q.size(1), H = q.size(2), hd = q.size(3), Hkv = k.size(2);
+  TORCH_CHECK(k.size(0) == B && k.size(1) == S && k.size(3) == hd && v.sizes() == k.sizes(), "k/v shape mismatch");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor o = torch::empty_like(q);
+  Tensor lse = torch::empty({B, H, S}, q.options().dtype(at::kFloat));
+  auto& st = device_state(q.device());
+  const int rc = seg::attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, S, H, Hkv, hd,
+                               st.status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "attn_fwd: unsupported shape or launch failure (code ", rc, ")");
+  return {o, lse};
+}
+
 }  // namespace
 
 void register_gemm(pybind11::module_& m) {
@@ -101,6 +120,7 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("out_f32") = false, pybind11::arg("a_mn") = false, pybind11::arg("b_mn") = false, pybind11::arg("alpha") = 1.0,
         pybind11::arg("beta") = 0.0, pybind11::arg("symmetric") = false,
         pybind11::arg("extra_dst") = std::vector<int64_t>());
+  m.def("fa_fwd", &fa_fwd);
   m.def("gemm_status", &gemm_status);
   m.def("gemm_reset_status", &gemm_reset_status);
 }

@@ -92,4 +92,10 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st);
 
+// ---- attn_fwd.cu (tcgen05 flash attention, forward)
+// q [B,S,H,hd], k/v [B,S,Hkv,hd] bf16, o like q, lse fp32 [B,H,S]; causal; hd == 64, S % 128 == 0.
+// Returns 0 when launched, a negative code for unsupported shapes.
+int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, int Hkv, int hd, int* status,
+             cudaStream_t st);
+
 }  // namespace seg

@@ -99,11 +99,11 @@ def qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, 
 
 
 # ----------------------------------------------------------------------------- attention
-def attention_fwd(q, k, v, causal: bool = True, q_start: int = 0):
+def attention_fwd(q, k, v, causal: bool = True, q_start: int = 0, for_backward: bool = True):
     if q.is_cuda:
         from sample_efficient_gpt_b200.ops import attention as attn_impl
 
-        return attn_impl.forward(q, k, v, causal, q_start)
+        return attn_impl.forward(q, k, v, causal, q_start, for_backward)
     return ref.attention_fwd(q, k, v, causal, q_start)
 
 

@@ -26,19 +26,23 @@ class _Tape:
         self.q, self.k, self.v, self.out = q, k, v, out
 
 
-def _native_ok(q: Tensor, k: Tensor, q_start: int) -> bool:
+def _native_ok(q: Tensor, k: Tensor, q_start: int, for_backward: bool) -> bool:
     impl = os.environ.get("SEGPT_ATTN_IMPL", "auto")
     if impl == "library" or not ops.has_kernel("fa_fwd"):
         if impl == "native":
             raise RuntimeError("SEGPT_ATTN_IMPL=native but the flash-attention kernels are not built")
         return False
+    if for_backward and not ops.has_kernel("fa_bwd"):
+        return False  # the library backward needs the library forward's tape
     hd = q.size(-1)
-    return q.dtype == torch.bfloat16 and hd in (64, 128) and q_start == 0 and q.size(1) == k.size(1) and q.size(1) % 128 == 0
+    return (q.dtype == torch.bfloat16 and hd == 64 and q_start == 0 and q.size(1) == k.size(1) and q.size(1) % 128 == 0
+            and q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
 
 
-def forward(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, q_start: int = 0):
-    """q [B,S,H,hd], k/v [B,S,Hkv,hd] -> (O [B,S,H,hd], ctx)."""
-    if _native_ok(q, k, q_start):
+def forward(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, q_start: int = 0, for_backward: bool = True):
+    """q [B,S,H,hd], k/v [B,S,Hkv,hd] -> (O [B,S,H,hd], ctx).  ``for_backward=False`` (evaluation) lets the native
+    forward kernel run even when no native backward is built."""
+    if causal and _native_ok(q, k, q_start, for_backward):
         ops._count()
         o, lse = ops.ext().fa_fwd(q, k, v, causal)
         return o, lse

@@ -106,8 +106,14 @@ def bench_attention(a):
     t_f = timeit(fwd, a.iters)
     fwd()
     t_b = timeit(lambda: (fwd(), bwd()), a.iters) - t_f
-    print(json.dumps({"op": "attention", "seq": S, "fwd_ms": t_f, "fwd_tflops": fl_f / t_f, "bwd_ms": t_b, "bwd_tflops": 2.5 * fl_f / t_b,
-                      "impl": "native" if ops.has_kernel("fa_fwd") else "library (SDPA)"}))
+    out = {"op": "attention", "seq": S, "library_fwd_ms": t_f, "library_fwd_tflops": fl_f / t_f, "library_bwd_ms": t_b,
+           "library_bwd_tflops": 2.5 * fl_f / t_b}
+    if ops.has_kernel("fa_fwd"):
+        from sample_efficient_gpt_b200.ops import gemm as G
+
+        t_n = timeit(lambda: ops.attention_fwd(q, k, v, True, 0, for_backward=False), a.iters)
+        out.update({"native_fwd_ms": t_n, "native_fwd_tflops": fl_f / t_n, "status": G.status()})
+    print(json.dumps(out))
 
 
 def bench_linear_ce(a):

@@ -97,7 +97,7 @@ class FusedEngine:
         ops.wgrad_accumulate(p.grad, dy, x, self._first_accum)
 
     # ------------------------------------------------------------------ one block
-    def _layer_fwd(self, i: int, res: Tensor, delta: Tensor | None, v1: Tensor | None, B: int, S: int, want_kurt=True):
+    def _layer_fwd(self, i: int, res: Tensor, delta: Tensor | None, v1: Tensor | None, B: int, S: int, want_kurt=True, train=True):
         blk = self.model.blocks[i]
         at = blk.attn
         H, Hkv, hd = self.H, self.Hkv, self.hd
@@ -110,7 +110,7 @@ class FusedEngine:
         q, k, v = ops.qkv_post_fwd(
             qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm
         )
-        o, lse = ops.attention_fwd(q, k, v, True, 0)
+        o, lse = ops.attention_fwd(q, k, v, True, 0, for_backward=train)
         g = ops.gate_fwd(o.view(T, H, hd), z) if at.gating else o.view(T, H * hd)
         a = ops.matmul_nt(g, self._w(at.out.linear.weight))
         y, n2, rstd2, _ = ops.add_rmsnorm_fwd(x, a, blk.ln2.gain, scale, blk.ln2.eps, self.lp, False)
@@ -247,7 +247,7 @@ class FusedEngine:
         res = model.embedding.weight.detach()[tokens.reshape(-1).long()].float()
         delta, v1, kurts = None, None, []
         for i in range(model.n_layers):
-            res, delta, v, kurt, _ = self._layer_fwd(i, res, delta, v1, B, S)
+            res, delta, v, kurt, _ = self._layer_fwd(i, res, delta, v1, B, S, train=False)
             if v1 is None:
                 v1 = v
             kurts.append(kurt)

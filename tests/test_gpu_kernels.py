@@ -164,3 +164,20 @@ def test_multi_tensor_adamw_ema_cast():
     _ext().cast_bf16(dst, ps)
     for d_, p in zip(dst, ps):
         assert torch.equal(d_, p.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 6, 2), (2, 1024, 3, 1)])
+def test_native_attention_forward(B, S, H, Hkv):
+    from sample_efficient_gpt_b200.ops import gemm as G
+
+    assert ops.has_kernel("fa_fwd")
+    torch.manual_seed(7)
+    q = torch.randn(B, S, H, 64, device=DEV).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, 64, device=DEV).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, 64, device=DEV).to(torch.bfloat16)
+    o, lse = _ext().fa_fwd(q, k, v, True)
+    torch.cuda.synchronize()
+    assert G.status() == 0, "a bounded wait inside the attention kernel gave up"
+    o_ref, lse_ref = ref.attention_fwd(q.float(), k.float(), v.float(), True, 0)
+    close(o, o_ref, 2e-2, 2e-2, name="O")
+    close(lse, lse_ref, 2e-2, name="LSE")
