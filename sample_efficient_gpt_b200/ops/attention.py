@@ -26,7 +26,7 @@ class _Tape:
         self.q, self.k, self.v, self.out = q, k, v, out
 
 
-def _native_ok(q: Tensor, k: Tensor, q_start: int, for_backward: bool) -> bool:
+def _native_ok(q: Tensor, k: Tensor, v: Tensor, q_start: int, for_backward: bool) -> bool:
     impl = os.environ.get("SEGPT_ATTN_IMPL", "auto")
     if impl == "library" or not ops.has_kernel("fa_fwd"):
         if impl == "native":
@@ -42,7 +42,7 @@ def _native_ok(q: Tensor, k: Tensor, q_start: int, for_backward: bool) -> bool:
 def forward(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, q_start: int = 0, for_backward: bool = True):
     """q [B,S,H,hd], k/v [B,S,Hkv,hd] -> (O [B,S,H,hd], ctx).  ``for_backward=False`` (evaluation) lets the native
     forward kernel run even when no native backward is built."""
-    if causal and _native_ok(q, k, q_start, for_backward):
+    if causal and _native_ok(q, k, v, q_start, for_backward):
         ops._count()
         o, lse = ops.ext().fa_fwd(q, k, v, causal)
         return o, lse
