@@ -10,9 +10,9 @@
 //   warp 1  : MMA issuer - S(j) = Q K_j^T into TMEM (128x128 fp32), and, once the softmax warps have written P(j) to
 //             shared memory, PV(j) = P(j) V_j into a second TMEM accumulator (128x64 fp32).  V is consumed in place as
 //             an MN-major operand, K as a K-major one.
-//   warps 2-5: softmax - every thread owns one query row: reads S with tcgen05.ld, online max/sum in the exp2 domain,
-//             writes P as bf16 into the swizzled operand layout, and accumulates O in registers
-//             (O = O*alpha + PV(j-1), one tile behind, so the PV product overlaps the next tile's first pass).
+//   warps 2-5: softmax - every thread owns one query row: reads S with tcgen05.ld into registers (and releases the S
+//             accumulator at once, so the next Q K^T overlaps the softmax), online max/sum in the exp2 domain, writes
+//             P as bf16 into the swizzled operand layout.  O accumulates in TMEM and is rescaled lazily.
 // The reference uses PyTorch SDPA on repeated K/V heads (transformer/attention.py:207-236) or a Triton kernel
 // (transformer/ops/triton_flash_attn.py:12-101).
 // Every mbarrier wait is bounded; on expiry the CTA unwinds, frees TMEM and sets the status word.
@@ -41,6 +41,12 @@ struct AttnParams {
   float* lse;
   int* status;
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -134,12 +140,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           umma_bf16(tmem_s, make_smem_desc(smem_u32(sQ) + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s, k > 0);
         umma_commit(smem_u32(s_full));
         if (!mbar_wait(smem_u32(p_full), j & 1, ab, 15)) break;
-        if (j > 0 && !mbar_wait(smem_u32(pv_empty), (j - 1) & 1, ab, 16)) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kAK / 16; ++k)
           umma_bf16(tmem_pv, make_smem_desc(smem_u32(sP) + (k >> 2) * (kAQ * 128) + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(sv + k * 2048, kTileBytes, 1024), idesc_pv, k > 0);
+                    make_smem_desc(sv + k * 2048, kTileBytes, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(smem_u32(pv_full));
         umma_commit(smem_u32(&kv_empty[st]));
       }
@@ -147,80 +152,78 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax warps: one query row per thread
+    // O accumulates in TMEM across key tiles.  It is rescaled only when the running maximum grew by more than 2^8
+    // since the last rescale (probabilities are then at most 256, harmless for bf16 operands and fp32 sums), which
+    // after the first tiles is rare; the decision is taken per warp because TMEM loads/stores are warp-collective.
     const int sub = warp & 3;
     const int r = sub * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
-    float o_acc[kAHD];
-#pragma unroll
-    for (int i = 0; i < kAHD; ++i) o_acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (!mbar_wait(smem_u32(s_full), j & 1, ab, 17)) { ok = false; break; }
       tc_fence_after();
-      const bool diag = (j == qt);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kAK / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
+      uint32_t v[kAK];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float x = __uint_as_float(v[e]);
-          if (!diag || (c * 32 + e) <= r) mx = fmaxf(mx, x);
-        }
+      for (int c = 0; c < kAK / 32; ++c) tmem_ld_32x32(tmem_s + lane_addr + c * 32, v + c * 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(s_empty));  // S is in registers: the next Q K^T may overwrite it
+      const bool diag = (j == qt);
+      float mx = -INFINITY;
+      if (diag) {
+#pragma unroll
+        for (int e = 0; e < kAK; ++e)
+          if (e <= r) mx = fmaxf(mx, __uint_as_float(v[e]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < kAK; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float alpha = exp2f(m - m_new);  // 0 on the first tile (m = -inf)
-      if (j > 0) {  // fold in P V of the previous tile (it is relative to the old maximum)
+      const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+      const bool need = (m_new - m_ref) > 8.f;  // true on the first tile (m_ref = -inf)
+      if (j > 0) {  // P V(j-1) must have finished reading the P tile (and O) before either is touched
         if (!mbar_wait(smem_u32(pv_full), (j - 1) & 1, ab, 18)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < kAHD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_pv + lane_addr + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o_acc[c * 32 + e] += __uint_as_float(v[e]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(pv_empty));
       }
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_tgt = need ? m_new : m_ref;
+        if (j > 0) {
+          const float alpha = ex2_approx(m_ref - m_tgt);
 #pragma unroll
-      for (int i = 0; i < kAHD; ++i) o_acc[i] *= alpha;
-      l *= alpha;
-      // pass 2: probabilities -> bf16 operand tile (row r, 16-byte chunk c16 stored at c16 ^ (r & 7) inside its atom)
-#pragma unroll 1
-      for (int c = 0; c < kAK / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        float pr[32];
+          for (int c = 0; c < kAHD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_pv + lane_addr + c * 32, o);
+            tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float x = __uint_as_float(v[e]) * p.scale_log2 - m_new;
-          const float pe = (!diag || (c * 32 + e) <= r) ? exp2f(x) : 0.f;
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_32x32(tmem_pv + lane_addr + c * 32, o);
+          }
+          tmem_st_wait();
+          l *= alpha;
+        }
+        m_ref = m_tgt;
+      }
+      // probabilities -> bf16 operand tile (row r, 16-byte chunk c16 stored at c16 ^ (r & 7) inside its 64-column atom)
+      const float neg_m = -m_ref;
+#pragma unroll
+      for (int c16 = 0; c16 < kAK / 8; ++c16) {
+        float pr[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int col = c16 * 8 + e;
+          float pe = ex2_approx(fmaf(__uint_as_float(v[col]), p.scale_log2, neg_m));
+          if (diag && col > r) pe = 0.f;
           pr[e] = pe;
           l += pe;
         }
-        uint8_t* atom = sP + (c >> 1) * (kAQ * 128) + r * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int c16 = (c & 1) * 4 + q4;
-          *reinterpret_cast<bf16x8*>(atom + ((c16 ^ (r & 7)) << 4)) = pack8(pr + q4 * 8);
-        }
+        uint8_t* atom = sP + (c16 >> 3) * (kAQ * 128) + r * 128;
+        *reinterpret_cast<bf16x8*>(atom + (((c16 & 7) ^ (r & 7)) << 4)) = pack8(pr);
       }
       tc_fence_before();
       fence_proxy_async();  // make the P tile visible to the tensor core's shared-memory reads
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(s_empty));
-        mbar_arrive(smem_u32(p_full));
-      }
-      m = m_new;
+      if (lane == 0) mbar_arrive(smem_u32(p_full));
     }
     if (ok && mbar_wait(smem_u32(pv_full), (n_tiles - 1) & 1, ab, 19)) {
       tc_fence_after();
@@ -229,16 +232,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       __nv_bfloat16* orow = p.o + (((size_t)b * p.S + row) * p.H + h) * kAHD;
 #pragma unroll
       for (int c = 0; c < kAHD / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_pv + lane_addr + c * 32, v);
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_pv + lane_addr + c * 32, o);
         tmem_ld_wait();
         float f[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) f[e] = (o_acc[c * 32 + e] + __uint_as_float(v[e])) * inv;
+        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(o[e]) * inv;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(orow + c * 32)[q4] = pack8(f + q4 * 8);
       }
-      p.lse[((size_t)b * p.H + h) * p.S + row] = (m + log2f(l)) * 0.6931471805599453f;
+      p.lse[((size_t)b * p.H + h) * p.S + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
     }
   }
 
