@@ -126,3 +126,62 @@ def test_hf_export_matches_own_tokenizer(tmp_path):
     hf = build_tokenizer(bpe.vocab, bpe.merges_tuples, ["<|endoftext|>"])
     for text in ["The quick brown fox", "It's 12345 o'clock", "def f(x):\n    return x + 1"]:
         assert [own.decode([i]) for i in own.encode(text)] == [hf.decode([i]) for i in hf.encode(text).ids]
+
+
+def _word_tokenizer():
+    from tokenizers import Tokenizer as HFTok, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    words = ["<|endoftext|>", "<unk>", "<|bos|>", "a", "b", "c", "d"]
+    tok = HFTok(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    return PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="<|endoftext|>",
+                                   additional_special_tokens=["<|bos|>"])
+
+
+def test_dataset_tokeniser_parquet_jsonl_txt(tmp_path, monkeypatch):
+    import gzip
+    import json
+
+    import numpy as np
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from sample_efficient_gpt_b200.tokenizer import tokenize_with_fast_tokenizer as T
+
+    monkeypatch.setenv("STAGE", "1")
+    proc = T.TokenizerProcessor(_word_tokenizer())
+    src = tmp_path / "finemath_x"
+    src.mkdir()
+    rows = [{"text": "a b", "score": 4.0}, {"text": "c", "score": 1.0}, {"text": "d d d", "score": 3.8}]
+    pq.write_table(pa.Table.from_pylist(rows), src / "part.0.parquet")
+    out = tmp_path / "tok"
+    n = proc.encode_hf(src, out)
+    tokens, offsets = np.load(out / "part0.npy"), np.load(out / "offsets_part.0.npy")
+    assert tokens.dtype == np.uint16 and offsets.dtype == np.int64 and n == 7
+    assert tokens.tolist() == [3, 4, 0, 6, 6, 6, 0] and offsets.tolist() == [0, 3, 7]  # score 1.0 <= 3.7 dropped, EOT appended
+    assert proc.encode_hf(src, out, limit=100) == 7  # finished shard is skipped but counted
+    assert T.threshold("finemath", 2) == 4.1 and T.threshold("pleias_synth", 3) == 2.1
+
+    js = tmp_path / "plain"
+    js.mkdir()
+    with gzip.open(js / "x.jsonl.gz", "wt") as f:
+        for t in ("a", "b c"):
+            f.write(json.dumps({"text": t}) + "\n")
+    proc.encode_hf(js, out)
+    assert np.load(out / "0.npy").tolist() == [3, 0, 4, 5, 0] and np.load(out / "offsets_0.npy").tolist() == [0, 2, 5]
+
+    monkeypatch.setenv("STAGE", "3")
+    assert proc.preprocess_text("q\n<think>r") == "<|bos|><|user_start|>q<|user_end|><|assistant_start|>\n<think>r<|assistant_end|><|endoftext|>"
+    assert proc.preprocess_text("x") == "<|bos|>x<|endoftext|>"
+    assert not proc.keep_row({"text": "short"}, "anything") and proc.keep_row({"text": "x" * 4001}, "anything")
+    monkeypatch.setenv("STAGE", "1")
+
+    txt = tmp_path / "txt"
+    txt.mkdir()
+    (txt / "c_train.txt").write_text("a b<|endoftext|>c d<|endoftext|>")
+    (txt / "c_val.txt").write_text("a a a a<|endoftext|>")
+    proc.encode_hf_txt(txt, out)
+    assert np.load(out / "c_train.npy").tolist() == [3, 4, 0, 5, 6, 0]
+    ratios = proc.compression_ratios(txt)
+    assert ratios["c_val.txt"] == pytest.approx(7 / 5)
