@@ -376,6 +376,7 @@ void muon_tail(const Tensor& v, const Tensor& slot_of, Tensor second, std::vecto
 
 void register_gemm(pybind11::module_& m);  // gemm_bindings.cpp
 void register_comm(pybind11::module_& m);  // comm_bindings.cpp
+void register_moe(pybind11::module_& m);   // moe_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of sample_efficient_gpt_b200";
@@ -395,4 +396,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("muon_tail", &muon_tail);
   register_gemm(m);
   register_comm(m);
+  register_moe(m);
 }

@@ -3,7 +3,7 @@
 // its own device; ranks meet at flag barriers that live in symmetric (peer-mapped) memory.
 //
 // all-reduce of a bucket (fp32 gradients G[n] in place, bf16 on the wire, W = this rank's wire buffer):
-//   A  pack    : W_me[s, b] = bf16(G[s, b])                       for every slice s, sub-slice b = blockIdx.x
+//   A  pack    : W_me[s, b] = bf16(G[s, b])                       for every slice s != me, sub-slice b = blockIdx.x
 //      barrier : block b of every rank has packed
 //   B  reduce  : slice me, sub-slice b: sum over ranks p (fixed order) of W_p[me, b] in fp32 -> G (fp32, final)
 //                and the bf16 result is stored into W_p[me, b] of every peer p           (reduce-scatter + push)
@@ -87,13 +87,19 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
   const int64_t v0 = vecs * blockIdx.x / nb, v1 = vecs * (blockIdx.x + 1) / nb;
   __nv_bfloat16* w_me = reinterpret_cast<__nv_bfloat16*>(pe.buf[rank]) + wire_off;
 
-  // A: pack
+  // A: pack the slices owned by other ranks (this rank's own slice is read as fp32 in phase B)
+  constexpr int kUnroll = 4;
   for (int s = 0; s < world; ++s) {
+    if (s == rank && mc_base == nullptr) continue;  // the multicast reduction reads every rank's copy from the wire buffers
     const int64_t base = (int64_t)s * slice;
-    for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-      float f[8];
-      load8<float>(grads + base + v * 8, f);
-      store8<__nv_bfloat16>(w_me + base + v * 8, f);
+    for (int64_t v = v0 + threadIdx.x; v < v1; v += (int64_t)blockDim.x * kUnroll) {
+      float f[kUnroll][8];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (v + (int64_t)u * blockDim.x < v1) load8<float>(grads + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (v + (int64_t)u * blockDim.x < v1) store8<__nv_bfloat16>(w_me + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
     }
   }
   if (!block_barrier(pe, rank, world, seq, status)) return;
@@ -103,28 +109,38 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
     const int64_t base = (int64_t)rank * slice;
     if (mc_base != nullptr) {
       __nv_bfloat16* mc = reinterpret_cast<__nv_bfloat16*>(mc_base) + wire_off;
-      for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-        uint32_t r[4];
-        multimem_ld_reduce_bf16x8(mc + base + v * 8, r);
-        multimem_st_bf16x8(mc + base + v * 8, r);
-        float f[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(r), f);
-        store8<float>(grads + base + v * 8, f);
+      for (int64_t v = v0 + threadIdx.x; v < v1; v += (int64_t)blockDim.x * kUnroll) {
+        uint32_t r[kUnroll][4];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          if (v + (int64_t)u * blockDim.x < v1) multimem_ld_reduce_bf16x8(mc + base + (v + (int64_t)u * blockDim.x) * 8, r[u]);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          if (v + (int64_t)u * blockDim.x < v1) {
+            const int64_t vv = v + (int64_t)u * blockDim.x;
+            multimem_st_bf16x8(mc + base + vv * 8, r[u]);
+            float f[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(r[u]), f);
+            store8<float>(grads + base + vv * 8, f);
+          }
       }
     } else {
       for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+        bf16x8 in[kMaxRanks];
+        float own[8];
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p)
+          if (p < world && p != rank)
+            in[p] = *reinterpret_cast<const bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(pe.buf[p]) + wire_off + base + v * 8);
+        load8<float>(grads + base + v * 8, own);
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        bf16x8 in[kMaxRanks];
 #pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
-          if (p < world) in[p] = *reinterpret_cast<const bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(pe.buf[p]) + wire_off + base + v * 8);
-#pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
+        for (int p = 0; p < kMaxRanks; ++p)  // fixed order of summation on every rank; each term is bf16-rounded
           if (p < world) {
             float f[8];
-            unpack8(in[p], f);
+            unpack8(p == rank ? pack8(own) : in[p], f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] += f[j];
           }
@@ -145,10 +161,14 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
   for (int s = 0; s < world; ++s) {
     if (s == rank) continue;
     const int64_t base = (int64_t)s * slice;
-    for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-      float f[8];
-      load8<__nv_bfloat16>(w_me + base + v * 8, f);
-      store8<float>(grads + base + v * 8, f);
+    for (int64_t v = v0 + threadIdx.x; v < v1; v += (int64_t)blockDim.x * kUnroll) {
+      float f[kUnroll][8];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (v + (int64_t)u * blockDim.x < v1) load8<__nv_bfloat16>(w_me + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (v + (int64_t)u * blockDim.x < v1) store8<float>(grads + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
     }
   }
 }

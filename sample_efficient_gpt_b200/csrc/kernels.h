@@ -70,7 +70,7 @@ void muon_tail(const void* v, const int32_t* slot_of, float* second, float* sq, 
 
 // ---- comm.cu (NVLink peer-memory collectives; one process per GPU)
 constexpr int kMaxRanks = 8;
-constexpr int kCommMaxBlocks = 64;  // flag words per rank = kCommMaxBlocks * kMaxRanks
+constexpr int kCommMaxBlocks = 128;  // flag words per rank = kCommMaxBlocks * kMaxRanks
 // grads: this rank's fp32 bucket (n elements, n % (world*8) == 0), reduced in place across ranks with bf16 on the wire.
 // wire_bufs[p] / flags[p]: peer-mapped wire buffer and flag array of rank p; wire_off: element offset of the bucket in the
 // wire buffers; mc_base: NVLS multicast address of the wire buffer or null; seq: first of two consecutive barrier numbers.
@@ -79,6 +79,31 @@ void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const
 // bufs[p] + off_bytes holds `world` chunks of chunk_bytes (multiple of 16); chunk `rank` is valid on entry, all on exit.
 void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,
                     uint32_t seq, int blocks, int* status, cudaStream_t st);
+
+// ---- moe.cu (router, slot assignment, expert-parallel push / pull over peer memory)
+constexpr int kMoeMaxExperts = 32;
+constexpr int kMoeMaxTopK = 4;
+constexpr int kMoeTokensPerBlock = 32;  // granularity of the (token, choice)-ordered slot scan
+constexpr int kMoeTailBlocks = 4;       // zero-filling CTAs per expert in the push kernel
+// x [T, d] bf16, wr [E, d] fp32 -> probs [T, E] fp32, idx [T, k] int32, w [T, k] fp32 (renormalised top-k weights);
+// block_counts / block_off: int32 scratch [ceil(T / kMoeTokensPerBlock), E]; totals [E] assignments per expert.
+// Returns non-zero when E, k or d is out of range (E <= 32, k <= min(4, E), d % 8 == 0).
+int moe_route(const void* x, const float* wr, int T, int d, int E, int k, float* probs, int* idx, float* w, int* block_counts,
+              int* block_off, int* totals, cudaStream_t st);
+// slot [T, k]: position of the assignment inside its expert (token-major order), -1 when >= cap.
+void moe_slots(const int* idx, const int* block_off, int T, int E, int k, int cap, int* slot, cudaStream_t st);
+// dst[r]: rank r's buffer [E / world][world][cap][d] bf16 (peer-mapped).  Row (e_local, rank, slot) <- w * x[t] for every kept
+// assignment (w == nullptr: unscaled); rows [min(totals[e], cap), cap) of this rank's regions are zero-filled.
+void moe_push(const void* x, const int* idx, const int* slot, const float* w, const int* totals, void* const* dst, int T, int d,
+              int E, int k, int cap, int world, int rank, cudaStream_t st);
+// out[t] = sum over kept assignments of w * src[owner](e_local, rank, slot) (w == nullptr: 1); with dots != nullptr also
+// dots[t, c] = <g[t], src2[owner] row> (0 for dropped assignments).  out is bf16 or fp32.
+void moe_pull(void* const* src, void* const* src2, const int* idx, const int* slot, const float* w, const void* g, void* out,
+              bool out_f32, float* dots, int T, int d, int E, int k, int cap, int world, int rank, cudaStream_t st);
+// dlogits [T, E] from the gradient of the renormalised weights dw [T, k] and a per-expert additive term aux_vec [E] on
+// d(probs) (load-balance loss), through the softmax.
+void moe_route_bwd(const float* probs, const int* idx, const float* dw, const float* aux_vec, int T, int E, int k, float* dlogits,
+                   cudaStream_t st);
 
 // ---- gemm.cu (tcgen05 / TMEM / TMA)
 // D[b] = alpha * A[b] * op(B[b]) + beta * C[b], bf16 inputs, fp32 accumulation, D and C bf16 or fp32.

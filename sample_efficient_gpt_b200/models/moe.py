@@ -31,14 +31,50 @@ from sample_efficient_gpt_b200.models.core import Linear, mup_trunc_normal_
 
 
 class Experts(nn.Module):
-    def __init__(self, n_local: int, d_model: int, d_ff: int, first_global_id: int = 0, device=None, dtype=None):
+    """The experts this rank holds: ``n_local`` consecutive ones out of ``n_total``, starting at ``first_global_id``.
+
+    Initial values are drawn for all ``n_total`` experts in order and only the local ones are kept, so that a model built
+    from the same seed has the same experts however they are split over ranks.  State-dict keys carry the *global*
+    expert id (``up.{g}`` / ``down.{g}``): a file written by one rank names the experts it holds, and loading picks the
+    local ones out of whatever a file offers.
+    """
+
+    def __init__(self, n_local: int, d_model: int, d_ff: int, first_global_id: int = 0, n_total: int | None = None, device=None,
+                 dtype=None):
         super().__init__()
         self.first_global_id = first_global_id
+        self.n_total = n_total if n_total is not None else first_global_id + n_local
         self.up = nn.ParameterList()
         self.down = nn.ParameterList()
-        for _ in range(n_local):
-            self.up.append(nn.Parameter(mup_trunc_normal_(torch.empty(2 * d_ff, d_model, device=device, dtype=dtype), d_model)))
-            self.down.append(nn.Parameter(mup_trunc_normal_(torch.empty(d_model, d_ff, device=device, dtype=dtype), d_ff)))
+        for g in range(self.n_total):
+            up = mup_trunc_normal_(torch.empty(2 * d_ff, d_model, dtype=dtype), d_model)
+            down = mup_trunc_normal_(torch.empty(d_model, d_ff, dtype=dtype), d_ff)
+            if first_global_id <= g < first_global_id + n_local:
+                self.up.append(nn.Parameter(up.to(device) if device is not None else up))
+                self.down.append(nn.Parameter(down.to(device) if device is not None else down))
+        self._register_state_dict_hook(self._globalise_keys)
+        self._register_load_state_dict_pre_hook(self._localise_keys)
+
+    @staticmethod
+    def _globalise_keys(module, state_dict, prefix, local_metadata):
+        if module.first_global_id == 0:
+            return state_dict
+        for kind in ("up", "down"):
+            moved = {e: state_dict.pop(f"{prefix}{kind}.{e}") for e in range(len(getattr(module, kind)))}
+            for e, t in moved.items():
+                state_dict[f"{prefix}{kind}.{module.first_global_id + e}"] = t
+        return state_dict
+
+    def _localise_keys(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        n_local = len(self.up)
+        for kind in ("up", "down"):
+            offered = {int(k[len(prefix) + len(kind) + 1:]): k for k in list(state_dict) if k.startswith(f"{prefix}{kind}.")}
+            picked = {g - self.first_global_id: state_dict.pop(k) for g, k in offered.items()
+                      if self.first_global_id <= g < self.first_global_id + n_local}
+            for k in offered.values():
+                state_dict.pop(k, None)  # experts of other ranks
+            for e, t in picked.items():
+                state_dict[f"{prefix}{kind}.{e}"] = t
 
     def forward(self, x: Tensor) -> Tensor:
         """x [E_local, C, d] -> [E_local, C, d]."""
@@ -80,7 +116,7 @@ class MoEFeedForward(nn.Module):
             assert n_experts % self.ep_world == 0, "experts must divide evenly across the expert-parallel group"
         self.n_local = n_experts // self.ep_world
         self.router = Linear(d_model, n_experts, device=device, dtype=dtype)
-        self.experts = Experts(self.n_local, d_model, self.d_ff, self.ep_rank * self.n_local, device=device, dtype=dtype)
+        self.experts = Experts(self.n_local, d_model, self.d_ff, self.ep_rank * self.n_local, n_experts, device=device, dtype=dtype)
         self.last_aux_loss: Tensor | None = None
         self.last_drop_fraction: Tensor | None = None
 

@@ -210,7 +210,7 @@ class Transformer(nn.Module):
         return out_seq, (torch.cat(eos_trace, dim=-1) if eos_trace else None)
 
 
-def build_model(mcfg, device="cpu", dtype=torch.float32) -> Transformer:
+def build_model(mcfg, device="cpu", dtype=torch.float32, ep_group=None) -> Transformer:
     """Instantiate from a ``ModelConfig`` (fp32 master weights, as trainer.py:99-117 of the reference)."""
     moe = None
     if getattr(mcfg, "n_experts", 0):
@@ -220,6 +220,7 @@ def build_model(mcfg, device="cpu", dtype=torch.float32) -> Transformer:
             d_ff=mcfg.moe_d_ff or mcfg.d_ff,
             capacity_factor=mcfg.moe_capacity_factor,
             aux_loss_weight=mcfg.moe_aux_loss_weight,
+            ep_group=ep_group,
         )
     return Transformer(
         mcfg.n_layers,

@@ -47,7 +47,7 @@ def _time_ms(fn, reps: int, warmup: int, flush) -> float:
     return float(t)
 
 
-def sweep(sizes_mb: list[int], reps: int, warmup: int, backends: list[str]) -> list[dict]:
+def sweep(sizes_mb: list[int], reps: int, warmup: int, backends: list[str], blocks: int = 128) -> list[dict]:
     from sample_efficient_gpt_b200.parallel.symm import SymmComm
 
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -64,7 +64,7 @@ def sweep(sizes_mb: list[int], reps: int, warmup: int, backends: list[str]) -> l
     for name in backends:
         if name in ("p2p", "multimem"):
             try:
-                c = SymmComm.create(dev, use_multimem=(name == "multimem"))
+                c = SymmComm.create(dev, use_multimem=(name == "multimem"), blocks=blocks)
                 c.register_buckets(flat, ranges)
                 comms[name] = c
             except RuntimeError as e:
@@ -74,7 +74,7 @@ def sweep(sizes_mb: list[int], reps: int, warmup: int, backends: list[str]) -> l
     for bi, (mb, (s, e)) in enumerate(zip(sizes_mb, ranges)):
         view = flat[s:e]
         nbytes = (e - s) * 4
-        row = {"mb": mb, "world": world}
+        row = {"mb": mb, "world": world, "blocks": blocks}
 
         def nccl_bf16():
             wire = view.to(torch.bfloat16)
@@ -143,6 +143,7 @@ def main(argv=None):
     p.add_argument("--reps", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--backends", default="nccl_bf16,nccl_fp32,p2p,multimem")
+    p.add_argument("--blocks", type=int, default=128, help="CTAs of the NVLink kernels (training uses 32 to leave SMs to the backward pass)")
     p.add_argument("--nccl-table", action="store_true")
     p.add_argument("--out", default=None)
     a = p.parse_args(argv)
@@ -156,7 +157,7 @@ def main(argv=None):
             while mb <= a.max_mb:
                 sizes.append(mb)
                 mb *= 2
-            rows = sweep(sizes, a.reps, a.warmup, a.backends.split(","))
+            rows = sweep(sizes, a.reps, a.warmup, a.backends.split(","), a.blocks)
         if a.out and dist.get_rank() == 0:
             os.makedirs(os.path.dirname(a.out) or ".", exist_ok=True)
             with open(a.out, "w") as f:

@@ -44,15 +44,18 @@ def assign_buckets(named_params: list[tuple[str, Tensor]], bucket_bytes: int) ->
 
 
 class DDP(nn.Module):
-    def __init__(self, module: nn.Module, bucket_size_mb: float = 30.1, comm=None, process_group=None):
+    def __init__(self, module: nn.Module, bucket_size_mb: float = 30.1, comm=None, process_group=None, is_local=None):
+        """``is_local(name)``: parameters that differ per rank by design (expert-parallel experts) - neither broadcast
+        nor reduced; their ``.grad`` is left to their owner."""
         super().__init__()
         assert dist.is_initialized(), "DDP needs an initialised process group"
         self.module = module
         self.group = process_group
         self.comm = comm  # SymmComm for the NVLink kernels, None for torch.distributed collectives
         self.world = dist.get_world_size(process_group)
-        named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
-        self._broadcast_parameters([p for _, p in module.named_parameters()])
+        is_local = is_local or (lambda name: False)
+        named = [(n, p) for n, p in module.named_parameters() if p.requires_grad and not is_local(n)]
+        self._broadcast_parameters([p for n, p in module.named_parameters() if not is_local(n)])
         by_name = dict(named)
         self.bucket_names = assign_buckets(named, int(bucket_size_mb * 1024 * 1024))
         # flat fp32 gradient storage, bucket after bucket

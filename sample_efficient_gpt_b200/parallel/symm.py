@@ -128,6 +128,11 @@ class SymmComm:
         hdl, off = self._handle_of(t)
         return [int(p) + off for r, p in enumerate(hdl.buffer_ptrs) if r != self.rank]
 
+    def all_addresses(self, t: Tensor) -> list[int]:
+        """Addresses of every rank's copy of ``t`` (a view of a ``symm_zeros`` buffer), in rank order, this rank's included."""
+        hdl, off = self._handle_of(t)
+        return [int(p) + off for p in hdl.buffer_ptrs]
+
     def barrier(self):
         """Device-side barrier across ranks on the current stream (a zero-byte all-gather)."""
         ops.ext().comm_allgather(self.flag_ptrs, self.flag_ptrs, 0, 0, self.rank, self.seq, 1, self.status)

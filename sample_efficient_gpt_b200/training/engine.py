@@ -37,17 +37,19 @@ class StepOutput:
     loss_bpb: Tensor | None
     kurtosis: Tensor  # [n_layers]
     loss_tok: Tensor | None = None
+    aux_loss: Tensor | None = None  # sum of the load-balance terms of the mixture-of-experts blocks
 
 
 def engine_supports(model: Transformer) -> bool:
     blk = model.blocks[0]
-    return (not blk.is_moe) and blk.attn.gating in (False, "per-head")
+    uniform = all(b.is_moe == blk.is_moe for b in model.blocks)
+    return uniform and blk.attn.gating in (False, "per-head")
 
 
 class FusedEngine:
-    def __init__(self, model: Transformer, act_dtype: torch.dtype = torch.bfloat16):
+    def __init__(self, model: Transformer, act_dtype: torch.dtype = torch.bfloat16, moe_exchange=None):
         if not engine_supports(model):
-            raise ValueError("FusedEngine: dense FFN and gating in {False, 'per-head'} only")
+            raise ValueError("FusedEngine: gating in {False, 'per-head'} and either all-dense or all-MoE blocks only")
         self.model = model
         self.lp = act_dtype
         self.grad_ready: Callable[[list[torch.nn.Parameter]], None] | None = None
@@ -59,6 +61,12 @@ class FusedEngine:
         at = model.blocks[0].attn
         self.H, self.Hkv, self.hd = at.n_heads, at.n_kv_heads, at.head_dim
         self._ones = torch.ones(1, dtype=torch.float32, device=model.embedding.weight.device)
+        self._loss_coef = 1.0
+        self.moe = None
+        if model.blocks[0].is_moe:
+            from sample_efficient_gpt_b200.training.moe_engine import MoEEngine
+
+            self.moe = MoEEngine(self, moe_exchange)
 
     # ------------------------------------------------------------------ helpers
     def refresh_shadows(self):
@@ -67,6 +75,8 @@ class FusedEngine:
             return
         ps = list(self.shadows.keys())
         torch._foreach_copy_([self.shadows[p] for p in ps], [p.detach() for p in ps])
+        if self.moe is not None:
+            self.moe.refresh()
 
     def register_with(self, optimizers):
         """Let the optimizers write the bf16 shadows in the same kernel that updates the masters."""
@@ -114,9 +124,13 @@ class FusedEngine:
         g = ops.gate_fwd(o.view(T, H, hd), z) if at.gating else o.view(T, H * hd)
         a = ops.matmul_nt(g, self._w(at.out.linear.weight))
         y, n2, rstd2, _ = ops.add_rmsnorm_fwd(x, a, blk.ln2.gain, scale, blk.ln2.eps, self.lp, False)
-        u = ops.matmul_nt(n2, self._w(blk.ffn.up.linear.weight))
-        f = ops.swiglu_fwd(u)
-        m = ops.matmul_nt(f, self._w(blk.ffn.down.linear.weight))
+        if blk.is_moe:
+            m, u = self.moe.forward(i, n2, train, record=want_kurt or not train)  # u: what the expert backward needs
+            f = None
+        else:
+            u = ops.matmul_nt(n2, self._w(blk.ffn.up.linear.weight))
+            f = ops.swiglu_fwd(u)
+            m = ops.matmul_nt(f, self._w(blk.ffn.down.linear.weight))
         saved = (x, n1, rstd1, qkv, z, q, k, v, o, lse, g, y, n2, rstd2, u, f)
         return y, m, v, kurt, saved
 
@@ -127,14 +141,17 @@ class FusedEngine:
         T = B * S
         x, n1, rstd1, qkv, z, q, k, v, o, lse, g, y, n2, rstd2, u, f = saved
         scale = float(blk.ln1.position_scale)
-        w_down, w_up = blk.ffn.down.linear.weight, blk.ffn.up.linear.weight
         w_out, w_qkv = at.out.linear.weight, at.qkv.linear.weight
 
-        df = ops.matmul_nn(dres_lp, self._w(w_down))
-        self._wgrad(w_down, dres_lp, f)
-        du = ops.swiglu_bwd(df, u)
-        dn2 = ops.matmul_nn(du, self._w(w_up))
-        self._wgrad(w_up, du, n2)
+        if blk.is_moe:
+            dn2 = self.moe.backward(i, dres_lp, n2, u, self._loss_coef, self._first_accum)
+        else:
+            w_down, w_up = blk.ffn.down.linear.weight, blk.ffn.up.linear.weight
+            df = ops.matmul_nn(dres_lp, self._w(w_down))
+            self._wgrad(w_down, dres_lp, f)
+            du = ops.swiglu_bwd(df, u)
+            dn2 = ops.matmul_nn(du, self._w(w_up))
+            self._wgrad(w_up, du, n2)
         dy, dy_lp, dgain2 = ops.add_rmsnorm_bwd(dn2, dres, y, blk.ln2.gain, rstd2, scale, self.lp)
         self._acc(blk.ln2.gain, dgain2)
 
@@ -185,6 +202,9 @@ class FusedEngine:
         model = self.model
         self.ensure_grads()
         self._first_accum = first_micro_step
+        self._loss_coef = loss_coef
+        if self.moe is not None:
+            self.moe.begin_step()
         B, S = tokens.shape
         T = B * S
         L = model.n_layers
@@ -236,7 +256,8 @@ class FusedEngine:
         if byte_len is not None:
             bl = byte_len[targets.reshape(-1).clamp_min(0).long()]
             bpb = (loss_tok * bl).sum() / bl.sum() * NATS_TO_BITS
-        return StepOutput(loss_tok.mean(), z_tok.mean(), bpb, torch.stack(kurts) / T, loss_tok)
+        aux = self.moe.aux_loss() if self.moe is not None else None
+        return StepOutput(loss_tok.mean(), z_tok.mean(), bpb, torch.stack(kurts) / T, loss_tok, aux)
 
     @torch.no_grad()
     def forward_loss(self, tokens: Tensor, targets: Tensor, byte_len: Tensor | None = None) -> StepOutput:
@@ -244,6 +265,8 @@ class FusedEngine:
         model = self.model
         B, S = tokens.shape
         T = B * S
+        if self.moe is not None:
+            self.moe.begin_step()
         res = model.embedding.weight.detach()[tokens.reshape(-1).long()].float()
         delta, v1, kurts = None, None, []
         for i in range(model.n_layers):

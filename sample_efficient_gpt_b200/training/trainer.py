@@ -118,7 +118,15 @@ class Trainer:
             self.wandb = M.JsonlSink(tc.metrics_jsonl)
 
         # fp32 master weights are created on the CPU and moved, so that init does not depend on the device
-        self.model = build_model(cfg.model, device="cpu", dtype=torch.float32)
+        self.ep_group = None
+        if self.is_distributed and tc.dist_mode == "ddp_ep" and getattr(cfg.model, "n_experts", 0):
+            self.ep_group = dist.group.WORLD
+            # experts are split over the ranks: every rank draws the same stream and keeps its own experts
+            with torch.random.fork_rng(devices=[]):
+                torch.manual_seed(42)
+                self.model = build_model(cfg.model, device="cpu", dtype=torch.float32, ep_group=self.ep_group)
+        else:
+            self.model = build_model(cfg.model, device="cpu", dtype=torch.float32)
         self.model.to(self.device)
         load_from = load_from or tc.load_from
         if load_from is not None:
@@ -129,7 +137,8 @@ class Trainer:
             if tc.dist_mode not in ("ddp", "ddp_ep"):
                 raise ValueError(f"Unsupported dist_mode={tc.dist_mode!r}; expected 'ddp' or 'ddp_ep'.")
             comm = self._make_comm()
-            self.ddp = DDP(self.model, bucket_size_mb=tc.bucket_size_mb, comm=comm)
+            local = (lambda n: ".experts." in n) if self.ep_group is not None else None
+            self.ddp = DDP(self.model, bucket_size_mb=tc.bucket_size_mb, comm=comm, is_local=local)
         self.total_params = M.non_embedding_params(cfg.model)
         if self.wandb is not None and self.rank_zero_only:
             self.wandb.log(
@@ -155,7 +164,7 @@ class Trainer:
         if load_components == "all":
             self._init_optimizers()
             if self.use_engine:
-                self.engine = FusedEngine(self.model, self.act_dtype)
+                self.engine = FusedEngine(self.model, self.act_dtype, moe_exchange=self._make_moe_exchange())
                 self.engine.ensure_grads()
                 self.engine.register_with(self.optimizers)
                 if self.ddp is not None:
@@ -221,6 +230,18 @@ class Trainer:
                 logger.warning(f"NVLink kernels unavailable ({type(e).__name__}: {e}); using torch.distributed collectives")
         return None
 
+    def _make_moe_exchange(self):
+        """Expert-parallel token exchange: NVLink push/pull kernels on symmetric memory when the communicator exists,
+        ``all_to_all_single`` otherwise; None (local buffers) without expert parallelism."""
+        if self.ep_group is None:
+            return None
+        from sample_efficient_gpt_b200.ops import moe as moe_ops
+
+        comm = self.ddp.comm if self.ddp is not None else None
+        if comm is not None and self.act_dtype == torch.bfloat16:
+            return moe_ops.PeerExchange(self.cfg.model.n_experts, comm)
+        return moe_ops.TorchExchange(self.cfg.model.n_experts, self.ep_group)
+
     @property
     def rank_zero_only(self) -> bool:
         return not self.is_distributed or self.rank == self.target_log_rank
@@ -239,8 +260,13 @@ class Trainer:
             self.optimizer = AdamW([p for _, p in named], **kw)
             self.optimizers = [self.optimizer]
             return
-        one_d = [p for n, p in named if p.ndim < 2 or "embedding" in n or "lm_head" in n]
-        two_d = [p for n, p in named if p.ndim >= 2 and "embedding" not in n and "lm_head" not in n]
+        adam_names = ("embedding", "lm_head", ".router.")
+        one_d = [p for n, p in named if p.ndim < 2 or any(k in n for k in adam_names)]
+        two_d = [p for n, p in named if p.ndim >= 2 and not any(k in n for k in adam_names)]
+        local_2d = []
+        if self.ep_group is not None:  # this rank's experts: never sharded, every rank steps its own
+            local_2d = [p for n, p in named if ".experts." in n]
+            two_d = [p for n, p in named if p.ndim >= 2 and not any(k in n for k in adam_names) and ".experts." not in n]
         for n, p in named:  # set as in the reference; only the Muon family reads lr_mul, whose params all get 1.0
             p.lr_mul = self.cfg.model.d_model**0.5 if "embedding" in n else (0.5 if "lm_head" in n else 1.0)
         self.optimizer1 = AdamW(one_d, **kw)
@@ -251,6 +277,9 @@ class Trainer:
         if self.ddp is not None and self.ddp.comm is not None:
             self.optimizer2.comm = self.ddp.comm
         self.optimizers = [self.optimizer1, self.optimizer2]
+        if local_2d:
+            self.optimizer3 = cls(local_2d, lr=muon_lr, momentum=oc.betas[0], weight_decay=muon_wd, shard=False)
+            self.optimizers.append(self.optimizer3)
 
     @property
     def tokens_processed(self) -> int:
@@ -354,10 +383,11 @@ class Trainer:
         if oc.use_muon:
             mlr = float(oc.lr if oc.muon_lr is None else oc.muon_lr)
             iter_lr = self._get_lr(mlr, mlr * oc.lr_min_coeff)
-            for pg in self.optimizers[1].param_groups:
-                if self.iteration < 300:
-                    pg["momentum"] = muon_momentum_warmup(self.iteration, oc.betas[0])
-                pg["lr"] = iter_lr
+            for opt in self.optimizers[1:]:  # the Muon family: shared matrices and, with expert parallelism, local experts
+                for pg in opt.param_groups:
+                    if self.iteration < 300:
+                        pg["momentum"] = muon_momentum_warmup(self.iteration, oc.betas[0])
+                    pg["lr"] = iter_lr
         return iter_lr, oc.muon_wd
 
     # ------------------------------------------------------------------ the step
@@ -388,10 +418,12 @@ class Trainer:
         coef = self._loss_coef()
         sync_ctx = self.ddp.no_sync() if (self.ddp is not None and not boundary) else nullcontext()
 
+        aux = None
         if self.engine is not None:
             with sync_ctx:
                 out = self.engine.forward_backward(inputs, targets, coef, self.id2byte_len, first_micro_step=first_micro)
             loss, z_loss, loss_bpb, kurt = out.loss, out.z_loss, out.loss_bpb, out.kurtosis
+            aux = out.aux_loss
         else:
             if first_micro:
                 self._zero_grads()
@@ -448,6 +480,8 @@ class Trainer:
         }
         if iter_wd is not None:
             log["wd"] = iter_wd
+        if aux is not None:
+            log["moe_aux_loss"] = aux.detach()
         for i, r in enumerate(update_ratios):
             log[f"opt_{i}_update_ratio"] = r
         return log

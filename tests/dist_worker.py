@@ -164,6 +164,118 @@ def train_gpu(rank, world):
         assert torch.allclose(a, b, atol=3e-2, rtol=0.1), (a - b).abs().max()
 
 
+def moe_ep_cpu(rank, world):
+    """Expert parallelism through the engine on gloo ranks: each rank holds half of the experts and half of the batch;
+    gradients must equal those of one process holding everything (no drops, no load-balance term: both depend on
+    how the batch is split)."""
+    moe = dict(n_experts=4, top_k=2, d_ff=64, capacity_factor=4.0, aux_loss_weight=0.0)
+    kw = dict(attn_qknorm=True, attn_val_residual=True, attn_gating="per-head", layernorm_scaling=True, n_kv_heads=2, weight_tying=True)
+    torch.manual_seed(11)
+    full = Transformer(2, 256, 64, 4, 128, moe=dict(moe), **kw)
+    torch.manual_seed(11)
+    part = Transformer(2, 256, 64, 4, 128, moe=dict(moe, ep_group=dist.group.WORLD), **kw)
+    assert len(part.blocks[0].ffn.experts.up) == 2
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 256, (4, 12), generator=g)
+    tg = torch.randint(0, 256, (4, 12), generator=g)
+    logits, _ = full(ids)
+    loss, _, _ = efficient_cross_entropy(logits, tg)
+    loss.backward()
+    from sample_efficient_gpt_b200.ops.moe import TorchExchange
+
+    eng = FusedEngine(part, torch.float32, moe_exchange=TorchExchange(4, dist.group.WORLD))
+    sl = slice(rank * 2, rank * 2 + 2)
+    out = eng.forward_backward(ids[sl], tg[sl], 0.5)
+    want = dict(full.named_parameters())
+    for n, p in part.named_parameters():
+        if ".experts." in n:
+            kind, e = n.rsplit(".", 2)[-2:]
+            ref_p = want[n.rsplit(".", 1)[0] + f".{int(e) + rank * 2}"]
+            assert torch.equal(p, ref_p), f"expert init differs: {n}"
+            got = p.grad
+        else:
+            ref_p = want[n]
+            got = p.grad.clone()
+            dist.all_reduce(got)
+        assert torch.allclose(got, ref_p.grad, rtol=2e-3, atol=1e-6 + 1e-4 * float(ref_p.grad.abs().max())), n
+    # a step with drops and the load-balance term: runs, stays finite, expert state dict names global ids
+    moe2 = dict(n_experts=4, top_k=2, d_ff=64, capacity_factor=0.7, aux_loss_weight=0.05, ep_group=dist.group.WORLD)
+    torch.manual_seed(3)
+    m2 = Transformer(2, 256, 64, 4, 128, moe=moe2, **kw)
+    e2 = FusedEngine(m2, torch.float32, moe_exchange=TorchExchange(4, dist.group.WORLD))
+    o2 = e2.forward_backward(ids[sl], tg[sl], 0.5)
+    assert torch.isfinite(o2.loss) and float(o2.aux_loss) > 0
+    assert all(torch.isfinite(p.grad).all() for p in m2.parameters())
+    keys = [k for k in m2.state_dict() if ".experts.up." in k and k.startswith("blocks.0.")]
+    assert sorted(int(k.rsplit(".", 1)[1]) for k in keys) == [rank * 2, rank * 2 + 1]
+
+
+def moe_gpu(rank, world):
+    """Expert-parallel exchange over peer memory against all_to_all_single, then a few optimizer steps of an MoE model with
+    dist_mode=ddp_ep on both communication backends."""
+    from sample_efficient_gpt_b200.ops import moe as M
+    from sample_efficient_gpt_b200.parallel.symm import SymmComm
+    from sample_efficient_gpt_b200.training.trainer import Trainer
+    from sample_efficient_gpt_b200.utils.config_tools import apply_overrides, load_cfg
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    comm = SymmComm.create(dev)
+    E, k, T, d = 4 * world, 2, 1500, 256
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(T, d, generator=g).to(dev).bfloat16()
+    wr = (torch.randn(E, d, generator=torch.Generator().manual_seed(7)) * 0.2).to(dev)
+    cap = M.capacity(T, k, E, 0.9)
+    probs, idx, w, slot, totals = M.route(x, wr, k, cap)
+    peer, ref = M.PeerExchange(E, comm), M.TorchExchange(E, dist.group.WORLD)
+    for scaled in (None, w):
+        peer.begin_step()
+        got = peer.dispatch("t", x, idx, slot, totals, scaled, cap)
+        want = ref.dispatch("t", x, idx, slot, totals, scaled, cap)
+        torch.cuda.synchronize()
+        assert torch.allclose(got.float(), want.float(), atol=1e-2, rtol=1e-2), "dispatch mismatch"
+        yb = peer.output_buffer("y", tuple(want.shape), torch.bfloat16, dev)
+        y2 = peer.output_buffer("y2", tuple(want.shape), torch.bfloat16, dev)
+        yb.copy_(torch.randn(want.shape, generator=g).to(dev))
+        y2.copy_(torch.randn(want.shape, generator=g).to(dev))
+        gv = torch.randn(T, d, generator=g).to(dev).bfloat16()
+        out, dots = peer.collect(yb, idx, slot, scaled, cap, torch.float32, dot_buf=y2, g=gv)
+        rout, rdots = ref.collect(yb.clone(), idx, slot, scaled, cap, torch.float32, dot_buf=y2.clone(), g=gv)
+        torch.cuda.synchronize()
+        assert torch.allclose(out, rout, atol=1e-4, rtol=1e-4) and torch.allclose(dots, rdots, atol=2e-3, rtol=1e-3), "collect mismatch"
+    comm.check()
+
+    results = {}
+    for backend in ("nccl", "p2p"):
+        cfg = load_cfg("tiny_cpu.yaml")
+        cfg = apply_overrides(cfg, {"trainer.device": f"cuda:{local}", "trainer.dtype": "bfloat16", "trainer.comm_backend": backend,
+                                    "trainer.dist_mode": "ddp_ep", "model.vocab_size": 4096, "data.batch_size": 4 * world,
+                                    "model.n_experts": 2 * world, "model.moe_top_k": 2, "model.moe_d_ff": 128,
+                                    "model.moe_capacity_factor": 1.25, "model.moe_aux_loss_weight": 0.01,
+                                    "optim.shard_muon": True, "trainer.save_dir": "/tmp/segpt_moe", "trainer.bucket_size_mb": 1.0})
+        tr = Trainer(cfg)
+        assert tr.engine is not None and tr.engine.moe is not None
+        assert isinstance(tr.engine.moe.ex, M.PeerExchange if backend == "p2p" else M.TorchExchange)
+        gg = torch.Generator().manual_seed(5 + rank)
+        for _ in range(3):
+            wds = torch.randint(0, 4096, (4, 257), generator=gg).cuda()
+            log = tr.train_step(wds[:, :-1], wds[:, 1:])
+            tr.iteration += 1
+        torch.cuda.synchronize()
+        assert torch.isfinite(log["train_loss"]) and float(log["moe_aux_loss"]) > 0
+        if tr.ddp.comm is not None:
+            tr.ddp.comm.check()
+        results[backend] = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+        shared = torch.cat([p.flatten() for n, p in results[backend].items() if ".experts." not in n])
+        other = [torch.empty_like(shared) for _ in range(world)]
+        dist.all_gather(other, shared)
+        for o in other:
+            assert torch.equal(o, shared), f"{backend}: replicated parameters diverged"
+    for n in results["nccl"]:
+        a, b = results["nccl"][n], results["p2p"][n]
+        assert torch.allclose(a, b, atol=3e-2, rtol=0.1), (n, float((a - b).abs().max()))
+
+
 def main():
     mode = sys.argv[1]
     cuda = mode.endswith("_gpu")
@@ -172,7 +284,7 @@ def main():
     dist.init_process_group("nccl" if cuda else "gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     try:
-        {"ddp_cpu": ddp_cpu, "comm_gpu": comm_gpu, "train_gpu": train_gpu}[mode](rank, world)
+        {"ddp_cpu": ddp_cpu, "moe_ep_cpu": moe_ep_cpu, "comm_gpu": comm_gpu, "train_gpu": train_gpu, "moe_gpu": moe_gpu}[mode](rank, world)
         dist.barrier()
         if rank == 0:
             print(f"WORKER-OK {mode}", flush=True)

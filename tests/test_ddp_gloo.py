@@ -22,6 +22,10 @@ def test_two_rank_gloo_ddp_and_sharded_muon():
     run_workers("ddp_cpu", 2, 29631)
 
 
+def test_two_rank_expert_parallel_engine():
+    run_workers("moe_ep_cpu", 2, 29633)
+
+
 def test_bucket_assignment_rule():
     import torch
 

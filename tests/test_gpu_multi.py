@@ -24,3 +24,8 @@ def test_comm_kernels_match_nccl():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
 def test_training_with_nvlink_kernels_matches_nccl():
     run_workers("train_gpu", 2, 29651, timeout=600, env_extra={"NCCL_NVLS_ENABLE": "0"})
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
+def test_expert_parallel_exchange_and_training():
+    run_workers("moe_gpu", 2, 29661, timeout=600, env_extra={"NCCL_NVLS_ENABLE": "0"})

@@ -1,5 +1,6 @@
 import math
 
+import pytest
 import torch
 
 from sample_efficient_gpt_b200.models import Transformer
@@ -63,3 +64,58 @@ def test_moe_transformer_trains_and_names():
     loss = logits.square().mean() + t.aux_loss()
     loss.backward()
     assert t.blocks[0].ffn.router.linear.weight.grad.abs().sum() > 0
+
+
+def _moe_model(seed=0, **kw):
+    from sample_efficient_gpt_b200.models import Transformer
+
+    torch.manual_seed(seed)
+    moe = dict(n_experts=4, top_k=2, d_ff=64, capacity_factor=kw.pop("capacity_factor", 1.25), aux_loss_weight=0.05)
+    return Transformer(2, 200, 64, 4, 128, attn_qknorm=True, attn_val_residual=True, attn_gating="per-head", layernorm_scaling=True,
+                       n_kv_heads=2, weight_tying=True, moe=moe, **kw)
+
+
+@pytest.mark.parametrize("cf", [1.25, 0.6])
+def test_engine_moe_matches_autograd(cf):
+    """Hand-scheduled MoE forward/backward (routing, dispatch, grouped GEMMs, combine, router backward incl. the
+    load-balance term and dropped assignments) against autograd of the module path."""
+    from sample_efficient_gpt_b200.training.engine import FusedEngine, engine_supports
+    from sample_efficient_gpt_b200.training.loss import efficient_cross_entropy
+
+    m = _moe_model(capacity_factor=cf)
+    assert engine_supports(m)
+    ids = torch.randint(0, 200, (2, 24))
+    tg = torch.randint(0, 200, (2, 24))
+    logits, _ = m(ids)
+    loss, _, _ = efficient_cross_entropy(logits, tg)
+    aux = m.aux_loss()
+    ((loss + aux) * 0.5).backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters()}
+    if cf < 1:
+        assert float(m.blocks[0].ffn.last_drop_fraction) > 0  # the small capacity really drops assignments
+    for p in m.parameters():
+        p.grad = None
+    eng = FusedEngine(m, torch.float32)
+    out = eng.forward_backward(ids, tg, 0.5)
+    assert float(out.loss) == pytest.approx(float(loss), rel=1e-5) and float(out.aux_loss) == pytest.approx(float(aux), rel=1e-5)
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, want[n], rtol=2e-3, atol=1e-6 + 1e-4 * float(want[n].abs().max())), n
+    eng.forward_backward(ids, tg, 0.5, first_micro_step=False)
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, 2 * want[n], rtol=2e-3, atol=1e-6 + 2e-4 * float(want[n].abs().max())), n
+    assert float(eng.forward_loss(ids, tg).loss) == pytest.approx(float(loss), rel=1e-5)
+
+
+def test_route_bwd_statement_matches_autograd():
+    from sample_efficient_gpt_b200.ops import moe as M
+
+    torch.manual_seed(3)
+    logits = torch.randn(17, 6, requires_grad=True)
+    probs = logits.softmax(-1)
+    w, idx = probs.topk(2, -1)
+    wn = w / w.sum(-1, keepdim=True)
+    dw = torch.randn(17, 2)
+    aux = torch.rand(6)
+    ((wn * dw).sum() + (probs * aux).sum()).backward()
+    got = M.route_bwd(probs.detach(), idx.int(), dw, aux)
+    assert torch.allclose(got, logits.grad, atol=1e-6)
