@@ -34,6 +34,17 @@ import torch.distributed as dist
 ROOT = Path(__file__).resolve().parent
 VOCAB, SEQ, MICRO_BATCH = 49152, 2048, 16
 METRIC = "training tokens/sec (IMU-1 430M, seq 2048, micro-batch 16/GPU, bf16)"
+MODEL_DESC = "IMU-1 430M (30 layers, d 1152, 18q/6kv heads x 64, SwiGLU 3072, vocab 49152)"
+# Further configurations of this package's own arm (``--model``); the headline (and the reference arm) is ``imu1``.
+MODELS = {
+    "imu1": None,
+    "moe": dict(yaml="imu1_moe.yaml", key=None, seq=2048, micro_batch=8, overrides={"trainer.dist_mode": "ddp_ep"},
+                metric="training tokens/sec (IMU-1 MoE 16 experts top-2, seq 2048, micro-batch 8/GPU, bf16)",
+                desc="IMU-1 attention stack, every FFN a 16-expert top-2 SwiGLU MoE (expert width 768, capacity 1.25, aux 0.01)"),
+    "dense_1p5b": dict(yaml="dense_1p5b.yaml", key=None, seq=4096, micro_batch=4, overrides={},
+                       metric="training tokens/sec (dense 1.5B, seq 4096, micro-batch 4/GPU, bf16, activation recompute)",
+                       desc="dense 1.5B (24 layers, d 2048, 16q/4kv heads x 128, SwiGLU 5632, vocab 49152)"),
+}
 
 
 def parse():
@@ -44,6 +55,7 @@ def parse():
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     p.add_argument("--config-key", type=str, default="bench")
     p.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
+    p.add_argument("--model", type=str, default="imu1", choices=sorted(MODELS), help="imu1 is the headline configuration")
     return p.parse_args()
 
 
@@ -167,7 +179,7 @@ def emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, impl, extra_cfg, h
     value = tokens / (ms_dev / 1e3)
     e2e_val = tokens / (ms_e2e / 1e3) if ms_e2e else None
     line = {
-        "metric": METRIC,
+        "metric": extra_cfg.pop("_metric", METRIC),
         "value": value,
         "unit": "tokens/s",
         "n_gpus": world,
@@ -181,7 +193,7 @@ def emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, impl, extra_cfg, h
         "data": "synthetic Zipf(s=1.1) token ids, random-init weights",
         "impl": impl,
         "config": {
-            "model": "IMU-1 430M (30 layers, d 1152, 18q/6kv heads x 64, SwiGLU 3072, vocab 49152)",
+            "model": extra_cfg.pop("_desc", MODEL_DESC),
             "global_batch": global_batch,
             "seq_len": SEQ,
             "parallelism": f"dp{world}",
@@ -200,6 +212,7 @@ def emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, impl, extra_cfg, h
 
 # ----------------------------------------------------------------------------- our implementation
 def run_ours(args):
+    global SEQ, MICRO_BATCH
     world, rank, local = dist_setup(args.gpus)
     from sample_efficient_gpt_b200 import ops
     from sample_efficient_gpt_b200.training.trainer import Trainer
@@ -214,7 +227,15 @@ def run_ours(args):
         obj = [str(tmp)]
         dist.broadcast_object_list(obj, src=0)
         tmp = Path(obj[0])
-    cfg = load_cfg(str(ROOT / "sample_efficient_gpt_b200/configs/imu1_base.yaml"), args.config_key)
+    spec = MODELS[args.model]
+    extra = {}
+    if spec is None:
+        cfg = load_cfg(str(ROOT / "sample_efficient_gpt_b200/configs/imu1_base.yaml"), args.config_key)
+    else:
+        SEQ, MICRO_BATCH = spec["seq"], spec["micro_batch"]
+        cfg = load_cfg(str(ROOT / "sample_efficient_gpt_b200/configs" / spec["yaml"]), spec["key"])
+        cfg = apply_overrides(cfg, {"trainer.ema_every": 10, **(spec["overrides"] if world > 1 else {})})
+        extra = {"_metric": spec["metric"], "_desc": spec["desc"]}
     cfg = apply_overrides(cfg, {
         "data.train_path": str(tmp / "train"), "data.validation_path": str(tmp / "val.npy"), "data.tokenizer_path": "",
         "data.batch_size": MICRO_BATCH * world, "data.context_length": SEQ,
@@ -266,7 +287,7 @@ def run_ours(args):
     if trainer.ddp is not None and trainer.ddp.comm is not None:
         trainer.ddp.comm.check()  # raises if a bounded wait on a peer gave up during the run
     emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, "ours",
-         {"comm": comm, "sharded_muon": bool(cfg.optim.shard_muon), "ema_every": cfg.trainer.ema_every}, h2d, d2h)
+         {"comm": comm, "sharded_muon": bool(cfg.optim.shard_muon), "ema_every": cfg.trainer.ema_every, **extra}, h2d, d2h)
     if world > 1:
         dist.destroy_process_group()
 

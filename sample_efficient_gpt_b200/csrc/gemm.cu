@@ -59,7 +59,29 @@ struct GemmParams {
   int symmetric;  // 1: D is symmetric (A == B, square): tiles wholly below the diagonal are skipped and mirrored
   void* D_extra[7];  // further destinations with D's layout (peer-mapped buffers of other ranks): every tile is
   int n_extra;       // stored to all of them, which turns the epilogue into the all-gather of the result
+  // Rows of A arrive from other ranks (expert-parallel dispatch): rows [r * region_rows, (r + 1) * region_rows) of every
+  // batch entry are complete once wait_flags[r] >= wait_seq (written by rank r with a system-scope release after its
+  // stores).  The producer waits, bounded, for the regions a tile touches before it issues the tile's first load.
+  const uint32_t* wait_flags;
+  uint32_t wait_seq;
+  int region_rows;
 };
+
+__device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t seq, const AbortState& ab, int code) {
+  uint32_t v;
+  const long long t0 = clock64();
+  while (true) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if ((int32_t)(v - seq) >= 0) return true;
+    if (*ab.cta_abort != 0) return false;
+    if (clock64() - t0 > ab.limit) {
+      *ab.cta_abort = 1;
+      atomicCAS(ab.global_status, 0, code);
+      return false;
+    }
+    __nanosleep(100);
+  }
+}
 
 // Tile enumeration shared by the three roles: tile t -> (batch, m_tile, n_tile), n fastest.
 struct TileCoord {
@@ -94,7 +116,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles * p.batch;
   const int k_blocks = (p.K + kBK - 1) / kBK;
-  const AbortState ab{cta_abort, p.status};
+  const AbortState ab{cta_abort, p.status, p.wait_flags != nullptr ? kPeerWaitCycles : kWaitCycles};
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
@@ -125,9 +147,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (elect_one()) {
       int it = 0;  // running stage counter across tiles
       bool ok = true;
+      uint32_t regions_ready = 0;  // bit r: rows of source region r have been seen complete
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
         if (p.symmetric && (tc.n + 1) * BN <= tc.m * kBM) continue;  // wholly below the diagonal: mirrored from its twin
+        if (!A_MN && p.wait_flags != nullptr) {
+          const int r0 = (tc.m * kBM) / p.region_rows;
+          const int last_row = min(tc.m * kBM + kBM, p.M) - 1;
+          for (int r = r0; r <= last_row / p.region_rows && ok; ++r) {
+            if (r < 32 && ((regions_ready >> r) & 1u)) continue;
+            ok = wait_region_flag(p.wait_flags + r, p.wait_seq, ab, 4);
+            if (r < 32) regions_ready |= 1u << r;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // rows written through the generic proxy, read by TMA
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -386,7 +420,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 
 int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
-              float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st) {
+              float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
+              const uint32_t* wait_flags, uint32_t wait_seq, int region_rows) {
   const int BN = (N <= 128) ? 128 : 256;
   CUtensorMap ma, mb;
   int r;
@@ -408,6 +443,9 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.symmetric = symmetric ? 1 : 0;
   p.n_extra = n_extra < 0 ? 0 : (n_extra > 7 ? 7 : n_extra);
   for (int i = 0; i < 7; ++i) p.D_extra[i] = i < p.n_extra ? d_extra[i] : nullptr;
+  p.wait_flags = (wait_flags != nullptr && region_rows > 0 && !a_mn_major) ? wait_flags : nullptr;
+  p.wait_seq = wait_seq;
+  p.region_rows = region_rows > 0 ? region_rows : 1;
 #define SEG_GEMM(BNv, AM, BM_)                                                                      \
   (out_f32 ? launch_gemm<BNv, AM, BM_, float>(ma, mb, p, sm_count, st)                              \
            : launch_gemm<BNv, AM, BM_, __nv_bfloat16>(ma, mb, p, sm_count, st))

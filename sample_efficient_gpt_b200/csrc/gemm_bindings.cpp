@@ -42,7 +42,8 @@ void check_operand(const Tensor& t, const char* name) {
 
 // D = alpha * A op(B) + beta * C
 Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, std::optional<Tensor> out, bool out_f32, bool a_mn,
-            bool b_mn, double alpha, double beta, bool symmetric, std::vector<int64_t> extra_dst) {
+            bool b_mn, double alpha, double beta, bool symmetric, std::vector<int64_t> extra_dst,
+            const std::optional<Tensor>& wait_flags, int64_t wait_seq, int64_t region_rows) {
   check_operand(a, "a");
   check_operand(b, "b");
   TORCH_CHECK(a.dim() == b.dim(), "a and b must have the same rank");
@@ -73,12 +74,19 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
   auto& st = device_state(a.device());
   const int64_t bsa = a.dim() == 3 ? a.stride(0) : 0, bsb = b.dim() == 3 ? b.stride(0) : 0, bsd = d.dim() == 3 ? d.stride(0) : 0;
   TORCH_CHECK(extra_dst.size() <= 7, "at most 7 extra destinations");
+  const uint32_t* wf = nullptr;
+  if (wait_flags.has_value()) {
+    TORCH_CHECK(wait_flags->is_cuda() && wait_flags->scalar_type() == at::kInt && wait_flags->is_contiguous() && !a_mn && region_rows > 0,
+                "wait_flags: contiguous CUDA int32 tensor, row-major A and region_rows > 0 required");
+    TORCH_CHECK(wait_flags->numel() * region_rows >= M, "wait_flags: one flag per region of rows");
+    wf = reinterpret_cast<const uint32_t*>(wait_flags->data_ptr<int>());
+  }
   void* extras[7] = {nullptr};
   for (size_t i = 0; i < extra_dst.size(); ++i) extras[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(extra_dst[i]));
   const int rc = seg::gemm_bf16(a.data_ptr(), b.data_ptr(), cptr, d.data_ptr(), M, N, K, batch, a.stride(-2), b.stride(-2),
                                 d.stride(-2), bsa, bsb, bsd, a_mn, b_mn, out_f32, (float)alpha, (float)beta, symmetric, extras,
                                 (int)extra_dst.size(), st.status.data_ptr<int>(), st.sm_count,
-                                at::cuda::getCurrentCUDAStream().stream());
+                                at::cuda::getCurrentCUDAStream().stream(), wf, (uint32_t)wait_seq, (int)region_rows);
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
   return d;
 }
@@ -119,7 +127,8 @@ void register_gemm(pybind11::module_& m) {
   m.def("gemm", &gemm, pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("c") = std::nullopt, pybind11::arg("out") = std::nullopt,
         pybind11::arg("out_f32") = false, pybind11::arg("a_mn") = false, pybind11::arg("b_mn") = false, pybind11::arg("alpha") = 1.0,
         pybind11::arg("beta") = 0.0, pybind11::arg("symmetric") = false,
-        pybind11::arg("extra_dst") = std::vector<int64_t>());
+        pybind11::arg("extra_dst") = std::vector<int64_t>(), pybind11::arg("wait_flags") = std::nullopt, pybind11::arg("wait_seq") = 0,
+        pybind11::arg("region_rows") = 0);
   m.def("fa_fwd", &fa_fwd);
   m.def("gemm_status", &gemm_status);
   m.def("gemm_reset_status", &gemm_reset_status);

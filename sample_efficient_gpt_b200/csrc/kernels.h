@@ -94,8 +94,11 @@ int moe_route(const void* x, const float* wr, int T, int d, int E, int k, float*
 void moe_slots(const int* idx, const int* block_off, int T, int E, int k, int cap, int* slot, cudaStream_t st);
 // dst[r]: rank r's buffer [E / world][world][cap][d] bf16 (peer-mapped).  Row (e_local, rank, slot) <- w * x[t] for every kept
 // assignment (w == nullptr: unscaled); rows [min(totals[e], cap), cap) of this rank's regions are zero-filled.
+// flags (optional): flags[r] is rank r's flag array; after all rows are stored, flags[r][rank] = seq is written with a
+// system-scope release (consumed by gemm_bf16's wait_flags).  done_counter: a zero-initialised device word.
 void moe_push(const void* x, const int* idx, const int* slot, const float* w, const int* totals, void* const* dst, int T, int d,
-              int E, int k, int cap, int world, int rank, cudaStream_t st);
+              int E, int k, int cap, int world, int rank, cudaStream_t st, uint32_t* const* flags = nullptr,
+              uint32_t* done_counter = nullptr, uint32_t seq = 0);
 // out[t] = sum over kept assignments of w * src[owner](e_local, rank, slot) (w == nullptr: 1); with dots != nullptr also
 // dots[t, c] = <g[t], src2[owner] row> (0 for dropped assignments).  out is bf16 or fp32.
 void moe_pull(void* const* src, void* const* src2, const int* idx, const int* slot, const float* w, const void* g, void* out,
@@ -113,9 +116,12 @@ void moe_route_bwd(const float* probs, const int* idx, const float* dw, const fl
 // d_extra[0..n_extra): up to 7 further destination buffers with D's layout (peer memory of other ranks).
 // Strides are in elements; bases and row strides must be 16-byte aligned.  Returns 0 when the launch was issued.
 // `status` is a device int that stays 0 unless a bounded wait inside the kernel gave up.
+// wait_flags (optional, A row-major only): rows [r * region_rows, (r+1) * region_rows) of A are written by another rank and
+// are complete once wait_flags[r] >= wait_seq; the kernel waits (bounded) per tile instead of the host ordering the launch.
 int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
-              float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st);
+              float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
+              const uint32_t* wait_flags = nullptr, uint32_t wait_seq = 0, int region_rows = 0);
 
 // ---- attn_fwd.cu (tcgen05 flash attention, forward)
 // q [B,S,H,hd], k/v [B,S,Hkv,hd] bf16, o like q, lse fp32 [B,H,S]; causal; hd == 64, S % 128 == 0.

@@ -15,8 +15,10 @@
 //             second buffer (backward: d(weight) = <dout[t], y_k[t]>)
 //   route_bwd gradient of the renormalised top-k weights, the load-balance term and the softmax -> d(logits)
 //
-// Ordering between ranks (rows pushed before the owner's GEMMs read them, outputs written before the sources pull them)
-// comes from the device-side flag barrier of comm.cu, launched between these kernels; none of the kernels here waits.
+// Ordering between ranks: outputs are written before the sources pull them because the device-side flag barrier of comm.cu
+// runs between the kernels; rows are pushed before the owner's GEMM reads them either through that barrier or, in the
+// overlapped mode, because the push kernel's last CTA releases a per-destination flag that the GEMM's producer acquires per
+// source region (gemm.cu).  None of the kernels here waits on anything.
 // The reference has no mixture-of-experts code; the specification is models/moe.py of this package.
 #include "common.cuh"
 #include "kernels.h"
@@ -136,12 +138,13 @@ __global__ void moe_slot_kernel(const int* __restrict__ idx, const int* __restri
 __global__ void __launch_bounds__(256) moe_push_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
                                                      const int* __restrict__ slot, const float* __restrict__ w,
                                                      const int* __restrict__ totals, MoeBufs dst, int T, int d, int E, int k, int cap,
-                                                     int e_local, int world, int rank, int n_row_blocks) {
+                                                     int e_local, int world, int rank, int n_row_blocks, MoeBufs flags,
+                                                     uint32_t* done_counter, uint32_t seq) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vecs = d / 8;
   if ((int)blockIdx.x < n_row_blocks) {
     const int t = blockIdx.x * 8 + warp;
-    if (t >= T) return;
+    if (t < T) {
     __nv_bfloat16* rows[kMoeMaxTopK];
     float ws[kMoeMaxTopK];
 #pragma unroll
@@ -174,6 +177,7 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const __nv_bfloat16* __re
           }
         }
     }
+    }
   } else {
     const int b = blockIdx.x - n_row_blocks;
     const int e = b / kMoeTailBlocks, part = b % kMoeTailBlocks;
@@ -182,6 +186,19 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const __nv_bfloat16* __re
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     for (int r = first + part * 8 + warp; r < cap; r += kMoeTailBlocks * 8)
       for (int v = lane; v < vecs; v += 32) *reinterpret_cast<uint4*>(base + (size_t)r * d + v * 8) = zero;
+  }
+  if (done_counter == nullptr) return;
+  // Completion signal: the last CTA to finish tells every destination rank that this rank's rows have landed.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_counter = 0;  // ready for the next launch (launches on one stream do not overlap)
+      __threadfence_system();
+      for (int r = 0; r < world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(flags.p[r]) + rank), "r"(seq) : "memory");
+    }
   }
 }
 
@@ -312,11 +329,13 @@ void moe_slots(const int* idx, const int* block_off, int T, int E, int k, int ca
 }
 
 void moe_push(const void* x, const int* idx, const int* slot, const float* w, const int* totals, void* const* dst, int T, int d,
-              int E, int k, int cap, int world, int rank, cudaStream_t st) {
+              int E, int k, int cap, int world, int rank, cudaStream_t st, uint32_t* const* flags, uint32_t* done_counter,
+              uint32_t seq) {
   const int n_row_blocks = (T + 7) / 8;
-  moe_push_kernel<<<n_row_blocks + E * kMoeTailBlocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), idx, slot, w, totals,
-                                                                     make_bufs(dst, world), T, d, E, k, cap, E / world, world, rank,
-                                                                     n_row_blocks);
+  const bool signal = flags != nullptr && done_counter != nullptr;
+  moe_push_kernel<<<n_row_blocks + E * kMoeTailBlocks, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), idx, slot, w, totals, make_bufs(dst, world), T, d, E, k, cap, E / world, world, rank,
+      n_row_blocks, make_bufs(signal ? reinterpret_cast<void* const*>(flags) : nullptr, world), signal ? done_counter : nullptr, seq);
 }
 
 void moe_pull(void* const* src, void* const* src2, const int* idx, const int* slot, const float* w, const void* g, void* out,

@@ -57,8 +57,11 @@ Tensor moe_slots(const Tensor& idx, const Tensor& block_off, int64_t cap) {
   return slot;
 }
 
+// flag_ptrs (one per rank, or empty) + done_counter (zeroed uint32/int32 CUDA scalar) + seq: completion signal for the
+// consumer's per-region waits.
 void moe_push(const Tensor& x, const Tensor& idx, const Tensor& slot, const std::optional<Tensor>& w, const Tensor& totals,
-              std::vector<int64_t> dst, int64_t cap, int64_t rank) {
+              std::vector<int64_t> dst, int64_t cap, int64_t rank, std::vector<int64_t> flag_ptrs,
+              const std::optional<Tensor>& done_counter, int64_t seq) {
   check(x, at::kBFloat16, "x");
   check(idx, at::kInt, "idx");
   check(slot, at::kInt, "slot");
@@ -69,8 +72,17 @@ void moe_push(const Tensor& x, const Tensor& idx, const Tensor& slot, const std:
   const int T = (int)x.size(0), d = (int)x.size(1), k = (int)idx.size(1), E = (int)totals.size(0);
   TORCH_CHECK(d % 8 == 0 && E % world == 0 && idx.size(0) == T && slot.sizes() == idx.sizes(), "moe_push: shape mismatch");
   c10::cuda::CUDAGuard guard(x.device());
+  void* flags[seg::kMaxRanks];
+  const bool signal = !flag_ptrs.empty();
+  if (signal) {
+    TORCH_CHECK((int)flag_ptrs.size() == world && done_counter.has_value(), "moe_push: flags need one array per rank and a counter");
+    check(*done_counter, at::kInt, "done_counter");
+    for (int i = 0; i < world; ++i) flags[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(flag_ptrs[i]));
+  }
   seg::moe_push(x.data_ptr(), idx.data_ptr<int>(), slot.data_ptr<int>(), w.has_value() ? w->data_ptr<float>() : nullptr,
-                totals.data_ptr<int>(), bufs, T, d, E, k, (int)cap, world, (int)rank, at::cuda::getCurrentCUDAStream().stream());
+                totals.data_ptr<int>(), bufs, T, d, E, k, (int)cap, world, (int)rank, at::cuda::getCurrentCUDAStream().stream(),
+                signal ? reinterpret_cast<uint32_t* const*>(flags) : nullptr,
+                signal ? reinterpret_cast<uint32_t*>(done_counter->data_ptr<int>()) : nullptr, (uint32_t)seq);
 }
 
 // returns (out [T,d], dots [T,k] or empty)
@@ -120,7 +132,9 @@ Tensor moe_route_bwd(const Tensor& probs, const Tensor& idx, const Tensor& dw, c
 void register_moe(pybind11::module_& m) {
   m.def("moe_route", &moe_route);
   m.def("moe_slots", &moe_slots);
-  m.def("moe_push", &moe_push);
+  m.def("moe_push", &moe_push, pybind11::arg("x"), pybind11::arg("idx"), pybind11::arg("slot"), pybind11::arg("w"),
+        pybind11::arg("totals"), pybind11::arg("dst"), pybind11::arg("cap"), pybind11::arg("rank"),
+        pybind11::arg("flag_ptrs") = std::vector<int64_t>{}, pybind11::arg("done_counter") = std::nullopt, pybind11::arg("seq") = 0);
   m.def("moe_pull", &moe_pull);
   m.def("moe_route_bwd", &moe_route_bwd);
   m.attr("MOE_MAX_EXPERTS") = seg::kMoeMaxExperts;

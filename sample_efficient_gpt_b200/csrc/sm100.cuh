@@ -54,10 +54,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // raised the CTA's abort flag) the wait gives up, records where it happened and the caller unwinds to the
 // common teardown.  A healthy kernel never comes close (the longest legitimate wait is one tile's mainloop).
 constexpr long long kWaitCycles = 2000000000LL;  // about one second at B200 clocks
+// Kernels whose producer waits for rows that another rank sends use this limit for every wait: ranks may be skewed by
+// seconds (a checkpoint write on one of them), and all roles of the CTA stand still while the producer waits.
+constexpr long long kPeerWaitCycles = 20000000000LL;  // about ten seconds
 
 struct AbortState {
   volatile int* cta_abort;  // shared memory flag, one per CTA
   int* global_status;       // device word: 0 = ok, otherwise code of the first wait that gave up
+  long long limit = kWaitCycles;
 };
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortState& ab, int code) {
@@ -66,7 +70,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*ab.cta_abort != 0) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > ab.limit) {
       *ab.cta_abort = 1;
       atomicCAS(ab.global_status, 0, code);
       return false;

@@ -98,7 +98,7 @@ class TorchExchange:
         buf = x.new_zeros(E * cap, d)
         buf.index_copy_(0, flat[keep], rows[keep])
         recv = self._a2a(buf.view(self.world, self.e_local, cap, d))  # [src, e_local, cap, d]
-        return recv.permute(1, 0, 2, 3).reshape(self.e_local, self.world * cap, d).contiguous()
+        return recv.permute(1, 0, 2, 3).reshape(self.e_local, self.world * cap, d).contiguous(), None
 
     def collect(self, buf: Tensor, idx: Tensor, slot: Tensor, w: Tensor | None, cap: int, out_dtype, dot_buf: Tensor | None = None,
                 g: Tensor | None = None):
@@ -125,13 +125,26 @@ class TorchExchange:
 class PeerExchange:
     """Exchange over symmetric memory with this package's push / pull kernels (bf16 CUDA tensors only)."""
 
-    def __init__(self, n_experts: int, comm=None, device=None):
+    def __init__(self, n_experts: int, comm=None, device=None, overlap: bool | None = None):
+        """``overlap``: instead of a barrier between the push and the first expert GEMM, the push signals per-destination
+        flags and the GEMM's producer waits per source region, so an expert's tiles start as soon as their rows are in
+        (default: on when there is more than one rank; ``SEGPT_MOE_OVERLAP=0`` switches it off)."""
+        import os
+
         self.comm = comm
         self.world = comm.world if comm is not None else 1
         self.rank = comm.rank if comm is not None else 0
         self.n_experts, self.e_local = n_experts, n_experts // self.world
         self.device = torch.device(device) if device is not None else (comm.device if comm is not None else torch.device("cuda"))
         self._bufs: dict = {}
+        if overlap is None:
+            overlap = os.environ.get("SEGPT_MOE_OVERLAP", "1") == "1"
+        self.overlap = bool(overlap and comm is not None and self.world > 1)
+        if self.overlap:
+            self.flags = comm.symm_zeros((64,), torch.int32)  # flags[src]: last dispatch of rank src that has fully landed
+            self.flag_ptrs = comm.all_addresses(self.flags)
+            self.done = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.seq = 0
 
     def begin_step(self):
         """Nobody may push into this step's buffers before every rank is done with the previous step's."""
@@ -159,10 +172,15 @@ class PeerExchange:
     def dispatch(self, key, x: Tensor, idx: Tensor, slot: Tensor, totals: Tensor, w: Tensor | None, cap: int) -> Tensor:
         buf = self._buffer(key, cap, x.size(1))
         ops._count()
+        view = buf.view(self.e_local, self.world * cap, x.size(1))
+        if self.overlap:
+            self.seq += 1
+            ops.ext().moe_push(x.contiguous(), idx, slot, w, totals, self._addresses(buf), cap, self.rank, self.flag_ptrs, self.done, self.seq)
+            return view, (self.flags, self.seq, cap)  # the consumer GEMM waits per source region
         ops.ext().moe_push(x.contiguous(), idx, slot, w, totals, self._addresses(buf), cap, self.rank)
         if self.comm is not None:
             self.comm.barrier()  # every rank's rows have landed before anybody's GEMMs read them
-        return buf.view(self.e_local, self.world * cap, x.size(1))
+        return view, None
 
     def collect(self, buf: Tensor, idx: Tensor, slot: Tensor, w: Tensor | None, cap: int, out_dtype, dot_buf: Tensor | None = None,
                 g: Tensor | None = None):

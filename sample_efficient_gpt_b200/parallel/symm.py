@@ -42,10 +42,17 @@ class SymmComm:
         self.use_multimem = use_multimem
         self.stream = torch.cuda.Stream(device=device, priority=-1)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # Two flag channels with their own sequence numbers: kernels of one channel run in the same order on every rank
+        # (they share a stream); kernels of different channels may be in flight at the same time and must not see each
+        # other's flag words.  Channel "bucket": gradient all-reduces on the side stream.  Channel "main": barriers and
+        # all-gathers on the caller's stream (Muon step, expert-parallel exchange).
         self.seq = 1
+        self.seq_main = 1
         self._handles: dict[int, tuple] = {}  # data_ptr -> (tensor, handle)
         self.flags, self._flags_hdl = self._alloc(ext.COMM_MAX_BLOCKS * ext.COMM_MAX_RANKS * 4, zero=True)
         self.flag_ptrs = [int(p) for p in self._flags_hdl.buffer_ptrs]
+        self.flags_main, self._flags_main_hdl = self._alloc(ext.COMM_MAX_BLOCKS * ext.COMM_MAX_RANKS * 4, zero=True)
+        self.flag_ptrs_main = [int(p) for p in self._flags_main_hdl.buffer_ptrs]
         self.wire = None
         self.bucket_ranges: list[tuple[int, int]] = []
         self.flat_grads: Tensor | None = None
@@ -118,10 +125,10 @@ class SymmComm:
         hdl, off = self._handle_of(t)
         chunk_bytes = chunk_rows * t[0].numel() * t.element_size()
         assert chunk_bytes % 16 == 0 and off % 16 == 0
-        ops.ext().comm_allgather([int(p) for p in hdl.buffer_ptrs], self.flag_ptrs, off, chunk_bytes, self.rank, self.seq,
+        ops.ext().comm_allgather([int(p) for p in hdl.buffer_ptrs], self.flag_ptrs_main, off, chunk_bytes, self.rank, self.seq_main,
                                  self.blocks, self.status)
         ops._count()
-        self.seq += 2
+        self.seq_main += 2
 
     def peer_addresses(self, t: Tensor) -> list[int]:
         """Addresses of the other ranks' copies of ``t`` (a view of a ``symm_zeros`` buffer)."""
@@ -135,9 +142,9 @@ class SymmComm:
 
     def barrier(self):
         """Device-side barrier across ranks on the current stream (a zero-byte all-gather)."""
-        ops.ext().comm_allgather(self.flag_ptrs, self.flag_ptrs, 0, 0, self.rank, self.seq, 1, self.status)
+        ops.ext().comm_allgather(self.flag_ptrs_main, self.flag_ptrs_main, 0, 0, self.rank, self.seq_main, 1, self.status)
         ops._count()
-        self.seq += 2
+        self.seq_main += 2
 
     def check(self):
         """Host read (synchronises): raises when a kernel gave up waiting for a peer."""

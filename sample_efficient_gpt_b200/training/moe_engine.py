@@ -24,12 +24,16 @@ from sample_efficient_gpt_b200 import ops
 from sample_efficient_gpt_b200.ops import moe as M
 
 
-def _bmm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Tensor | None = None, out_f32: bool = False, accumulate: bool = False):
-    """Batched ``op(a) @ op(b)``: a is [.., M, K] (or [.., K, M] with a_mn), b is [.., N, K] (or [.., K, N] with b_mn)."""
+def _bmm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Tensor | None = None, out_f32: bool = False, accumulate: bool = False,
+         wait=None):
+    """Batched ``op(a) @ op(b)``: a is [.., M, K] (or [.., K, M] with a_mn), b is [.., N, K] (or [.., K, N] with b_mn).
+    ``wait``: per-source-region arrival flags of ``a`` (see ``ops.gemm.gemm``); only the tcgen05 GEMM can honour them."""
     from sample_efficient_gpt_b200.ops import gemm as G
 
     if a.dtype == torch.bfloat16 and G.usable(a, b, out) and ops.kernel_enabled("moe_gemm"):
-        return G.gemm(a, b, c=out if accumulate else None, out=out, out_f32=out_f32, a_mn=a_mn, b_mn=b_mn, beta=1.0 if accumulate else 0.0)
+        return G.gemm(a, b, c=out if accumulate else None, out=out, out_f32=out_f32, a_mn=a_mn, b_mn=b_mn, beta=1.0 if accumulate else 0.0,
+                      wait=wait)
+    assert wait is None, "arrival flags need the tcgen05 GEMM"
     A = a.transpose(-1, -2) if a_mn else a
     B = b if b_mn else b.transpose(-1, -2)
     if out_f32 and a.is_cuda and a.dtype != torch.float32:
@@ -107,8 +111,8 @@ class MoEEngine:
         if record:  # not when a checkpointed block is recomputed in the backward sweep
             self.aux_terms.append(ffn.aux_loss_weight * self.E * (frac * probs.mean(0)).sum())
             self.drop_fractions.append((slot < 0).float().mean())
-        xb = self.ex.dispatch(("x", i), n2, idx, slot, totals, None, cap)  # [E_local, world * cap, d]
-        u = _bmm(xb, self.up_w[i], False, False)
+        xb, arrival = self.ex.dispatch(("x", i), n2, idx, slot, totals, None, cap)  # [E_local, world * cap, d]
+        u = _bmm(xb, self.up_w[i], False, False, wait=arrival)
         a = ops.swiglu_fwd(u.view(-1, u.size(-1))).view(u.size(0), u.size(1), self.f)
         yb = _bmm(a, self.down_w[i], False, False, out=self.ex.output_buffer(("y", i), (xb.size(0), xb.size(1), d), n2.dtype, n2.device))
         m, _ = self.ex.collect(yb, idx, slot, w, cap, n2.dtype)
@@ -122,8 +126,8 @@ class MoEEngine:
         ffn = self.eng.model.blocks[i].ffn
         probs, idx, w, slot, totals, frac, cap, xb, u, a, yb = saved
         T, d = n2.shape
-        dyb = self.ex.dispatch("dy", dm, idx, slot, totals, w, cap)  # rows already scaled by the routing weights
-        da = _bmm(dyb, self.down_w[i], False, True)  # [E_local, R, f]
+        dyb, arrival = self.ex.dispatch("dy", dm, idx, slot, totals, w, cap)  # rows already scaled by the routing weights
+        da = _bmm(dyb, self.down_w[i], False, True, wait=arrival)  # [E_local, R, f]; the later GEMMs follow it on the stream
         acc = (not first) and self.grads_in_stacks
         _bmm(dyb, a, True, True, out=self.down_g[i], out_f32=True, accumulate=acc)
         du = ops.swiglu_bwd(da.view(-1, self.f), u.view(-1, u.size(-1))).view_as(u)

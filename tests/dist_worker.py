@@ -230,8 +230,12 @@ def moe_gpu(rank, world):
     peer, ref = M.PeerExchange(E, comm), M.TorchExchange(E, dist.group.WORLD)
     for scaled in (None, w):
         peer.begin_step()
-        got = peer.dispatch("t", x, idx, slot, totals, scaled, cap)
-        want = ref.dispatch("t", x, idx, slot, totals, scaled, cap)
+        got, arrival = peer.dispatch("t", x, idx, slot, totals, scaled, cap)
+        want, _ = ref.dispatch("t", x, idx, slot, totals, scaled, cap)
+        if arrival is not None:  # rows are consumed through the GEMM's per-region waits: multiply by the identity
+            from sample_efficient_gpt_b200.ops import gemm as G
+            eye = torch.eye(d, device=dev, dtype=torch.bfloat16).expand(got.size(0), d, d).contiguous()
+            got = G.gemm(got, eye, wait=arrival)
         torch.cuda.synchronize()
         assert torch.allclose(got.float(), want.float(), atol=1e-2, rtol=1e-2), "dispatch mismatch"
         yb = peer.output_buffer("y", tuple(want.shape), torch.bfloat16, dev)

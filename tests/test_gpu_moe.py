@@ -51,8 +51,8 @@ def test_push_pull_match_reference_single_rank(scaled):
     peer, ref = M.PeerExchange(E, None, "cuda"), M.TorchExchange(E, None)
     ww = w if scaled else None
     peer._buffer("b", cap, d).fill_(7.0)  # stale content: tails must come back as zeros
-    got = peer.dispatch("b", x, idx, slot, totals, ww, cap)
-    want = ref.dispatch("b", x, idx, slot, totals, ww, cap)
+    got, _ = peer.dispatch("b", x, idx, slot, totals, ww, cap)
+    want, _ = ref.dispatch("b", x, idx, slot, totals, ww, cap)
     assert got.shape == want.shape == (E, cap, d)
     assert torch.allclose(got.float(), want.float(), atol=1e-2 if scaled else 0, rtol=1e-2 if scaled else 0)
     y = torch.randn_like(want)
