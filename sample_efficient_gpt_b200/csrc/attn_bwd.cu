@@ -1,0 +1,373 @@
+// Causal flash-attention backward for sm_100a on tcgen05 tensor cores, native GQA, head_dim 64, bf16.
+//
+// Given q [B,S,H,hd], k/v [B,S,Hkv,hd], o, dO [B,S,H,hd], lse [B,H,S] (natural log) it produces dq [B,S,H,hd] and
+// dk/dv [B,S,Hkv,hd].  With s = q k^T / sqrt(hd), P = exp(s - lse), D = rowsum(dO * o):
+//   dV = P^T dO,   dP = dO V^T,   dS = P * (dP - D),   dQ = dS K / sqrt(hd),   dK = dS^T Q / sqrt(hd).
+//
+// One CTA owns one key tile (128 keys) of one (batch, kv head) and walks over the query heads that share the kv head and
+// the query tiles at or after the key tile (causal).  It works on the *transposed* tiles, so that the thread that owns a
+// TMEM lane (= a key row) writes whole operand rows:
+//   S^T  = K Q^T   and  dP^T = V dO^T      (both K-major x K-major, 128x128 fp32 accumulators in TMEM)
+//   P^T, dS^T -> bf16 into shared memory in the 128-byte-swizzled K-major operand layout
+//   dV  += P^T  dO   (A K-major,  B = dO as MN-major operand, accumulates in TMEM over the whole walk)
+//   dK  += dS^T Q    (same shapes, accumulates in TMEM over the whole walk)
+//   dQ_i = dS  K     (A = the dS^T tile read as an MN-major operand, B = K as MN-major; fresh accumulator per tile,
+//                     drained with vector atomic adds into an fp32 dQ buffer because other key tiles add to the same rows)
+// TMEM: S^T 128 + dP^T 128 + dV 64 + dK 64 + dQ 64 = 448 of 512 columns, one CTA per SM.
+// Roles (192 threads): warp 0 TMA producer (K/V once; Q and dO tiles through a 2-stage ring; 4-D tensor maps, no
+// multicast), warp 1 MMA issuer, warps 2-5 the element-wise stage (one key row per thread); lse and D of the step's queries travel with the tiles as bulk copies.
+// Two small kernels frame it: `attn_bwd_prep` (D and lse in the exp2 domain) and `attn_bwd_finish` (dQ fp32 -> bf16).
+// The reference relies on PyTorch SDPA's backward or a Triton kernel with fp32 atomics for dQ
+// (transformer/ops/triton_flash_attn.py:104-201).  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "sm100.cuh"
+
+namespace seg {
+
+using namespace sm100;
+
+constexpr int kBT = 128;   // keys per CTA and queries per step
+constexpr int kBHD = 64;   // head dim
+constexpr int kBwdThreads = 192;
+constexpr int kBTile = kBT * kBHD * 2;   // 16 KB: one K, V, Q or dO tile
+constexpr int kBPds = kBT * kBT * 2;     // 32 KB: P^T or dS^T (two 64-column atoms)
+constexpr int kBwdSmem = 2 * kBTile /*K,V*/ + 2 * 2 * kBTile /*Q,dO x 2 stages*/ + 2 * kBPds + 2 * 2 * kBT * 4 /*lse2, D x 2*/ + 256 + 1024;
+
+struct AttnBwdParams {
+  int B, S, H, Hkv;
+  float scale_log2;  // log2(e) / sqrt(hd)
+  float scale;       // 1 / sqrt(hd)
+  const float* lse2;  // [B,H,S] lse * log2(e)
+  const float* dsum;  // [B,H,S] rowsum(dO * o)
+  float* dq_acc;      // [B,S,H,hd] fp32, zero-initialised
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int* status;
+};
+
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kBTile;
+  uint8_t* sQdO = sV + kBTile;            // stage s: Q at s*32K, dO at s*32K + 16K
+  uint8_t* sP = sQdO + 4 * kBTile;
+  uint8_t* sDS = sP + kBPds;
+  float* sLse = reinterpret_cast<float*>(sDS + kBPds);  // [2][128]
+  float* sD = sLse + 2 * kBT;                            // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sD + 2 * kBT);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;   // [2]
+  uint64_t* qdo_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;     // S^T and dP^T are in TMEM
+  uint64_t* pds_full = bars + 6;   // P^T and dS^T are in shared memory (and S^T/dP^T have been read)
+  uint64_t* mma_done = bars + 7;   // dV/dK/dQ MMAs of the step finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_t = p.S / kBT;
+  const int jt = blockIdx.x;  // key tile; small j = long walk, scheduled first
+  const int bg = blockIdx.y;
+  const int b = bg / p.Hkv, g = bg % p.Hkv;
+  const int group = p.H / p.Hkv;
+  const int per_head = n_t - jt;       // query tiles jt .. n_t-1
+  const int n_steps = group * per_head;
+  const AbortState ab{cta_abort, p.status};
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    mbar_init(smem_u32(kv_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&qdo_full[s]), 1);
+      mbar_init(smem_u32(&qdo_empty[s]), 1);
+    }
+    mbar_init(smem_u32(s_full), 1);
+    mbar_init(smem_u32(pds_full), 4);
+    mbar_init(smem_u32(mma_done), 1);
+    fence_barrier_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    prefetch_tensormap(&map_do);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 320, tm_dq = tmem_base + 384;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(smem_u32(kv_full), 2 * kBTile);
+      tma_load_4d(smem_u32(sK), &map_k, smem_u32(kv_full), 0, g, jt * kBT, b);
+      tma_load_4d(smem_u32(sV), &map_v, smem_u32(kv_full), 0, g, jt * kBT, b);
+      for (int n = 0; n < n_steps; ++n) {
+        const int st = n & 1;
+        if (!mbar_wait(smem_u32(&qdo_empty[st]), ((n >> 1) & 1) ^ 1, ab, 21)) break;
+        const int h = g * group + n / per_head, it = jt + n % per_head;
+        const uint32_t fb = smem_u32(&qdo_full[st]);
+        mbar_expect_tx(fb, 2 * kBTile + 2 * kBT * 4);
+        tma_load_4d(smem_u32(sQdO + st * 2 * kBTile), &map_q, fb, 0, h, it * kBT, b);
+        tma_load_4d(smem_u32(sQdO + st * 2 * kBTile + kBTile), &map_do, fb, 0, h, it * kBT, b);
+        const size_t stat = ((size_t)b * p.H + h) * p.S + (size_t)it * kBT;  // 128 floats: 512-byte aligned
+        bulk_load(smem_u32(sLse + st * kBT), p.lse2 + stat, kBT * 4, fb);
+        bulk_load(smem_u32(sD + st * kBT), p.dsum + stat, kBT * 4, fb);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t id_s = make_idesc_bf16(kBT, kBT, false, false);    // K (K-major) x Q (K-major)
+      constexpr uint32_t id_kv = make_idesc_bf16(kBT, kBHD, false, true);   // P^T / dS^T (K-major) x dO / Q (MN-major)
+      constexpr uint32_t id_dq = make_idesc_bf16(kBT, kBHD, true, true);    // dS (MN-major view of dS^T) x K (MN-major)
+      const uint32_t sk = smem_u32(sK), sv = smem_u32(sV), sp = smem_u32(sP), sds = smem_u32(sDS);
+      auto issue_s = [&](int n) {
+        const uint32_t sq = smem_u32(sQdO + (n & 1) * 2 * kBTile), sdo = sq + kBTile;
+#pragma unroll
+        for (int k = 0; k < kBHD / 16; ++k)
+          umma_bf16(tm_s, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + k * 32, 16, 1024), id_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < kBHD / 16; ++k)
+          umma_bf16(tm_dp, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + k * 32, 16, 1024), id_s, k > 0);
+        umma_commit(smem_u32(s_full));
+      };
+      bool ok = mbar_wait(smem_u32(kv_full), 0, ab, 22) && mbar_wait(smem_u32(&qdo_full[0]), 0, ab, 23);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int st = n & 1;
+        const uint32_t sq = smem_u32(sQdO + st * 2 * kBTile), sdo = sq + kBTile;
+        if (!mbar_wait(smem_u32(pds_full), n & 1, ab, 24)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
+          const uint64_t a_p = make_smem_desc(sp + (k >> 2) * (kBT * 128) + (k & 3) * 32, 16, 1024);
+          const uint64_t a_ds = make_smem_desc(sds + (k >> 2) * (kBT * 128) + (k & 3) * 32, 16, 1024);
+          umma_bf16(tm_dv, a_p, make_smem_desc(sdo + k * 2048, kBTile, 1024), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+          umma_bf16(tm_dk, a_ds, make_smem_desc(sq + k * 2048, kBTile, 1024), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys: 16 key rows of 128 bytes per step
+          umma_bf16(tm_dq, make_smem_desc(sds + k * 2048, kBT * 128, 1024), make_smem_desc(sk + k * 2048, kBTile, 1024), id_dq, k > 0);
+        umma_commit(smem_u32(mma_done));
+        umma_commit(smem_u32(&qdo_empty[st]));
+        if (n + 1 < n_steps) {
+          if (!mbar_wait(smem_u32(&qdo_full[(n + 1) & 1]), ((n + 1) >> 1) & 1, ab, 25)) break;
+          tc_fence_after();
+          issue_s(n + 1);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ element-wise stage: one key row per thread
+    const int sub = warp & 3;
+    const int r = sub * 32 + lane;  // key row inside the tile == TMEM lane; also the query row when draining dQ
+    const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+    bool ok = true;
+    for (int n = 0; n < n_steps && ok; ++n) {
+      const int h = g * group + n / per_head, it = jt + n % per_head;
+      const int st = n & 1;
+      // the per-query statistics arrive with the Q / dO tiles of the stage
+      if (!mbar_wait(smem_u32(&qdo_full[st]), (n >> 1) & 1, ab, 28)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(s_full), n & 1, ab, 26)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (it == jt);
+      const float* lse_s = sLse + st * kBT;
+      const float* d_s = sD + st * kBT;
+#pragma unroll
+      for (int c = 0; c < kBT / 32; ++c) {
+        uint32_t sv_[32], dpv[32];
+        tmem_ld_32x32(tm_s + lane_addr + c * 32, sv_);
+        tmem_ld_32x32(tm_dp + lane_addr + c * 32, dpv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c16 = 0; c16 < 4; ++c16) {
+          float pr[8], ds[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = c * 32 + c16 * 8 + e;  // query index inside the tile
+            float pe = ex2_fast(fmaf(__uint_as_float(sv_[c16 * 8 + e]), p.scale_log2, -lse_s[col]));
+            if (diag && col < r) pe = 0.f;  // causal: the query must not precede the key
+            pr[e] = pe;
+            ds[e] = pe * (__uint_as_float(dpv[c16 * 8 + e]) - d_s[col]);
+          }
+          const int chunk = c * 4 + c16;  // 16-byte chunk index along the row (16 chunks of 8 columns)
+          const int off = (chunk >> 3) * (kBT * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+          *reinterpret_cast<bf16x8*>(sP + off) = pack8(pr);
+          *reinterpret_cast<bf16x8*>(sDS + off) = pack8(ds);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(pds_full));
+      // drain dQ of this step (lane = query row) while the tensor core already works on the next S^T / dP^T
+      if (!mbar_wait(smem_u32(mma_done), n & 1, ab, 27)) { ok = false; break; }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + (((size_t)b * p.S + (size_t)it * kBT + r) * p.H + h) * kBHD;
+#pragma unroll
+      for (int c = 0; c < kBHD / 32; ++c) {
+        uint32_t qv[32];
+        tmem_ld_32x32(tm_dq + lane_addr + c * 32, qv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 4)
+          red_add_v4(dq_row + c * 32 + e, __uint_as_float(qv[e]) * p.scale, __uint_as_float(qv[e + 1]) * p.scale,
+                     __uint_as_float(qv[e + 2]) * p.scale, __uint_as_float(qv[e + 3]) * p.scale);
+      }
+      tc_fence_before();
+    }
+    if (ok && n_steps > 0) {
+      // dV and dK of this key tile: the last mma_done has been waited for above
+      tc_fence_after();
+      const size_t row = (((size_t)b * p.S + (size_t)jt * kBT + r) * p.Hkv + g) * kBHD;
+#pragma unroll
+      for (int c = 0; c < kBHD / 32; ++c) {
+        uint32_t a[32], d[32];
+        tmem_ld_32x32(tm_dv + lane_addr + c * 32, a);
+        tmem_ld_32x32(tm_dk + lane_addr + c * 32, d);
+        tmem_ld_wait();
+        float fv[32], fk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          fv[e] = __uint_as_float(a[e]);
+          fk[e] = __uint_as_float(d[e]) * p.scale;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          reinterpret_cast<bf16x8*>(p.dv + row + c * 32)[q4] = pack8(fv + q4 * 8);
+          reinterpret_cast<bf16x8*>(p.dk + row + c * 32)[q4] = pack8(fk + q4 * 8);
+        }
+      }
+    }
+  }
+
+  if (*cta_abort != 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+// D[b,h,s] = sum_hd dO * o, lse2 = lse * log2(e).  One warp per (token, head) row.
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                          const float* __restrict__ lse, float* __restrict__ dsum,
+                                                          float* __restrict__ lse2, int B, int S, int H) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int rows = B * S * H;
+  if (warp >= rows) return;
+  // row index over [B,S,H]; 64 elements per row: 2 per lane
+  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + (size_t)warp * kBHD)[lane];
+  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(d_o + (size_t)warp * kBHD)[lane];
+  const float2 fa = __bfloat1622float2(a), fg = __bfloat1622float2(g);
+  const float s = warp_sum(fa.x * fg.x + fa.y * fg.y);
+  if (lane == 0) {
+    const int h = warp % H, bs = warp / H;
+    const int sidx = bs % S, b = bs / S;
+    const size_t out = ((size_t)b * H + h) * S + sidx;
+    dsum[out] = s;
+    lse2[out] = lse[out] * 1.4426950408889634f;
+  }
+}
+
+__global__ void __launch_bounds__(256) attn_bwd_finish_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, size_t n8) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float f[8];
+  load8<float>(acc + i * 8, f);
+  store8<__nv_bfloat16>(dq + i * 8, f);
+}
+
+typedef CUresult (*EncodeTiledFnB)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_map_bshd_b(CUtensorMap* map, const void* base, int B, int S, int heads, int hd) {
+  static EncodeTiledFnB fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return -1;
+    fn = reinterpret_cast<EncodeTiledFnB>(ptr);
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)heads * hd * 2, (cuuint64_t)S * heads * hd * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+int attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+             float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st) {
+  if (hd != kBHD || S % kBT != 0 || H % Hkv != 0) return -10;
+  CUtensorMap mq, mk, mv, mdo;
+  int r = make_map_bshd_b(&mq, q, B, S, H, hd);
+  if (r == 0) r = make_map_bshd_b(&mk, k, B, S, Hkv, hd);
+  if (r == 0) r = make_map_bshd_b(&mv, v, B, S, Hkv, hd);
+  if (r == 0) r = make_map_bshd_b(&mdo, d_o, B, S, H, hd);
+  if (r != 0) return 100 + r;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const size_t n = (size_t)B * S * H * hd;
+  if (cudaMemsetAsync(dq_acc, 0, n * sizeof(float), st) != cudaSuccess) return -4;
+  const int rows = B * S * H;
+  attn_bwd_prep_kernel<<<(rows * 32 + 255) / 256, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o),
+                                                                lse, dsum, lse2, B, S, H);
+  AttnBwdParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
+  p.scale = 1.f / sqrtf((float)hd);
+  p.scale_log2 = 1.4426950408889634f * p.scale;
+  p.lse2 = lse2;
+  p.dsum = dsum;
+  p.dq_acc = dq_acc;
+  p.dk = static_cast<__nv_bfloat16*>(dk);
+  p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.status = status;
+  dim3 grid(S / kBT, B * Hkv);
+  attn_bwd_kernel<<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, p);
+  attn_bwd_finish_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace seg

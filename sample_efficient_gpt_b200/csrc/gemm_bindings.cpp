@@ -121,6 +121,31 @@ std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor
   return {o, lse};
 }
 
+// Backward of fa_fwd on the tcgen05 kernel: returns (dq, dk, dv).
+std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                          const Tensor& lse, bool causal) {
+  TORCH_CHECK(causal, "only causal attention is implemented");
+  for (const Tensor* t : {&d_o, &q, &k, &v, &o}) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->dim() == 4, "dO/q/k/v/o must be contiguous CUDA bf16 [B,S,H,hd]");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "dO/q/k/v/o must be 16-byte aligned");
+  }
+  const int B = q.size(0), S = q.size(1), H = q.size(2), hd = q.size(3), Hkv = k.size(2);
+  TORCH_CHECK(k.size(0) == B && k.size(1) == S && k.size(3) == hd && v.sizes() == k.sizes() && o.sizes() == q.sizes() && d_o.sizes() == q.sizes(),
+              "shape mismatch");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.dim() == 3 && lse.size(0) == B && lse.size(1) == H &&
+                  lse.size(2) == S, "lse must be contiguous fp32 [B,H,S]");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor dq = torch::empty_like(q), dk = torch::empty_like(k), dv = torch::empty_like(v);
+  Tensor acc = torch::empty(q.sizes(), q.options().dtype(at::kFloat));
+  Tensor dsum = torch::empty_like(lse), lse2 = torch::empty_like(lse);
+  auto& st = device_state(q.device());
+  const int rc = seg::attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(), dq.data_ptr(),
+                               dk.data_ptr(), dv.data_ptr(), acc.data_ptr<float>(), dsum.data_ptr<float>(), lse2.data_ptr<float>(), B, S, H,
+                               Hkv, hd, st.status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "attn_bwd: unsupported shape or launch failure (code ", rc, ")");
+  return {dq, dk, dv};
+}
+
 }  // namespace
 
 void register_gemm(pybind11::module_& m) {
@@ -130,6 +155,7 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("extra_dst") = std::vector<int64_t>(), pybind11::arg("wait_flags") = std::nullopt, pybind11::arg("wait_seq") = 0,
         pybind11::arg("region_rows") = 0);
   m.def("fa_fwd", &fa_fwd);
+  m.def("fa_bwd", &fa_bwd);
   m.def("gemm_status", &gemm_status);
   m.def("gemm_reset_status", &gemm_reset_status);
 }

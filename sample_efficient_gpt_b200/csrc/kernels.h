@@ -123,6 +123,12 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
               const uint32_t* wait_flags = nullptr, uint32_t wait_seq = 0, int region_rows = 0);
 
+// ---- attn_bwd.cu (tcgen05 flash attention, backward)
+// q, o, d_o, dq [B,S,H,hd]; k, v, dk, dv [B,S,Hkv,hd] bf16; lse [B,H,S] fp32 from the forward.  Scratch: dq_acc fp32 like q
+// (zeroed here), dsum and lse2 fp32 [B,H,S].  Causal; hd == 64, S % 128 == 0.  Returns 0 when launched.
+int attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+             float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st);
+
 // ---- attn_fwd.cu (tcgen05 flash attention, forward)
 // q [B,S,H,hd], k/v [B,S,Hkv,hd] bf16, o like q, lse fp32 [B,H,S]; causal; hd == 64, S % 128 == 0.
 // Returns 0 when launched, a negative code for unsupported shapes.

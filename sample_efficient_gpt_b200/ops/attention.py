@@ -1,9 +1,11 @@
 """Causal GQA attention on CUDA tensors: forward returning (O, ctx) and backward from ctx.
 
-Preferred implementation: this package's tcgen05 flash-attention kernels (``fa_fwd`` / ``fa_bwd`` in the
-extension) when they are built and support the shape.  Otherwise the library path: PyTorch's fused SDPA
-(flash / cuDNN backend, native GQA), differentiated through a private autograd tape so that the caller
-needs no autograd graph of its own.  ``SEGPT_ATTN_IMPL=library|native`` forces one of the two.
+Two implementations: this package's tcgen05 flash-attention kernels (``fa_fwd`` / ``fa_bwd`` in the extension; causal,
+head_dim 64, sequence a multiple of 128) and the library path: PyTorch's fused SDPA (flash / cuDNN backend, native GQA),
+differentiated through a private autograd tape so that the caller needs no autograd graph of its own.
+``SEGPT_ATTN_IMPL=native|library|auto``: ``auto`` (default) runs the native forward where no backward follows
+(evaluation, generation) and the library pair in training, where the library is currently the faster of the two;
+``native`` trains on the tcgen05 forward + backward kernels.
 """
 
 from __future__ import annotations
@@ -32,7 +34,7 @@ def _native_ok(q: Tensor, k: Tensor, v: Tensor, q_start: int, for_backward: bool
         if impl == "native":
             raise RuntimeError("SEGPT_ATTN_IMPL=native but the flash-attention kernels are not built")
         return False
-    if for_backward and not ops.has_kernel("fa_bwd"):
+    if for_backward and (impl != "native" or not ops.has_kernel("fa_bwd")):
         return False  # the library backward needs the library forward's tape
     hd = q.size(-1)
     return (q.dtype == torch.bfloat16 and hd == 64 and q_start == 0 and q.size(1) == k.size(1) and q.size(1) % 128 == 0

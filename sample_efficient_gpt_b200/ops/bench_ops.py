@@ -4,7 +4,8 @@
   python -m sample_efficient_gpt_b200.ops.bench_ops --op ns --rows 1152 --cols 3072 --batch 30
   python -m sample_efficient_gpt_b200.ops.bench_ops --op attention --seq 2048        (B 8, 18q/6kv heads of 64, fwd+bwd)
   python -m sample_efficient_gpt_b200.ops.bench_ops --op linear_ce                    ([32768,1152] x [49152,1152])
-  python -m sample_efficient_gpt_b200.ops.bench_ops --op elementwise
+  python -m sample_efficient_gpt_b200.ops.bench_ops --op elementwise                  (norms, SwiGLU, qkv post-processing, gate, AdamW, EMA)
+  python -m sample_efficient_gpt_b200.ops.bench_ops --op moe                          (router, dispatch, combine, router backward)
 Each line reports milliseconds, achieved TFLOP/s or GB/s, and the library call it replaces where there is one.
 """
 
@@ -112,7 +113,12 @@ def bench_attention(a):
         from sample_efficient_gpt_b200.ops import gemm as G
 
         t_n = timeit(lambda: ops.attention_fwd(q, k, v, True, 0, for_backward=False), a.iters)
-        out.update({"native_fwd_ms": t_n, "native_fwd_tflops": fl_f / t_n, "status": G.status()})
+        out.update({"native_fwd_ms": t_n, "native_fwd_tflops": fl_f / t_n})
+        if ops.has_kernel("fa_bwd"):
+            o_n, lse_n = ops.ext().fa_fwd(q, k, v, True)
+            t_nb = timeit(lambda: ops.ext().fa_bwd(do, q, k, v, o_n, lse_n, True), a.iters)
+            out.update({"native_bwd_ms": t_nb, "native_bwd_tflops": 2.5 * fl_f / t_nb})
+        out["status"] = G.status()
     print(json.dumps(out))
 
 
@@ -132,29 +138,105 @@ def bench_linear_ce(a):
         torch.nn.functional.cross_entropy(logits.float(), tg).backward()
 
     fl = 3 * 2.0 * T * d * V / 1e9
-    t_o, t_l = timeit(ours, a.iters), timeit(lib, max(2, a.iters // 2))
-    print(json.dumps({"op": "linear_ce_fwd_bwd", "ours_ms": t_o, "ours_tflops": fl / t_o, "materialised_logits_ms": t_l}))
+    t_o = timeit(ours, a.iters)
+    ops._DISABLED.add("ce_gemm")  # same chunking and CE kernel, library GEMMs
+    try:
+        t_c = timeit(ours, a.iters)
+    finally:
+        ops._DISABLED.discard("ce_gemm")
+    t_l = timeit(lib, max(2, a.iters // 2))
+    print(json.dumps({"op": "linear_ce_fwd_bwd", "ours_ms": t_o, "ours_tflops": fl / t_o, "with_library_gemms_ms": t_c,
+                      "with_library_gemms_tflops": fl / t_c, "materialised_logits_ms": t_l}))
+
+
+def measured_hbm_gbs() -> tuple[float, str]:
+    """Copy bandwidth measured on this pool (MEASURED_PEAKS.json at the repository root), else the stated fallback."""
+    from pathlib import Path
+
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "of measured"
+    return 6650.0, "of fallback"
+
+
+def report(rows, iters):
+    peak, label = measured_hbm_gbs()
+    for name, fn, nbytes in rows:
+        t = timeit(fn, iters)
+        gbs = nbytes / t / 1e6
+        print(json.dumps({"op": name, "ms": round(t, 4), "gb_per_s": round(gbs, 1), "mbytes": round(nbytes / 1e6, 1), "frac_hbm": round(gbs / peak, 3),
+                          "frac_of": label}))
 
 
 def bench_elementwise(a):
-    T, d, F = 32768, 1152, 3072
+    """Memory-bound kernels at the IMU-1 training shapes (T = 16 x 2048 tokens); bytes are the algorithmic minimum."""
+    T, d, F, H, Hkv, hd, B, S = 32768, 1152, 3072, 18, 6, 64, 16, 2048
     res, delta, gain = torch.randn(T, d, device="cuda"), rnd(T, d), torch.ones(d, device="cuda")
     x, y, rstd, _ = ops.add_rmsnorm_fwd(res, delta, gain, 1.0, 1e-5, torch.bfloat16, True)
     u, df = rnd(T, 2 * F), rnd(T, F)
+    from sample_efficient_gpt_b200.models.rope import RotaryPositionalEmbedding
+
+    rope = RotaryPositionalEmbedding(10000.0, hd, S, device="cuda")
+    qkv = rnd(T, (H + 2 * Hkv) * hd)
+    one = torch.ones(1, device="cuda")
+    v1 = ops.qkv_post_fwd(qkv, None, rope.cos, rope.sin, one, one, one * 0.5, one, B, S, H, Hkv, hd, True)[2].clone()
+    q, k, v = ops.qkv_post_fwd(qkv, v1, rope.cos, rope.sin, one, one, one * 0.5, one, B, S, H, Hkv, hd, True)
+    dq, dk, dv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    o, z, dg = rnd(T, H, hd), rnd(T, H), rnd(T, H * hd)
+    nq, nkv = T * H * hd, T * Hkv * hd
+    # flat parameter sets for the multi-tensor optimizer kernels (about the AdamW share of IMU-1: 2 x 49152 x 1152)
+    ps = [torch.randn(49152, 1152, device="cuda") for _ in range(2)]
+    gs, ms, vs = ([torch.randn_like(p) * 1e-3 for p in ps] for _ in range(3))
+    vs = [t.abs() for t in vs]
+    sh = [p.bfloat16() for p in ps]
+    ema = [p.clone() for p in ps]
+    npar = sum(p.numel() for p in ps)
     rows = [
         ("add_rmsnorm_fwd", lambda: ops.add_rmsnorm_fwd(res, delta, gain, 1.0, 1e-5, torch.bfloat16, True), T * d * (4 + 2 + 4 + 2)),
         ("add_rmsnorm_bwd", lambda: ops.add_rmsnorm_bwd(y, res, x, gain, rstd, 1.0, torch.bfloat16), T * d * (2 + 4 + 4 + 4 + 2)),
         ("swiglu_fwd", lambda: ops.swiglu_fwd(u), T * F * 6),
         ("swiglu_bwd", lambda: ops.swiglu_bwd(df, u), T * F * 10),
+        ("qkv_post_fwd", lambda: ops.qkv_post_fwd(qkv, v1, rope.cos, rope.sin, one, one, one * 0.5, one, B, S, H, Hkv, hd, True),
+         2 * ((nq + 2 * nkv) * 2 + nkv)),
+        ("qkv_post_bwd", lambda: ops.qkv_post_bwd(dq, dk, dv, qkv, v1, rope.cos, rope.sin, one, one, one * 0.5, one, B, S, H, Hkv, hd, True),
+         2 * ((nq + 2 * nkv) * 3 + 2 * nkv)),
+        ("gate_fwd", lambda: ops.gate_fwd(o, z), 2 * (2 * nq + T * H)),
+        ("gate_bwd", lambda: ops.gate_bwd(dg, o, z), 2 * (3 * nq + 2 * T * H)),
+        ("fused_adamw", lambda: ops.fused_adamw(ps, gs, ms, vs, sh, 1e-3, 0.1, 0.9, 0.95, 1e-8, 1e-3), npar * (4 * 4 + 3 * 4 + 2)),
+        ("fused_ema", lambda: ops.fused_ema(ema, ps, 0.999), npar * 12),
     ]
-    for name, fn, nbytes in rows:
-        t = timeit(fn, a.iters)
-        print(json.dumps({"op": name, "ms": t, "gb_per_s": nbytes / t / 1e6}))
+    report(rows, a.iters)
+
+
+def bench_moe(a):
+    """Routing and exchange kernels of the MoE block at the IMU-1 MoE shapes on one GPU (T = 8 x 2048 tokens, 16 experts,
+    top-2, capacity 1.25): with one rank the peer stores/loads go to local memory, so the figures are HBM fractions."""
+    from sample_efficient_gpt_b200.ops import moe as M
+
+    T, d, E, k = 16384, 1152, 16, 2
+    x, wr = rnd(T, d), torch.randn(E, d, device="cuda") * 0.1
+    cap = M.capacity(T, k, E, 1.25)
+    probs, idx, w, slot, totals = M.route(x, wr, k, cap)
+    ex = M.PeerExchange(E, None, "cuda")
+    xb, _ = ex.dispatch("x", x, idx, slot, totals, None, cap)
+    yb = ex.output_buffer("y", tuple(xb.shape), torch.bfloat16, "cuda")
+    yb.copy_(xb)
+    kept = int((slot >= 0).sum())
+    dw, aux = torch.randn(T, k, device="cuda"), torch.rand(E, device="cuda")
+    rows = [
+        ("moe_route (+scan +slots)", lambda: M.route(x, wr, k, cap), T * d * 2 + T * E * 4 + T * k * 12),
+        ("moe_push (dispatch)", lambda: ex.dispatch("x", x, idx, slot, totals, None, cap), T * d * 2 + E * cap * d * 2),
+        ("moe_push (scaled, backward)", lambda: ex.dispatch("x", x, idx, slot, totals, w, cap), T * d * 2 + E * cap * d * 2),
+        ("moe_pull (combine)", lambda: ex.collect(yb, idx, slot, w, cap, torch.bfloat16), kept * d * 2 + T * d * 2),
+        ("moe_pull (+dots, backward)", lambda: ex.collect(yb, idx, slot, None, cap, torch.float32, dot_buf=yb, g=x), 2 * kept * d * 2 + T * d * 2 + T * d * 4),
+        ("moe_route_bwd", lambda: M.route_bwd(probs, idx, dw, aux), T * E * 8 + T * k * 8),
+    ]
+    report(rows, a.iters)
 
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise"])
+    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe"])
     p.add_argument("--m", type=int, default=8192)
     p.add_argument("--n", type=int, default=1920)
     p.add_argument("--k", type=int, default=1152)
@@ -165,7 +247,7 @@ def main():
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--iters", type=int, default=10)
     a = p.parse_args()
-    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise}[a.op](a)
+    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe}[a.op](a)
 
 
 if __name__ == "__main__":

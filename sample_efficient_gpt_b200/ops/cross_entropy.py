@@ -3,6 +3,9 @@
 The [tokens, vocab] logits are produced chunk by chunk into one reused bf16 buffer, turned into losses and
 (in place) into logit gradients by ``ce_chunk_fwd_bwd`` (one read and one write of the chunk), and
 immediately consumed by the two gradient GEMMs, so the only full-size tensors are the inputs and outputs.
+The three GEMMs of a chunk run on this package's tcgen05 GEMM (``x W^T``, ``dlogits W`` and ``dlogits^T x`` read their
+operands in place through K-major / MN-major tensor maps; the weight gradient accumulates in fp32 through the GEMM's
+``beta * C`` epilogue); ``SEGPT_DISABLE_KERNELS=ce_gemm`` sends them to the library instead.
 Math: transformer/ops/cross_entropy.py:96-247 and fused_linear_cross_entropy.py:13-346 of the reference
 (the latter is present but unused there; its live path stores all logits).
 """
@@ -44,14 +47,24 @@ def linear_ce_fwd_bwd(h, w, targets, lse_square_scale, ignore_index, grad_scale,
     chunk = min(chunk, T)
     buf = _logits_buffer(chunk, V, dev)
     ext = ops.ext()
+    from sample_efficient_gpt_b200.ops import gemm as G
+
+    own = ops.kernel_enabled("ce_gemm") and G.usable(h, w, buf) and d % 8 == 0 and (dw is None or G.usable(dw))
     for s in range(0, T, chunk):
         e = min(T, s + chunk)
         lg = buf[: e - s]
-        torch.mm(h[s:e], w.t(), out=lg)
+        if own:
+            G.gemm(h[s:e], w, out=lg)
+        else:
+            torch.mm(h[s:e], w.t(), out=lg)
         ext.ce_chunk_fwd_bwd(lg, targets[s:e], loss[s:e], z[s:e], lse[s:e], lse_square_scale, ignore_index,
                              grad_scale, logit_scale, need_grad)
         ops._count()
         if need_grad:
-            torch.mm(lg, w, out=dh[s:e])
-            torch.addmm(dw, lg.t(), h[s:e], out_dtype=torch.float32, out=dw)
+            if own:
+                G.gemm(lg, w, b_mn=True, out=dh[s:e])
+                G.gemm(lg, h[s:e], a_mn=True, b_mn=True, c=dw, out=dw, out_f32=True, beta=1.0)
+            else:
+                torch.mm(lg, w, out=dh[s:e])
+                torch.addmm(dw, lg.t(), h[s:e], out_dtype=torch.float32, out=dw)
     return loss, z, dh, dw

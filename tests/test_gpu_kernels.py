@@ -181,3 +181,30 @@ def test_native_attention_forward(B, S, H, Hkv):
     o_ref, lse_ref = ref.attention_fwd(q.float(), k.float(), v.float(), True, 0)
     close(o, o_ref, 2e-2, 2e-2, name="O")
     close(lse, lse_ref, 2e-2, name="LSE")
+
+
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 6, 2), (2, 1024, 3, 1)])
+def test_native_attention_backward(B, S, H, Hkv):
+    """dq/dk/dv of the tcgen05 backward kernel against autograd of the fp32 statement of the same attention."""
+    from sample_efficient_gpt_b200.ops import gemm as G
+
+    assert ops.has_kernel("fa_bwd")
+    torch.manual_seed(11)
+    q = torch.randn(B, S, H, 64, device=DEV).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, 64, device=DEV).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, 64, device=DEV).to(torch.bfloat16)
+    do = torch.randn(B, S, H, 64, device=DEV).to(torch.bfloat16)
+    o, lse = _ext().fa_fwd(q, k, v, True)
+    dq, dk, dv = _ext().fa_bwd(do, q, k, v, o, lse, True)
+    torch.cuda.synchronize()
+    assert G.status() == 0, "a bounded wait inside the attention kernel gave up"
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    rep = H // Hkv
+    kk, vv = kf.repeat_interleave(rep, dim=2), vf.repeat_interleave(rep, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", qf, kk) / 8.0
+    s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device=DEV), 1), float("-inf"))
+    o_ref = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), vv)
+    o_ref.backward(do.float())
+    close(dq, qf.grad, 3e-2, 3e-2, name="dQ")
+    close(dk, kf.grad, 3e-2, 3e-2, name="dK")
+    close(dv, vf.grad, 3e-2, 3e-2, name="dV")
