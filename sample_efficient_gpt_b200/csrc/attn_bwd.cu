@@ -14,8 +14,8 @@
 //   dQ_i = dS  K     (A = the dS^T tile read as an MN-major operand, B = K as MN-major; fresh accumulator per tile,
 //                     drained with vector atomic adds into an fp32 dQ buffer because other key tiles add to the same rows)
 // TMEM: S^T 128 + dP^T 128 + dV 64 + dK 64 + dQ 64 = 448 of 512 columns, one CTA per SM.
-// Roles (192 threads): warp 0 TMA producer (K/V once; Q and dO tiles through a 2-stage ring; 4-D tensor maps, no
-// multicast), warp 1 MMA issuer, warps 2-5 the element-wise stage (one key row per thread); lse and D of the step's queries travel with the tiles as bulk copies.
+// Roles (320 threads): warp 0 TMA producer (K/V once; Q and dO tiles through a 2-stage ring; 4-D tensor maps, no
+// multicast), warp 1 MMA issuer, warps 2-9 the element-wise stage (a key row and half of the query columns per thread); lse and D of the step's queries travel with the tiles as bulk copies.
 // Two small kernels frame it: `attn_bwd_prep` (D and lse in the exp2 domain) and `attn_bwd_finish` (dQ fp32 -> bf16).
 // The reference relies on PyTorch SDPA's backward or a Triton kernel with fp32 atomics for dQ
 // (transformer/ops/triton_flash_attn.py:104-201).  Every mbarrier wait is bounded.
@@ -31,7 +31,7 @@ using namespace sm100;
 
 constexpr int kBT = 128;   // keys per CTA and queries per step
 constexpr int kBHD = 64;   // head dim
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // producer warp, MMA warp, 8 element-wise warps
 constexpr int kBTile = kBT * kBHD * 2;   // 16 KB: one K, V, Q or dO tile
 constexpr int kBPds = kBT * kBT * 2;     // 32 KB: P^T or dS^T (two 64-column atoms)
 constexpr int kBwdSmem = 2 * kBTile /*K,V*/ + 2 * 2 * kBTile /*Q,dO x 2 stages*/ + 2 * kBPds + 2 * 2 * kBT * 4 /*lse2, D x 2*/ + 256 + 1024;
@@ -103,7 +103,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(smem_u32(&qdo_empty[s]), 1);
     }
     mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(pds_full), 4);
+    mbar_init(smem_u32(pds_full), 8);
     mbar_init(smem_u32(mma_done), 1);
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -190,8 +190,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ element-wise stage: one key row per thread
+    // ------------------------------------------------------------------ element-wise stage
+    // Eight warps: warp % 4 selects the TMEM sub-partition (32 key rows), the two warps of a sub-partition split the
+    // 128 query columns in halves, so that every scheduler has two warps to alternate between.
     const int sub = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = sub * 32 + lane;  // key row inside the tile == TMEM lane; also the query row when draining dQ
     const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
     bool ok = true;
@@ -206,7 +209,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float* lse_s = sLse + st * kBT;
       const float* d_s = sD + st * kBT;
 #pragma unroll
-      for (int c = 0; c < kBT / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sv_[32], dpv[32];
         tmem_ld_32x32(tm_s + lane_addr + c * 32, sv_);
         tmem_ld_32x32(tm_dp + lane_addr + c * 32, dpv);
@@ -214,13 +218,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int c16 = 0; c16 < 4; ++c16) {
           float pr[8], ds[8];
+          const int col0 = c * 32 + c16 * 8;  // query index inside the tile
+          const float4 la = *reinterpret_cast<const float4*>(lse_s + col0), lb = *reinterpret_cast<const float4*>(lse_s + col0 + 4);
+          const float4 da = *reinterpret_cast<const float4*>(d_s + col0), db = *reinterpret_cast<const float4*>(d_s + col0 + 4);
+          const float ls[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+          const float dd[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int col = c * 32 + c16 * 8 + e;  // query index inside the tile
-            float pe = ex2_fast(fmaf(__uint_as_float(sv_[c16 * 8 + e]), p.scale_log2, -lse_s[col]));
-            if (diag && col < r) pe = 0.f;  // causal: the query must not precede the key
+            float pe = ex2_fast(fmaf(__uint_as_float(sv_[c16 * 8 + e]), p.scale_log2, -ls[e]));
+            if (diag && col0 + e < r) pe = 0.f;  // causal: the query must not precede the key
             pr[e] = pe;
-            ds[e] = pe * (__uint_as_float(dpv[c16 * 8 + e]) - d_s[col]);
+            ds[e] = pe * (__uint_as_float(dpv[c16 * 8 + e]) - dd[e]);
           }
           const int chunk = c * 4 + c16;  // 16-byte chunk index along the row (16 chunks of 8 columns)
           const int off = (chunk >> 3) * (kBT * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
@@ -232,43 +240,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(pds_full));
-      // drain dQ of this step (lane = query row) while the tensor core already works on the next S^T / dP^T
+      // drain dQ of this step (lane = query row; each half takes 32 of the 64 columns) while the tensor core already
+      // works on the next S^T / dP^T
       if (!mbar_wait(smem_u32(mma_done), n & 1, ab, 27)) { ok = false; break; }
       tc_fence_after();
-      float* dq_row = p.dq_acc + (((size_t)b * p.S + (size_t)it * kBT + r) * p.H + h) * kBHD;
-#pragma unroll
-      for (int c = 0; c < kBHD / 32; ++c) {
+      float* dq_row = p.dq_acc + (((size_t)b * p.S + (size_t)it * kBT + r) * p.H + h) * kBHD + half * 32;
+      {
         uint32_t qv[32];
-        tmem_ld_32x32(tm_dq + lane_addr + c * 32, qv);
+        tmem_ld_32x32(tm_dq + lane_addr + half * 32, qv);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; e += 4)
-          red_add_v4(dq_row + c * 32 + e, __uint_as_float(qv[e]) * p.scale, __uint_as_float(qv[e + 1]) * p.scale,
+          red_add_v4(dq_row + e, __uint_as_float(qv[e]) * p.scale, __uint_as_float(qv[e + 1]) * p.scale,
                      __uint_as_float(qv[e + 2]) * p.scale, __uint_as_float(qv[e + 3]) * p.scale);
       }
       tc_fence_before();
     }
     if (ok && n_steps > 0) {
-      // dV and dK of this key tile: the last mma_done has been waited for above
+      // dV (first four warps) and dK (the other four) of this key tile: the last mma_done has been waited for above
       tc_fence_after();
       const size_t row = (((size_t)b * p.S + (size_t)jt * kBT + r) * p.Hkv + g) * kBHD;
+      const uint32_t src = half == 0 ? tm_dv : tm_dk;
+      __nv_bfloat16* dst = (half == 0 ? p.dv : p.dk) + row;
+      const float mul = half == 0 ? 1.f : p.scale;
 #pragma unroll
       for (int c = 0; c < kBHD / 32; ++c) {
-        uint32_t a[32], d[32];
-        tmem_ld_32x32(tm_dv + lane_addr + c * 32, a);
-        tmem_ld_32x32(tm_dk + lane_addr + c * 32, d);
+        uint32_t a[32];
+        tmem_ld_32x32(src + lane_addr + c * 32, a);
         tmem_ld_wait();
-        float fv[32], fk[32];
+        float f[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          fv[e] = __uint_as_float(a[e]);
-          fk[e] = __uint_as_float(d[e]) * p.scale;
-        }
+        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(a[e]) * mul;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          reinterpret_cast<bf16x8*>(p.dv + row + c * 32)[q4] = pack8(fv + q4 * 8);
-          reinterpret_cast<bf16x8*>(p.dk + row + c * 32)[q4] = pack8(fk + q4 * 8);
-        }
+        for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(dst + c * 32)[q4] = pack8(f + q4 * 8);
       }
     }
   }

@@ -171,15 +171,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(s_empty));  // S is in registers: the next Q K^T may overwrite it
       const bool diag = (j == qt);
-      float mx = -INFINITY;
+      // four independent chains for the maximum (and for the sum below): a single chain of 128 dependent operations
+      // would leave the two warps that share a scheduler stalled on instruction latency
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (diag) {
 #pragma unroll
         for (int e = 0; e < kAK; ++e)
-          if (e <= r) mx = fmaxf(mx, __uint_as_float(v[e]));
+          if (e <= r) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
       } else {
 #pragma unroll
-        for (int e = 0; e < kAK; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        for (int e = 0; e < kAK; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx * p.scale_log2);
       const bool need = (m_new - m_ref) > 8.f;  // true on the first tile (m_ref = -inf)
       if (j > 0) {  // P V(j-1) must have finished reading the P tile (and O) before either is touched
@@ -206,6 +209,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       // probabilities -> bf16 operand tile (row r, 16-byte chunk c16 stored at c16 ^ (r & 7) inside its 64-column atom)
       const float neg_m = -m_ref;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c16 = 0; c16 < kAK / 8; ++c16) {
         float pr[8];
@@ -215,11 +219,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           float pe = ex2_approx(fmaf(__uint_as_float(v[col]), p.scale_log2, neg_m));
           if (diag && col > r) pe = 0.f;
           pr[e] = pe;
-          l += pe;
+          l4[e & 3] += pe;
         }
         uint8_t* atom = sP + (c16 >> 3) * (kAQ * 128) + r * 128;
         *reinterpret_cast<bf16x8*>(atom + (((c16 & 7) ^ (r & 7)) << 4)) = pack8(pr);
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tc_fence_before();
       fence_proxy_async();  // make the P tile visible to the tensor core's shared-memory reads
       __syncwarp();

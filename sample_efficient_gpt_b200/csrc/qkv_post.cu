@@ -43,11 +43,23 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   for (int64_t it = 0; it < rounds; ++it, idx += stride) {
     const bool live = idx < total;
-    const int sub = (int)(idx % LPH);
-    const int64_t sg = live ? idx / LPH : 0;
-    const int slot = (int)(sg % nslots);
-    const int64_t t = sg / nslots;
-    const int s = (int)(t % p.S);
+    int sub, slot, s;
+    int64_t t;
+    if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values dominate otherwise
+      const uint32_t i32 = live ? (uint32_t)idx : 0u;
+      sub = (int)(i32 % LPH);
+      const uint32_t sg = i32 / LPH;
+      slot = (int)(sg % (uint32_t)nslots);
+      const uint32_t t32 = sg / (uint32_t)nslots;
+      s = (int)(t32 % (uint32_t)p.S);
+      t = t32;
+    } else {
+      sub = (int)(idx % LPH);
+      const int64_t sg = live ? idx / LPH : 0;
+      slot = (int)(sg % nslots);
+      t = sg / nslots;
+      s = (int)(t % p.S);
+    }
     float x1[8], x2[8];
     if (live) {
       const T* src = qkv + (size_t)t * nslots * HD + (size_t)slot * HD + sub * 8;
@@ -125,11 +137,23 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   for (int64_t it = 0; it < rounds; ++it, idx += stride) {
     const bool live = idx < total;
-    const int sub = (int)(idx % LPH);
-    const int64_t sg = live ? idx / LPH : 0;
-    const int slot = (int)(sg % nslots);
-    const int64_t t = sg / nslots;
-    const int s = (int)(t % p.S);
+    int sub, slot, s;
+    int64_t t;
+    if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values dominate otherwise
+      const uint32_t i32 = live ? (uint32_t)idx : 0u;
+      sub = (int)(i32 % LPH);
+      const uint32_t sg = i32 / LPH;
+      slot = (int)(sg % (uint32_t)nslots);
+      const uint32_t t32 = sg / (uint32_t)nslots;
+      s = (int)(t32 % (uint32_t)p.S);
+      t = t32;
+    } else {
+      sub = (int)(idx % LPH);
+      const int64_t sg = live ? idx / LPH : 0;
+      slot = (int)(sg % nslots);
+      t = sg / nslots;
+      s = (int)(t % p.S);
+    }
     const size_t row_off = (size_t)t * nslots * HD + (size_t)slot * HD + sub * 8;
     float x1[8], x2[8];
     if (live) {
