@@ -29,6 +29,13 @@ void check_lp(const Tensor& t, bool bf16, const char* name) {
   check_cuda(t, name);
   TORCH_CHECK(t.scalar_type() == (bf16 ? at::kBFloat16 : at::kFloat), name, " has the wrong dtype");
 }
+// [rows, cols] activations that may be a column slice of a wider buffer: unit column stride, 16-byte aligned rows.
+void check_rows(const Tensor& t, bool bf16, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2 && t.stride(1) == 1, name, " must be a CUDA matrix with unit column stride");
+  TORCH_CHECK(t.scalar_type() == (bf16 ? at::kBFloat16 : at::kFloat), name, " has the wrong dtype");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0 && (t.stride(0) * t.element_size()) % 16 == 0, name,
+              " rows must start on 16-byte boundaries");
+}
 void check_f32(const Tensor& t, const char* name) {
   check_cuda(t, name);
   TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
@@ -156,11 +163,12 @@ std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTens
                                                 const Tensor& qgain, const Tensor& a1, const Tensor& a2, const Tensor& vs, int B,
                                                 int S, int H, int Hkv, int hd, bool qknorm) {
   const bool bf16 = qkv.scalar_type() == at::kBFloat16;
-  check_lp(qkv, bf16, "qkv");
+  check_rows(qkv, bf16, "qkv");
   TORCH_CHECK(qkv.size(0) == (int64_t)B * S && qkv.size(1) == (int64_t)(H + 2 * Hkv) * hd, "qkv has the wrong shape");
   if (v1.has_value()) check_lp(*v1, bf16, "v1");
   c10::cuda::CUDAGuard guard(qkv.device());
   auto p = make_post(cos, sin, qgain, a1, a2, vs, B, S, H, Hkv, hd, qknorm);
+  p.qkv_stride = qkv.stride(0);
   Tensor q = torch::empty({B, S, H, hd}, qkv.options());
   Tensor k = torch::empty({B, S, Hkv, hd}, qkv.options());
   Tensor v = torch::empty({B, S, Hkv, hd}, qkv.options());
@@ -171,9 +179,9 @@ std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTens
 std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
     const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& qkv, const OptTensor& v1, const Tensor& cos,
     const Tensor& sin, const Tensor& qgain, const Tensor& a1, const Tensor& a2, const Tensor& vs, int B, int S, int H, int Hkv,
-    int hd, bool qknorm) {
+    int hd, bool qknorm, const OptTensor& dqkv_out) {
   const bool bf16 = qkv.scalar_type() == at::kBFloat16;
-  check_lp(qkv, bf16, "qkv");
+  check_rows(qkv, bf16, "qkv");
   check_lp(dq, bf16, "dq");
   check_lp(dk, bf16, "dk");
   check_cuda(dv, "dv");
@@ -184,7 +192,17 @@ std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
   auto p = make_post(cos, sin, qgain, a1, a2, vs, B, S, H, Hkv, hd, qknorm);
   const int64_t T = (int64_t)B * S;
   auto f32 = qkv.options().dtype(at::kFloat);
-  Tensor dqkv = torch::empty_like(qkv);
+  // dqkv shares qkv's row stride: either a fresh buffer of qkv's layout or the caller's wider one (same stride as qkv)
+  Tensor dqkv;
+  if (dqkv_out.has_value()) {
+    dqkv = *dqkv_out;
+    check_rows(dqkv, bf16, "dqkv_out");
+    TORCH_CHECK(dqkv.size(0) == qkv.size(0) && dqkv.size(1) == qkv.size(1) && dqkv.stride(0) == qkv.stride(0),
+                "dqkv_out must have qkv's shape and row stride");
+  } else {
+    dqkv = torch::empty_strided(qkv.sizes(), qkv.strides(), qkv.options());
+  }
+  p.qkv_stride = qkv.stride(0);
   OptTensor dv1;
   if (v1.has_value()) dv1 = torch::empty({B, S, Hkv, hd}, f32);
   Tensor scalars = torch::empty({4}, f32);
@@ -387,7 +405,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gate_fwd", &gate_fwd);
   m.def("gate_bwd", &gate_bwd);
   m.def("qkv_post_fwd", &qkv_post_fwd);
-  m.def("qkv_post_bwd", &qkv_post_bwd);
+  m.def("qkv_post_bwd", &qkv_post_bwd, pybind11::arg("dq"), pybind11::arg("dk"), pybind11::arg("dv"), pybind11::arg("qkv"),
+        pybind11::arg("v1"), pybind11::arg("cos"), pybind11::arg("sin"), pybind11::arg("qgain"), pybind11::arg("a1"), pybind11::arg("a2"),
+        pybind11::arg("vs"), pybind11::arg("B"), pybind11::arg("S"), pybind11::arg("H"), pybind11::arg("Hkv"), pybind11::arg("hd"),
+        pybind11::arg("qknorm"), pybind11::arg("dqkv_out") = std::nullopt);
   m.def("ce_chunk_fwd_bwd", &ce_chunk_fwd_bwd);
   m.def("adamw", &adamw);
   m.def("ema", &ema);

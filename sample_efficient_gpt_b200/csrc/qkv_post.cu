@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
     }
     float x1[8], x2[8];
     if (live) {
-      const T* src = qkv + (size_t)t * nslots * HD + (size_t)slot * HD + sub * 8;
+      const T* src = qkv + (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
       load8<T>(src, x1);
       load8<T>(src + HALF, x2);
     }
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
       t = sg / nslots;
       s = (int)(t % p.S);
     }
-    const size_t row_off = (size_t)t * nslots * HD + (size_t)slot * HD + sub * 8;
+    const size_t row_off = (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
     float x1[8], x2[8];
     if (live) {
       load8<T>(qkv + row_off, x1);

@@ -91,11 +91,17 @@ def qkv_post_fwd(qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qkn
     return ref.qkv_post_fwd(qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm)
 
 
-def qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm):
+def qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm, dqkv_out=None):
+    """``qkv`` may be a column slice of a wider projection output; ``dqkv_out`` (same shape and row stride as ``qkv``)
+    receives the gradient in place of a fresh buffer."""
     if _use_cuda(qkv, "qkv_post_bwd"):
         _count(2)
-        return ext().qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm)
-    return ref.qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm)
+        return ext().qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm, dqkv_out)
+    out = ref.qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm)
+    if dqkv_out is not None:
+        dqkv_out.copy_(out[0])
+        out = (dqkv_out, *out[1:])
+    return out
 
 
 # ----------------------------------------------------------------------------- attention

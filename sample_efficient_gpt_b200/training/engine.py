@@ -47,7 +47,7 @@ def engine_supports(model: Transformer) -> bool:
 
 
 class FusedEngine:
-    def __init__(self, model: Transformer, act_dtype: torch.dtype = torch.bfloat16, moe_exchange=None):
+    def __init__(self, model: Transformer, act_dtype: torch.dtype = torch.bfloat16, moe_exchange=None, fuse_gate: bool | None = None):
         if not engine_supports(model):
             raise ValueError("FusedEngine: gating in {False, 'per-head'} and either all-dense or all-MoE blocks only")
         self.model = model
@@ -62,6 +62,22 @@ class FusedEngine:
         self.H, self.Hkv, self.hd = at.n_heads, at.n_kv_heads, at.head_dim
         self._ones = torch.ones(1, dtype=torch.float32, device=model.embedding.weight.device)
         self._loss_coef = 1.0
+        # The per-head gate projection ([d] -> [H], e.g. 1152 -> 18) is far too narrow for a GEMM of its own: its weight
+        # rows are appended to the qkv weight (in the low-precision shadow, padded to a multiple of 8 rows), so that the
+        # gate logits, their data gradient and their weight gradient ride along with the qkv GEMMs.
+        self.fuse_gate = (act_dtype != torch.float32) if fuse_gate is None else fuse_gate
+        self.qkvz_w: dict[int, Tensor] = {}
+        self._wg_tmp: Tensor | None = None
+        if self.fuse_gate and at.gating == "per-head":
+            for i, blk in enumerate(model.blocks):
+                wq, wg = blk.attn.qkv.linear.weight, blk.attn.attn_gate.linear.weight
+                n_qkv, H = wq.size(0), wg.size(0)
+                n_ext = (n_qkv + H + 7) // 8 * 8
+                cat = torch.zeros((n_ext, wq.size(1)), dtype=act_dtype, device=wq.device)
+                cat[:n_qkv].copy_(wq.detach())
+                cat[n_qkv : n_qkv + H].copy_(wg.detach())
+                self.qkvz_w[i] = cat
+                self.shadows[wq], self.shadows[wg] = cat[:n_qkv], cat[n_qkv : n_qkv + H]
         self.moe = None
         if model.blocks[0].is_moe:
             from sample_efficient_gpt_b200.training.moe_engine import MoEEngine
@@ -114,8 +130,13 @@ class FusedEngine:
         T = B * S
         scale = float(blk.ln1.position_scale)
         x, n1, rstd1, kurt = ops.add_rmsnorm_fwd(res, delta, blk.ln1.gain, scale, blk.ln1.eps, self.lp, want_kurt)
-        qkv = ops.matmul_nt(n1, self._w(at.qkv.linear.weight))
-        z = ops.matmul_nt(n1, self._w(at.attn_gate.linear.weight)) if at.gating else None
+        if i in self.qkvz_w:
+            n_qkv = at.qkv.linear.weight.size(0)
+            qkvz = ops.matmul_nt(n1, self.qkvz_w[i])
+            qkv, z = qkvz[:, :n_qkv], qkvz[:, n_qkv : n_qkv + H].contiguous()
+        else:
+            qkv = ops.matmul_nt(n1, self._w(at.qkv.linear.weight))
+            z = ops.matmul_nt(n1, self._w(at.attn_gate.linear.weight)) if at.gating else None
         qgain = at.sdpa_qknorm.gain if at.qknorm else self._ones
         q, k, v = ops.qkv_post_fwd(
             qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm
@@ -165,8 +186,17 @@ class FusedEngine:
         if i == 0 and dv1_acc is not None:
             dv = dv.float() + dv1_acc
         qgain = at.sdpa_qknorm.gain if at.qknorm else self._ones
+        fused = i in self.qkvz_w
+        dqkvz = None
+        if fused:  # [dqkv | dz | zero padding], the layout of the fused projection's output
+            n_qkv, n_ext = w_qkv.size(0), self.qkvz_w[i].size(0)
+            dqkvz = torch.empty((T, n_ext), dtype=qkv.dtype, device=qkv.device)
+            dqkvz[:, n_qkv : n_qkv + H] = dz
+            if n_ext > n_qkv + H:
+                dqkvz[:, n_qkv + H :] = 0
         dqkv, dv1, dqg, da1, da2, dvs = ops.qkv_post_bwd(
-            dq, dk, dv, qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm
+            dq, dk, dv, qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm,
+            dqkv_out=dqkvz[:, :n_qkv] if fused else None,
         )
         if dv1 is not None:
             dv1_acc = dv1 if dv1_acc is None else dv1_acc.add_(dv1)
@@ -176,12 +206,21 @@ class FusedEngine:
             self._acc(at.alpha1, da1)
             self._acc(at.alpha2, da2)
             self._acc(at.scale, dvs)
-        dn1 = ops.matmul_nn(dqkv, self._w(w_qkv))
-        self._wgrad(w_qkv, dqkv, n1)
-        if at.gating:
+        if fused:
             w_gate = at.attn_gate.linear.weight
-            dn1.addmm_(dz, self._w(w_gate))
-            self._wgrad(w_gate, dz, n1)
+            dn1 = ops.matmul_nn(dqkvz, self.qkvz_w[i])
+            if self._wg_tmp is None or self._wg_tmp.shape != (n_ext, w_qkv.size(1)):
+                self._wg_tmp = torch.empty((n_ext, w_qkv.size(1)), dtype=torch.float32, device=qkv.device)
+            ops.wgrad_accumulate(self._wg_tmp, dqkvz, n1, True)
+            self._acc(w_qkv, self._wg_tmp[:n_qkv])
+            self._acc(w_gate, self._wg_tmp[n_qkv : n_qkv + H])
+        else:
+            dn1 = ops.matmul_nn(dqkv, self._w(w_qkv))
+            self._wgrad(w_qkv, dqkv, n1)
+            if at.gating:
+                w_gate = at.attn_gate.linear.weight
+                dn1.addmm_(dz, self._w(w_gate))
+                self._wgrad(w_gate, dz, n1)
         dx, dx_lp, dgain1 = ops.add_rmsnorm_bwd(dn1, dy, x, blk.ln1.gain, rstd1, scale, self.lp)
         self._acc(blk.ln1.gain, dgain1)
         if self.grad_ready is not None:

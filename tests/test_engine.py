@@ -50,6 +50,28 @@ def test_engine_gradients_match_autograd(kw):
     assert float(ev.loss) == pytest.approx(float(loss), rel=1e-5)
 
 
+def test_engine_fused_gate_projection_matches_autograd():
+    """qkv and gate projections as one GEMM (gate rows appended to the qkv weight, strided qkv view, [dqkv | dz] gradient)."""
+    m = _model()
+    ids = torch.randint(0, 300, (2, 33))
+    tg = torch.randint(0, 300, (2, 33))
+    logits, _ = m(ids)
+    loss, _, _ = efficient_cross_entropy(logits, tg)
+    loss.backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters()}
+    for p in m.parameters():
+        p.grad = None
+    eng = FusedEngine(m, torch.float32, fuse_gate=True)
+    assert len(eng.qkvz_w) == 3 and eng.qkvz_w[0].size(0) % 8 == 0
+    out = eng.forward_backward(ids, tg, 1.0)
+    assert float(out.loss) == pytest.approx(float(loss), rel=1e-5)
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, want[n], rtol=2e-3, atol=1e-6 + 1e-4 * float(want[n].abs().max())), n
+    eng.forward_backward(ids, tg, 1.0, first_micro_step=False)
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, 2 * want[n], rtol=2e-3, atol=1e-6 + 2e-4 * float(want[n].abs().max())), n
+
+
 def test_engine_rejects_unsupported_models():
     m = _model(attn_gating="elementwise")
     assert not engine_supports(m)
