@@ -5,6 +5,9 @@ evals/chat_web.py:89-110).
 * ``StaticKVCache``: keys/values in buffers allocated once for ``max_len`` positions and written in place - a decode
   step appends one column instead of re-concatenating the whole cache.
 * ``SamplingParams``: n, max_tokens, temperature, top_k, top_p, stop_token_ids (the subset of vLLM's the evaluations use).
+* ``GraphDecoder``: the one-token decode step of a dense model as a CUDA graph over static buffers (token, position,
+  per-layer K/V caches of ``max_len`` positions, a position mask): the ~12 small kernels per layer of a decode step are
+  launch-bound, a graph replay issues them in one call.  The prompt is prefilled eagerly into the same buffers.
 * ``ChatEngine``: renders conversations (tokenizer chat template, else the ``<|user_start|>...`` special-token format,
   else a plain-text fallback), runs prompts of equal length as one batch (the model has no padding mask), samples on the
   device, and checks for "all rows finished" every few steps so the decode loop does not synchronise per token.
@@ -38,8 +41,9 @@ class StaticKVCache(KVCache):
     def append(self, k: Tensor, v: Tensor):
         if self._k is None:
             b, h, _, d = k.shape
-            self._k = k.new_empty(b, h, self.max_len, d)
-            self._v = v.new_empty(b, h, self.max_len, d)
+            # zero-filled: positions beyond the current length are masked in attention, but 0 x NaN would still poison it
+            self._k = k.new_zeros(b, h, self.max_len, d)
+            self._v = v.new_zeros(b, h, self.max_len, d)
         s = k.size(2)
         if self._n + s > self.max_len:
             raise ValueError(f"KV cache overflow: {self._n}+{s} > {self.max_len}")
@@ -48,6 +52,99 @@ class StaticKVCache(KVCache):
         self._n += s
         self.keys, self.values = self._k[:, :, : self._n], self._v[:, :, : self._n]
         return self.keys, self.values
+
+
+class GraphDecoder:
+    """Static-shape decode step ``(token [B,1], position) -> logits [B,V]`` captured in a CUDA graph.
+
+    Follows models/attention.py (rotated keys and un-mixed values are cached; value mix, QK-norm and gate are applied at
+    use) with every shape fixed: the new key/value are written at ``pos`` with ``index_copy_``, attention runs over all
+    ``max_len`` cached positions under the mask ``arange(max_len) <= pos``.  Dense blocks only.
+    """
+
+    def __init__(self, model, batch: int, max_len: int, device, autocast):
+        import torch.nn.functional as F
+
+        self.model, self.B, self.max_len, self.device, self.autocast, self.F = model, batch, max_len, torch.device(device), autocast, F
+        at = model.blocks[0].attn
+        if any(b.is_moe for b in model.blocks) or at.gating not in (False, "per-head"):
+            raise ValueError("graph decode supports dense blocks with per-head (or no) gating")
+        self.caches = [StaticKVCache(max_len) for _ in range(model.n_layers)]
+        self.token = torch.zeros(batch, 1, dtype=torch.long, device=self.device)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.arange = torch.arange(max_len, device=self.device)
+        self.logits: Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+
+    def reset(self):
+        for c in self.caches:
+            c._n = 0
+            c.keys = c.values = None
+
+    def _step(self) -> Tensor:
+        from sample_efficient_gpt_b200.models.rope import apply_rope
+
+        F, model, pos = self.F, self.model, self.pos
+        mask = (self.arange <= pos).view(1, 1, 1, self.max_len)
+        x = model.embedding(self.token)
+        v1 = None
+        for blk, cache in zip(model.blocks, self.caches):
+            at = blk.attn
+            b, h, hkv, hd = self.B, at.n_heads, at.n_kv_heads, at.head_dim
+            n1 = blk.ln1(x)
+            q, k, v = at.qkv(n1).split((h * hd, hkv * hd, hkv * hd), dim=-1)
+            q = q.view(b, 1, h, hd).transpose(1, 2)
+            k = k.view(b, 1, hkv, hd).transpose(1, 2)
+            v = v.view(b, 1, hkv, hd).transpose(1, 2)
+            cos, sin = at.rope.cos.index_select(0, pos), at.rope.sin.index_select(0, pos)
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            cache._k.index_copy_(2, pos, k.to(cache._k.dtype))
+            cache._v.index_copy_(2, pos, v.to(cache._v.dtype))
+            kf, vf = cache._k, cache._v
+            vm = at.mix_values(vf, vf if v1 is None else v1)
+            if v1 is None:
+                v1 = vm
+            if at.qknorm:
+                q, kf = at.sdpa_qknorm.normalize(q, kf.to(q.dtype))
+            o = F.scaled_dot_product_attention(q, kf.to(q.dtype), vm.to(q.dtype), attn_mask=mask, enable_gqa=True).transpose(1, 2)
+            if at.gating:
+                o = (2.0 * at.attn_gate(n1).sigmoid()).unsqueeze(-1) * o
+            y = x + at.out(o.reshape(b, 1, h * hd))
+            x = y + blk.ffn(blk.ln2(y))
+        logits = model.lm_head(model.final_norm(x))[:, -1, :]
+        return logits * model.output_mult if model.output_mult != 1.0 else logits
+
+    @torch.inference_mode()
+    def prefill(self, prompt: Tensor) -> Tensor:
+        """Eager forward of the prompt [B,S] into the static caches; returns the last position's logits."""
+        self.reset()
+        with self.autocast:
+            logits, _ = self.model(prompt, kv_cache=self.caches)
+        self.pos.fill_(prompt.size(1))
+        return logits[:, -1, :]
+
+    @torch.inference_mode()
+    def step(self, tokens: Tensor) -> Tensor:
+        """Feed one token per row at the current position; returns logits [B,V] (a static buffer) and advances."""
+        self.token.copy_(tokens.view(self.B, 1))
+        if self.device.type != "cuda":  # no graphs on the CPU: the same static-shape step, eagerly
+            with self.autocast:
+                self.logits = self._step()
+            self.pos.add_(1)
+            return self.logits
+        if self.graph is None:
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side), self.autocast:  # warm-up outside the capture (lazy initialisations, autotuning)
+                for _ in range(2):
+                    self._step()
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph), self.autocast:
+                self.logits = self._step()
+        self.graph.replay()
+        self.pos.add_(1)
+        return self.logits
 
 
 @dataclass
@@ -89,12 +186,15 @@ def _message_text(content) -> str:
 
 class ChatEngine:
     def __init__(self, model, tokenizer, device="cpu", max_model_len: int = 2048, chat_template: str | None = None,
-                 dtype: torch.dtype | None = None, sync_every: int = 16):
+                 dtype: torch.dtype | None = None, sync_every: int = 16, cuda_graphs: bool | None = None):
         self.model, self.tokenizer, self.device = model.to(device).eval(), tokenizer, torch.device(device)
         self.max_model_len, self.chat_template, self.sync_every = max_model_len, chat_template, sync_every
         self.autocast = (torch.autocast("cuda", dtype=dtype or torch.bfloat16) if self.device.type == "cuda" else nullcontext())
         vocab = tokenizer.get_vocab() if hasattr(tokenizer, "get_vocab") else {}
         self._special = {t: vocab[t] for t in SPECIAL_FORMAT if t in vocab}
+        dense = not any(b.is_moe for b in self.model.blocks) and self.model.blocks[0].attn.gating in (False, "per-head")
+        self.cuda_graphs = (self.device.type == "cuda" and dense) if cuda_graphs is None else (cuda_graphs and self.device.type == "cuda")
+        self._decoders: dict[int, GraphDecoder] = {}  # batch size -> decoder (caches for max_model_len positions)
 
     # ---- prompt rendering -------------------------------------------------------------------------------------------
     def render(self, messages: list[dict]) -> list[int]:
@@ -128,15 +228,24 @@ class ChatEngine:
         budget = min(p.max_tokens, self.max_model_len - S)
         if budget <= 0:
             return [[] for _ in range(B)]
-        caches = [StaticKVCache(S + budget) for _ in range(self.model.n_layers)]
         stop = torch.tensor(sorted(set(p.stop_token_ids)), device=self.device, dtype=torch.long)
         out = torch.zeros(B, budget, dtype=torch.long, device=self.device)
         done = torch.zeros(B, dtype=torch.bool, device=self.device)
         step_in, steps = prompt, 0
+        decoder = None
+        if self.cuda_graphs:
+            decoder = self._decoders.get(B)
+            if decoder is None:
+                decoder = self._decoders[B] = GraphDecoder(self.model, B, self.max_model_len, self.device, self.autocast)
+        else:
+            caches = [StaticKVCache(S + budget) for _ in range(self.model.n_layers)]
         with self.autocast:
             for t in range(budget):
-                logits, _ = self.model(step_in, kv_cache=caches)
-                nxt = sample_next(logits[:, -1, :], p, gen)
+                if decoder is not None:
+                    last = decoder.prefill(prompt) if t == 0 else decoder.step(step_in)
+                else:
+                    last = self.model(step_in, kv_cache=caches)[0][:, -1, :]
+                nxt = sample_next(last, p, gen)
                 if stop.numel():
                     done = done | torch.isin(nxt, stop)
                 out[:, t] = torch.where(done, torch.full_like(nxt, -1), nxt)

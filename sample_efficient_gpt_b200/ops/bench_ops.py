@@ -5,6 +5,7 @@
   python -m sample_efficient_gpt_b200.ops.bench_ops --op attention --seq 2048        (B 8, 18q/6kv heads of 64, fwd+bwd)
   python -m sample_efficient_gpt_b200.ops.bench_ops --op linear_ce                    ([32768,1152] x [49152,1152])
   python -m sample_efficient_gpt_b200.ops.bench_ops --op elementwise                  (norms, SwiGLU, qkv post-processing, gate, AdamW, EMA)
+  python -m sample_efficient_gpt_b200.ops.bench_ops --op decode                       (generation: eager vs CUDA-graph decode step)
   python -m sample_efficient_gpt_b200.ops.bench_ops --op moe                          (router, dispatch, combine, router backward)
 Each line reports milliseconds, achieved TFLOP/s or GB/s, and the library call it replaces where there is one.
 """
@@ -234,9 +235,45 @@ def bench_moe(a):
     report(rows, a.iters)
 
 
+def bench_decode(a):
+    """Tokens per second of the one-token decode step of IMU-1 430M (random init, bf16), eager KV-cache decode against the
+    CUDA-graph replay of the same step; the prompt is 128 tokens, 128 tokens are generated."""
+    import time
+
+    from sample_efficient_gpt_b200.evals.generation import ChatEngine, SamplingParams
+    from sample_efficient_gpt_b200.models import build_model
+    from sample_efficient_gpt_b200.utils.config_tools import load_cfg
+
+    cfg = load_cfg("imu1_base.yaml", "stable")
+    model = build_model(cfg.model).cuda().eval()
+
+    class Tok:
+        eos_token_id = None
+        chat_template = None
+
+        def get_vocab(self):
+            return {}
+
+    for batch in (1, 8):
+        prompts = [[(7 * i + j) % 1000 + 10 for j in range(128)] for i in range(batch)]
+        row = {"op": "decode", "batch": batch, "new_tokens": 128}
+        for name, graphs in (("eager", False), ("cuda_graph", True)):
+            eng = ChatEngine(model, Tok(), "cuda", max_model_len=512, cuda_graphs=graphs)
+            p = SamplingParams(max_tokens=128, temperature=0.0)
+            eng.generate_ids([list(x) for x in prompts], p)  # warm-up (and graph capture)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.generate_ids([list(x) for x in prompts], p)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            row[f"{name}_ms_per_token"] = dt / 128 * 1e3
+            row[f"{name}_tokens_per_s"] = batch * 128 / dt
+        print(json.dumps(row))
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe"])
+    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe", "decode"])
     p.add_argument("--m", type=int, default=8192)
     p.add_argument("--n", type=int, default=1920)
     p.add_argument("--k", type=int, default=1152)
@@ -247,7 +284,7 @@ def main():
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--iters", type=int, default=10)
     a = p.parse_args()
-    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe}[a.op](a)
+    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe, "decode": bench_decode}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -234,6 +234,27 @@ def test_static_cache_matches_full_forward():
         assert rows[0] == ids[len(p):]
 
 
+def test_static_decode_step_matches_full_forward():
+    """The fixed-shape decode step (what the CUDA graph captures) against re-running the whole sequence."""
+    from contextlib import nullcontext
+
+    from sample_efficient_gpt_b200.evals.generation import GraphDecoder
+
+    model = tiny_model()
+    dec = GraphDecoder(model, 2, 24, "cpu", nullcontext())
+    prompt = torch.tensor([[3, 4, 5, 6], [7, 8, 9, 10]])
+    ids = prompt.clone()
+    logits = dec.prefill(prompt)
+    for _ in range(5):
+        want, _ = model(ids)
+        assert torch.allclose(logits, want[:, -1, :], atol=2e-4, rtol=1e-4)
+        nxt = logits.argmax(-1, keepdim=True)
+        ids = torch.cat([ids, nxt], dim=1)
+        logits = dec.step(nxt)
+    dec.prefill(prompt[:, :2])  # reuse of the same buffers for a shorter prompt: stale entries are masked
+    assert torch.allclose(dec.step(prompt[:, 2:3]), model(prompt[:, :3])[0][:, -1, :], atol=2e-4, rtol=1e-4)
+
+
 def test_sampling_rules_and_stop_tokens():
     logits = torch.tensor([[0.0, 1.0, 5.0, 2.0]])
     assert int(sample_next(logits, SamplingParams(temperature=0.0))) == 2
