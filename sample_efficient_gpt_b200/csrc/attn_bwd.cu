@@ -12,7 +12,8 @@
 //   dV  += P^T  dO   (A K-major,  B = dO as MN-major operand, accumulates in TMEM over the whole walk)
 //   dK  += dS^T Q    (same shapes, accumulates in TMEM over the whole walk)
 //   dQ_i = dS  K     (A = the dS^T tile read as an MN-major operand, B = K as MN-major; fresh accumulator per tile,
-//                     drained with vector atomic adds into an fp32 dQ buffer because other key tiles add to the same rows)
+//                     drained through swizzled shared-memory boxes and TMA reductions (cp.reduce.async.bulk.tensor ... add)
+//                     into an fp32 dQ buffer because other key tiles add to the same rows)
 // TMEM: S^T 128 + dP^T 128 + dV 64 + dK 64 + dQ 64 = 448 of 512 columns, one CTA per SM.
 // Roles (320 threads): warp 0 TMA producer (K/V once; Q and dO tiles through a 2-stage ring; 4-D tensor maps, no
 // multicast), warp 1 MMA issuer, warps 2-9 the element-wise stage (a key row and half of the query columns per thread); lse and D of the step's queries travel with the tiles as bulk copies.
@@ -34,7 +35,8 @@ constexpr int kBHD = 64;   // head dim
 constexpr int kBwdThreads = 320;  // producer warp, MMA warp, 8 element-wise warps
 constexpr int kBTile = kBT * kBHD * 2;   // 16 KB: one K, V, Q or dO tile
 constexpr int kBPds = kBT * kBT * 2;     // 32 KB: P^T or dS^T (two 64-column atoms)
-constexpr int kBwdSmem = 2 * kBTile /*K,V*/ + 2 * 2 * kBTile /*Q,dO x 2 stages*/ + 2 * kBPds + 2 * 2 * kBT * 4 /*lse2, D x 2*/ + 256 + 1024;
+constexpr int kBDq = 8 * 32 * 32 * 4;     // 32 KB: one 32-row x 32-column fp32 box of dQ per element-wise warp
+constexpr int kBwdSmem = 2 * kBTile /*K,V*/ + 2 * 2 * kBTile /*Q,dO x 2 stages*/ + 2 * kBPds + kBDq + 2 * 2 * kBT * 4 /*lse2, D x 2*/ + 256 + 1024;
 
 struct AttnBwdParams {
   int B, S, H, Hkv;
@@ -59,13 +61,20 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+// TMA reduction: global[box at coords] += shared box (fp32 add, element type and swizzle from the tensor map).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                const __grid_constant__ CUtensorMap map_dq, AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -73,7 +82,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint8_t* sQdO = sV + kBTile;            // stage s: Q at s*32K, dO at s*32K + 16K
   uint8_t* sP = sQdO + 4 * kBTile;
   uint8_t* sDS = sP + kBPds;
-  float* sLse = reinterpret_cast<float*>(sDS + kBPds);  // [2][128]
+  uint8_t* sDQ = sDS + kBPds;  // [8 warps][32 rows][128 B], 128-byte swizzled boxes of the dQ tile
+  float* sLse = reinterpret_cast<float*>(sDQ + kBDq);  // [2][128]
   float* sD = sLse + 2 * kBT;                            // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sD + 2 * kBT);
   uint64_t* kv_full = bars;
@@ -110,6 +120,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
     prefetch_tensormap(&map_do);
+    prefetch_tensormap(&map_dq);
   }
   if (warp == 0) {
     __syncwarp();
@@ -244,15 +255,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // works on the next S^T / dP^T
       if (!mbar_wait(smem_u32(mma_done), n & 1, ab, 27)) { ok = false; break; }
       tc_fence_after();
-      float* dq_row = p.dq_acc + (((size_t)b * p.S + (size_t)it * kBT + r) * p.H + h) * kBHD + half * 32;
+      // This warp's 32 rows x 32 columns of dQ: TMEM -> registers -> its swizzled 4 KB box in shared memory -> one TMA
+      // reduction into the fp32 accumulator (other key tiles add to the same rows).
       {
+        uint8_t* box = sDQ + (warp - 2) * 4096;
+        if (n > 0) {  // the previous step's reduction must have read the box
+          if (lane == 0) bulk_wait_read0();
+          __syncwarp();
+        }
         uint32_t qv[32];
         tmem_ld_32x32(tm_dq + lane_addr + half * 32, qv);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          red_add_v4(dq_row + e, __uint_as_float(qv[e]) * p.scale, __uint_as_float(qv[e + 1]) * p.scale,
-                     __uint_as_float(qv[e + 2]) * p.scale, __uint_as_float(qv[e + 3]) * p.scale);
+        for (int c = 0; c < 8; ++c) {
+          const float4 f = make_float4(__uint_as_float(qv[c * 4]) * p.scale, __uint_as_float(qv[c * 4 + 1]) * p.scale,
+                                       __uint_as_float(qv[c * 4 + 2]) * p.scale, __uint_as_float(qv[c * 4 + 3]) * p.scale);
+          *reinterpret_cast<float4*>(box + lane * 128 + ((c ^ (lane & 7)) << 4)) = f;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_4d(&map_dq, smem_u32(box), half * 32, h, it * kBT + sub * 32, b);
+          bulk_commit();
+        }
       }
       tc_fence_before();
     }
@@ -277,6 +302,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   }
 
+  if (warp >= 2 && lane == 0) bulk_wait0();  // outstanding dQ reductions of this warp are complete before the CTA ends
   if (*cta_abort != 0) {
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
   }
@@ -339,11 +365,32 @@ static int make_map_bshd_b(CUtensorMap* map, const void* base, int B, int S, int
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+static int make_map_dq_acc(CUtensorMap* map, const float* base, int B, int S, int H, int hd) {
+  static EncodeTiledFnB fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return -1;
+    fn = reinterpret_cast<EncodeTiledFnB>(ptr);
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)hd * 4, (cuuint64_t)H * hd * 4, (cuuint64_t)S * H * hd * 4};
+  cuuint32_t box[4] = {32, 1, 32, 1};  // 32 fp32 = 128 bytes: one swizzle row
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 int attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
              float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st) {
   if (hd != kBHD || S % kBT != 0 || H % Hkv != 0) return -10;
-  CUtensorMap mq, mk, mv, mdo;
-  int r = make_map_bshd_b(&mq, q, B, S, H, hd);
+  CUtensorMap mq, mk, mv, mdo, mdq;
+  int r = make_map_dq_acc(&mdq, dq_acc, B, S, H, hd);
+  if (r == 0) r = make_map_bshd_b(&mq, q, B, S, H, hd);
   if (r == 0) r = make_map_bshd_b(&mk, k, B, S, Hkv, hd);
   if (r == 0) r = make_map_bshd_b(&mv, v, B, S, Hkv, hd);
   if (r == 0) r = make_map_bshd_b(&mdo, d_o, B, S, H, hd);
@@ -369,7 +416,7 @@ int attn_bwd(const void* q, const void* k, const void* v, const void* o, const v
   p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = status;
   dim3 grid(S / kBT, B * Hkv);
-  attn_bwd_kernel<<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, p);
+  attn_bwd_kernel<<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, p);
   attn_bwd_finish_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n / 8);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
