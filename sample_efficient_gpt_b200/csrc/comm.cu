@@ -77,9 +77,11 @@ __device__ __forceinline__ void multimem_st_bf16x8(void* mc_ptr, const uint32_t*
 }
 
 // n is padded by the host so that n % (world * 8) == 0; slice = n / world elements.
+// sq_out (optional): += sum of squares of the reduced values of this rank's slice (the gradient norm then needs only a
+// sum of one scalar per rank instead of a pass over every gradient tensor).
 __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict__ grads, CommPeers pe, void* mc_base,
                                                              int64_t wire_off, int64_t n, int rank, int world, uint32_t seq,
-                                                             int* status) {
+                                                             int* status, float* __restrict__ sq_out) {
   const int64_t slice = n / world;
   const int nb = gridDim.x;
   // sub-slice b of a slice, in units of 8 elements
@@ -105,6 +107,7 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
   if (!block_barrier(pe, rank, world, seq, status)) return;
 
   // B: reduce my slice, push the result to everyone
+  float sq = 0.f;
   {
     const int64_t base = (int64_t)rank * slice;
     if (mc_base != nullptr) {
@@ -122,6 +125,8 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
             float f[8];
             unpack8(*reinterpret_cast<const bf16x8*>(r[u]), f);
             store8<float>(grads + base + vv * 8, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sq = fmaf(f[j], f[j], sq);
           }
       }
     } else {
@@ -149,11 +154,18 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
         unpack8(out, fin);  // every rank ends with the same bf16-rounded value
         store8<float>(grads + base + v * 8, fin);
 #pragma unroll
+        for (int j = 0; j < 8; ++j) sq = fmaf(fin[j], fin[j], sq);
+#pragma unroll
         for (int p = 0; p < kMaxRanks; ++p)
           if (p < world && p != rank)
             *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(pe.buf[p]) + wire_off + base + v * 8) = out;
       }
     }
+  }
+  if (sq_out != nullptr) {
+    __shared__ float red_s[32];
+    const float total = block_sum(sq, red_s);
+    if (threadIdx.x == 0) atomicAdd(sq_out, total);
   }
   if (!block_barrier(pe, rank, world, seq + 1, status)) return;
 
@@ -202,9 +214,9 @@ static CommPeers make_peers(void* const* bufs, uint32_t* const* flags, int world
 }
 
 void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
-                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st) {
+                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st, float* sq_out) {
   allreduce_bucket_kernel<<<blocks, 512, 0, st>>>(grads, make_peers(wire_bufs, flags, world), mc_base, wire_off, n, rank, world, seq,
-                                                  status);
+                                                  status, sq_out);
 }
 
 void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,

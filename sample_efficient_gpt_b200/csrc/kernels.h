@@ -75,8 +75,10 @@ constexpr int kCommMaxBlocks = 128;  // flag words per rank = kCommMaxBlocks * k
 // grads: this rank's fp32 bucket (n elements, n % (world*8) == 0), reduced in place across ranks with bf16 on the wire.
 // wire_bufs[p] / flags[p]: peer-mapped wire buffer and flag array of rank p; wire_off: element offset of the bucket in the
 // wire buffers; mc_base: NVLS multicast address of the wire buffer or null; seq: first of two consecutive barrier numbers.
+// sq_out (optional, fp32 scalar): += sum of squares of the reduced slice this rank owns.
 void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
-                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st);
+                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st,
+                           float* sq_out = nullptr);
 // bufs[p] + off_bytes holds `world` chunks of chunk_bytes (multiple of 16); chunk `rank` is valid on entry, all on exit.
 void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,
                     uint32_t seq, int blocks, int* status, cudaStream_t st);

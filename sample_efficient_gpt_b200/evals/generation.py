@@ -57,9 +57,8 @@ class StaticKVCache(KVCache):
 class GraphDecoder:
     """Static-shape decode step ``(token [B,1], position) -> logits [B,V]`` captured in a CUDA graph.
 
-    Follows models/attention.py (rotated keys and un-mixed values are cached; value mix, QK-norm and gate are applied at
-    use) with every shape fixed: the new key/value are written at ``pos`` with ``index_copy_``, attention runs over all
-    ``max_len`` cached positions under the mask ``arange(max_len) <= pos``.  Dense blocks only.
+    Same math as models/attention.py with every shape fixed: the new key/value are written at ``pos`` with ``index_copy_``,
+    attention runs over all ``max_len`` cached positions under the mask ``arange(max_len) <= pos``.  Dense blocks only.
     """
 
     def __init__(self, model, batch: int, max_len: int, device, autocast):
@@ -82,6 +81,8 @@ class GraphDecoder:
             c.keys = c.values = None
 
     def _step(self) -> Tensor:
+        """The caches hold *finished* keys and values (rotated + QK-normalised keys, mixed values): per position these
+        transformations do not depend on later tokens, so they are applied once, when a position is written."""
         from sample_efficient_gpt_b200.models.rope import apply_rope
 
         F, model, pos = self.F, self.model, self.pos
@@ -98,15 +99,14 @@ class GraphDecoder:
             v = v.view(b, 1, hkv, hd).transpose(1, 2)
             cos, sin = at.rope.cos.index_select(0, pos), at.rope.sin.index_select(0, pos)
             q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-            cache._k.index_copy_(2, pos, k.to(cache._k.dtype))
-            cache._v.index_copy_(2, pos, v.to(cache._v.dtype))
-            kf, vf = cache._k, cache._v
-            vm = at.mix_values(vf, vf if v1 is None else v1)
+            vm = at.mix_values(v, v if v1 is None else v1)
             if v1 is None:
                 v1 = vm
             if at.qknorm:
-                q, kf = at.sdpa_qknorm.normalize(q, kf.to(q.dtype))
-            o = F.scaled_dot_product_attention(q, kf.to(q.dtype), vm.to(q.dtype), attn_mask=mask, enable_gqa=True).transpose(1, 2)
+                q, k = at.sdpa_qknorm.normalize(q, k)
+            cache._k.index_copy_(2, pos, k.to(cache._k.dtype))
+            cache._v.index_copy_(2, pos, vm.to(cache._v.dtype))
+            o = F.scaled_dot_product_attention(q, cache._k.to(q.dtype), cache._v.to(q.dtype), attn_mask=mask, enable_gqa=True).transpose(1, 2)
             if at.gating:
                 o = (2.0 * at.attn_gate(n1).sigmoid()).unsqueeze(-1) * o
             y = x + at.out(o.reshape(b, 1, h * hd))
@@ -116,10 +116,23 @@ class GraphDecoder:
 
     @torch.inference_mode()
     def prefill(self, prompt: Tensor) -> Tensor:
-        """Eager forward of the prompt [B,S] into the static caches; returns the last position's logits."""
+        """Eager forward of the prompt [B,S] into the static caches (raw: rotated keys, un-mixed values, as the model's own
+        KV cache keeps them), then one pass that finishes them in place; returns the last position's logits."""
         self.reset()
         with self.autocast:
             logits, _ = self.model(prompt, kv_cache=self.caches)
+            S = prompt.size(1)
+            v1 = None
+            for blk, cache in zip(self.model.blocks, self.caches):
+                at = blk.attn
+                raw_v = cache._v[:, :, :S]
+                vm = at.mix_values(raw_v, raw_v if v1 is None else v1)
+                if v1 is None:
+                    v1 = vm.clone()
+                cache._v[:, :, :S] = vm.to(cache._v.dtype)
+                if at.qknorm:
+                    kk = cache._k[:, :, :S]
+                    cache._k[:, :, :S] = at.sdpa_qknorm.normalize(kk, kk)[1].to(cache._k.dtype)
         self.pos.fill_(prompt.size(1))
         return logits[:, -1, :]
 
@@ -186,10 +199,14 @@ def _message_text(content) -> str:
 
 class ChatEngine:
     def __init__(self, model, tokenizer, device="cpu", max_model_len: int = 2048, chat_template: str | None = None,
-                 dtype: torch.dtype | None = None, sync_every: int = 16, cuda_graphs: bool | None = None):
+                 dtype: torch.dtype | None = None, sync_every: int = 16, cuda_graphs: bool | None = None, cast_weights: bool = False):
         self.model, self.tokenizer, self.device = model.to(device).eval(), tokenizer, torch.device(device)
         self.max_model_len, self.chat_template, self.sync_every = max_model_len, chat_template, sync_every
         self.autocast = (torch.autocast("cuda", dtype=dtype or torch.bfloat16) if self.device.type == "cuda" else nullcontext())
+        if cast_weights and self.device.type == "cuda" and (dtype or torch.bfloat16) != torch.float32:
+            # serving: keep the weights in the compute dtype instead of re-casting fp32 masters on every decode step
+            for prm in self.model.parameters():  # parameters only: the fp32 rotary tables and norm scales stay as they are
+                prm.data = prm.data.to(dtype or torch.bfloat16)
         vocab = tokenizer.get_vocab() if hasattr(tokenizer, "get_vocab") else {}
         self._special = {t: vocab[t] for t in SPECIAL_FORMAT if t in vocab}
         dense = not any(b.is_moe for b in self.model.blocks) and self.model.blocks[0].attn.gating in (False, "per-head")
@@ -337,4 +354,4 @@ def load_engine(checkpoint: str, device="cuda", dtype: str = "bfloat16", max_mod
         tr = Trainer(load_from=str(path), load_components="infer", **{"trainer.device": str(device)})
         model, tokenizer, template = tr.model, tr.tokenizer, None
     torch_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, "auto": None}[dtype]
-    return ChatEngine(model, tokenizer, device, max_model_len, template, torch_dtype)
+    return ChatEngine(model, tokenizer, device, max_model_len, template, torch_dtype, cast_weights=True)

@@ -258,7 +258,7 @@ def bench_decode(a):
         prompts = [[(7 * i + j) % 1000 + 10 for j in range(128)] for i in range(batch)]
         row = {"op": "decode", "batch": batch, "new_tokens": 128}
         for name, graphs in (("eager", False), ("cuda_graph", True)):
-            eng = ChatEngine(model, Tok(), "cuda", max_model_len=512, cuda_graphs=graphs)
+            eng = ChatEngine(model, Tok(), "cuda", max_model_len=512, cuda_graphs=graphs, cast_weights=True)
             p = SamplingParams(max_tokens=128, temperature=0.0)
             eng.generate_ids([list(x) for x in prompts], p)  # warm-up (and graph capture)
             torch.cuda.synchronize()

@@ -164,6 +164,17 @@ class DDP(nn.Module):
     def zero_grad(self, set_to_none: bool = False):
         self.flat_grads.zero_()
 
+    def reduced_grad_norm(self, extra: list[Tensor] | None = None) -> Tensor | None:
+        """Gradient norm from the partial sums of squares that the NVLink reduction kernels produced while reducing
+        (None with the torch.distributed path).  ``extra``: gradients that did not go through the buckets (rank-local
+        parameters).  Call once per step, after ``finish_gradient_synchronization``."""
+        if self.comm is None:
+            return None
+        sq = self.comm.take_grad_sq()
+        if extra:
+            sq = sq + torch.stack([n.float() ** 2 for n in torch._foreach_norm(extra)]).sum()
+        return sq.sqrt().squeeze(0)
+
     def finish_gradient_synchronization(self) -> float:
         t0 = time.monotonic()
         if self.comm is not None:

@@ -54,6 +54,8 @@ class SymmComm:
         self.flags_main, self._flags_main_hdl = self._alloc(ext.COMM_MAX_BLOCKS * ext.COMM_MAX_RANKS * 4, zero=True)
         self.flag_ptrs_main = [int(p) for p in self._flags_main_hdl.buffer_ptrs]
         self.wire = None
+        # sum of squares of the reduced gradient slices this rank owns, accumulated by the bucket kernels of one step
+        self.grad_sq = torch.zeros(1, dtype=torch.float32, device=device)
         self.bucket_ranges: list[tuple[int, int]] = []
         self.flat_grads: Tensor | None = None
 
@@ -112,12 +114,20 @@ class SymmComm:
         self.stream.wait_event(ev)
         with torch.cuda.stream(self.stream):
             ops.ext().comm_allreduce_bucket(self.flat_grads[s:e], self.wire_ptrs, self.flag_ptrs, self.mc_ptr, s, self.rank,
-                                            self.seq, self.blocks, self.status)
+                                            self.seq, self.blocks, self.status, self.grad_sq)
         ops._count()
         self.seq += 2
 
     def wait_all(self):
         torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+    def take_grad_sq(self) -> Tensor:
+        """Sum over ranks of the per-rank partial sums of squares gathered since the last call (= ||reduced gradients||^2 of
+        everything that went through ``all_reduce_bucket``); resets the accumulator.  Call after ``wait_all``."""
+        total = self.grad_sq.clone()
+        self.grad_sq.zero_()
+        dist.all_reduce(total, group=self.group)
+        return total
 
     # ------------------------------------------------------------------ all-gather
     def all_gather_inplace(self, t: Tensor, chunk_rows: int):

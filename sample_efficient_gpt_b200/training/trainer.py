@@ -452,8 +452,13 @@ class Trainer:
             params = [p for p in self.model.parameters() if p.grad is not None]
             if tc.clip_fix:
                 gnorm = clip_grad_norm_(params, tc.max_grad_norm)
-            else:
-                gnorm = grad_norm([p.grad for p in params])  # norm only: the reference's clipping never scales
+            else:  # norm only: the reference's clipping never scales
+                gnorm = None
+                if self.ddp is not None and ga == 1:
+                    local = [p.grad for n, p in self.model.named_parameters() if p.grad is not None and p not in self.ddp.param_bucket]
+                    gnorm = self.ddp.reduced_grad_norm(local)  # partial sums from inside the reduction kernels
+                if gnorm is None:
+                    gnorm = grad_norm([p.grad for p in params])
             update_ratios = [opt.step() for opt in self.optimizers]
             if self.ema is not None:
                 self.ema.maybe_update()
