@@ -65,6 +65,12 @@ struct GemmParams {
   const uint32_t* wait_flags;
   uint32_t wait_seq;
   int region_rows;
+  // Routed output (expert-parallel combine): instead of D, rows [r * route_rows, (r + 1) * route_rows) of every batch entry
+  // are stored into D_route[r] (peer-mapped buffer of rank r) at element offset
+  //   route_base + batch * route_batch_stride + (row - r * route_rows) * ldd + column.
+  void* D_route[8];
+  int route_rows;  // 0: plain output
+  int64_t route_batch_stride, route_base;
 };
 
 __device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t seq, const AbortState& ab, int code) {
@@ -241,6 +247,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
                   (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
     for (int d = 0; d < p.n_extra; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_extra[d]) & 15) == 0);
+    if (p.route_rows > 0) {
+      vec_ok = (p.ldd % 8 == 0) && ((p.route_base * sizeof(OutT)) % 16 == 0) && ((p.route_batch_stride * sizeof(OutT)) % 16 == 0);
+      for (int d = 0; d < 8; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_route[d]) & 15) == 0);
+    }
     int local_tile = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -252,6 +262,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       const int row0 = tc.m * kBM + sub * 32;  // first row of this warp's 32-row band
       const int64_t boff = (int64_t)tc.b * p.batch_stride_d;
+      // routed output: destination buffer and row offset of the 8 rows this lane stores (rows row0 + rsub + 4 i)
+      OutT* rbase[8];
+      if (p.route_rows > 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = row0 + rsub + 4 * i;
+          const int reg = r / p.route_rows;
+          rbase[i] = reinterpret_cast<OutT*>(p.D_route[reg < 8 ? reg : 7]) + p.route_base + (int64_t)tc.b * p.route_batch_stride +
+                     (int64_t)(r - reg * p.route_rows) * p.ldd;
+        }
+      }
       float4 cnext[8];
       bool have_next = false;
       auto fetch_c = [&](int col, float4* dst) {  // coalesced read of C[row0 + rsub + 4i, col + 4q .. +4)
@@ -307,8 +328,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (C != nullptr) {
                   f.x += p.beta * ccur[i].x; f.y += p.beta * ccur[i].y; f.z += p.beta * ccur[i].z; f.w += p.beta * ccur[i].w;
                 }
-                store4<OutT>(D + off, f);
-                for (int d = 0; d < p.n_extra; ++d) store4<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + off, f);
+                if (p.route_rows > 0) {
+                  store4<OutT>(rbase[i] + col + 4 * q, f);
+                } else {
+                  store4<OutT>(D + off, f);
+                  for (int d = 0; d < p.n_extra; ++d) store4<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + off, f);
+                }
               } else {
                 const float fv[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
@@ -316,8 +341,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                   if (4 * q + e < ncols) {
                     float val = fv[e];
                     if (C != nullptr) val += p.beta * to_f<OutT>(C[off + e]);
-                    D[off + e] = from_f<OutT>(val);
-                    for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[off + e] = from_f<OutT>(val);
+                    if (p.route_rows > 0) {
+                      rbase[i][col + 4 * q + e] = from_f<OutT>(val);
+                    } else {
+                      D[off + e] = from_f<OutT>(val);
+                      for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[off + e] = from_f<OutT>(val);
+                    }
                     if (e == 0) f.x = val; else if (e == 1) f.y = val; else if (e == 2) f.z = val; else f.w = val;
                   }
                 }
@@ -421,8 +450,11 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
-              const uint32_t* wait_flags, uint32_t wait_seq, int region_rows) {
+              const uint32_t* wait_flags, uint32_t wait_seq, int region_rows, void* const* d_route, int n_route, int route_rows,
+              int64_t route_batch_stride, int64_t route_base) {
   const int BN = (N <= 128) ? 128 : 256;
+  if (n_route > 0 && (C != nullptr || symmetric || n_extra > 0 || route_rows <= 0 || (int64_t)n_route * route_rows < M || n_route > 8))
+    return -5;  // routed output excludes the addend, the mirrored output and the extra destinations
   CUtensorMap ma, mb;
   int r;
   if (a_mn_major)  // memory [K, M]
@@ -446,6 +478,10 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.wait_flags = (wait_flags != nullptr && region_rows > 0 && !a_mn_major) ? wait_flags : nullptr;
   p.wait_seq = wait_seq;
   p.region_rows = region_rows > 0 ? region_rows : 1;
+  p.route_rows = n_route > 0 ? route_rows : 0;
+  p.route_batch_stride = route_batch_stride;
+  p.route_base = route_base;
+  for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;
 #define SEG_GEMM(BNv, AM, BM_)                                                                      \
   (out_f32 ? launch_gemm<BNv, AM, BM_, float>(ma, mb, p, sm_count, st)                              \
            : launch_gemm<BNv, AM, BM_, __nv_bfloat16>(ma, mb, p, sm_count, st))

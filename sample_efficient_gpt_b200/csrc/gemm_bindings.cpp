@@ -43,7 +43,8 @@ void check_operand(const Tensor& t, const char* name) {
 // D = alpha * A op(B) + beta * C
 Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, std::optional<Tensor> out, bool out_f32, bool a_mn,
             bool b_mn, double alpha, double beta, bool symmetric, std::vector<int64_t> extra_dst,
-            const std::optional<Tensor>& wait_flags, int64_t wait_seq, int64_t region_rows) {
+            const std::optional<Tensor>& wait_flags, int64_t wait_seq, int64_t region_rows, std::vector<int64_t> route_ptrs,
+            int64_t route_rows, int64_t route_batch_stride, int64_t route_base, int64_t route_ld) {
   check_operand(a, "a");
   check_operand(b, "b");
   TORCH_CHECK(a.dim() == b.dim(), "a and b must have the same rank");
@@ -58,7 +59,11 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
   c10::cuda::CUDAGuard guard(a.device());
   auto opts = a.options().dtype(out_f32 ? at::kFloat : at::kBFloat16);
   Tensor d;
-  if (out.has_value()) {
+  const bool routed = !route_ptrs.empty();
+  if (routed) {
+    TORCH_CHECK(!out.has_value() && !c.has_value() && route_ld > 0, "routed output: no out / c tensors, and the destination row stride is required");
+    d = torch::empty({0}, opts);  // nothing is stored locally
+  } else if (out.has_value()) {
     d = *out;
     TORCH_CHECK(d.is_cuda() && d.scalar_type() == (out_f32 ? at::kFloat : at::kBFloat16), "out has the wrong dtype");
     TORCH_CHECK(d.stride(-1) == 1 && d.size(-2) == M && d.size(-1) == N, "out has the wrong shape");
@@ -72,7 +77,10 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
     cptr = c->data_ptr();
   }
   auto& st = device_state(a.device());
-  const int64_t bsa = a.dim() == 3 ? a.stride(0) : 0, bsb = b.dim() == 3 ? b.stride(0) : 0, bsd = d.dim() == 3 ? d.stride(0) : 0;
+  const int64_t bsa = a.dim() == 3 ? a.stride(0) : 0, bsb = b.dim() == 3 ? b.stride(0) : 0, bsd = (!routed && d.dim() == 3) ? d.stride(0) : 0;
+  void* routes[8] = {nullptr};
+  TORCH_CHECK(route_ptrs.size() <= 8, "at most 8 routed destinations");
+  for (size_t i = 0; i < route_ptrs.size(); ++i) routes[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(route_ptrs[i]));
   TORCH_CHECK(extra_dst.size() <= 7, "at most 7 extra destinations");
   const uint32_t* wf = nullptr;
   if (wait_flags.has_value()) {
@@ -83,10 +91,11 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
   }
   void* extras[7] = {nullptr};
   for (size_t i = 0; i < extra_dst.size(); ++i) extras[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(extra_dst[i]));
-  const int rc = seg::gemm_bf16(a.data_ptr(), b.data_ptr(), cptr, d.data_ptr(), M, N, K, batch, a.stride(-2), b.stride(-2),
-                                d.stride(-2), bsa, bsb, bsd, a_mn, b_mn, out_f32, (float)alpha, (float)beta, symmetric, extras,
+  const int rc = seg::gemm_bf16(a.data_ptr(), b.data_ptr(), cptr, routed ? nullptr : d.data_ptr(), M, N, K, batch, a.stride(-2), b.stride(-2),
+                                routed ? route_ld : d.stride(-2), bsa, bsb, bsd, a_mn, b_mn, out_f32, (float)alpha, (float)beta, symmetric, extras,
                                 (int)extra_dst.size(), st.status.data_ptr<int>(), st.sm_count,
-                                at::cuda::getCurrentCUDAStream().stream(), wf, (uint32_t)wait_seq, (int)region_rows);
+                                at::cuda::getCurrentCUDAStream().stream(), wf, (uint32_t)wait_seq, (int)region_rows, routes,
+                                (int)route_ptrs.size(), (int)route_rows, route_batch_stride, route_base);
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
   return d;
 }
@@ -153,7 +162,8 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("out_f32") = false, pybind11::arg("a_mn") = false, pybind11::arg("b_mn") = false, pybind11::arg("alpha") = 1.0,
         pybind11::arg("beta") = 0.0, pybind11::arg("symmetric") = false,
         pybind11::arg("extra_dst") = std::vector<int64_t>(), pybind11::arg("wait_flags") = std::nullopt, pybind11::arg("wait_seq") = 0,
-        pybind11::arg("region_rows") = 0);
+        pybind11::arg("region_rows") = 0, pybind11::arg("route_ptrs") = std::vector<int64_t>(), pybind11::arg("route_rows") = 0,
+        pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0);
   m.def("fa_fwd", &fa_fwd);
   m.def("fa_bwd", &fa_bwd);
   m.def("gemm_status", &gemm_status);

@@ -124,7 +124,11 @@ void moe_route_bwd(const float* probs, const int* idx, const float* dw, const fl
 int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
-              const uint32_t* wait_flags = nullptr, uint32_t wait_seq = 0, int region_rows = 0);
+              const uint32_t* wait_flags = nullptr, uint32_t wait_seq = 0, int region_rows = 0, void* const* d_route = nullptr,
+              int n_route = 0, int route_rows = 0, int64_t route_batch_stride = 0, int64_t route_base = 0);
+// d_route (optional): routed output - rows [r * route_rows, (r+1) * route_rows) of every batch entry go to d_route[r] (a buffer of
+// rank r, peer-mapped) at element offset route_base + batch * route_batch_stride + (row - r * route_rows) * ldd + column; D is
+// not written.  Not combinable with C, symmetric or d_extra.
 
 // ---- attn_bwd.cu (tcgen05 flash attention, backward)
 // q, o, d_o, dq [B,S,H,hd]; k, v, dk, dv [B,S,Hkv,hd] bf16; lse [B,H,S] fp32 from the forward.  Scratch: dq_acc fp32 like q

@@ -3,10 +3,8 @@
 //   q and k (eps 1e-6, q times a learnable scalar), value residual v' = s*c*(a1*v + a2*v1), c = rsqrt(a1^2+a2^2+1e-8).
 // Reference math: transformer/rope.py:36-56, transformer/attention.py:51-63 and 222-228.
 // Layouts: qkv [T, (H+2Hkv)*hd]; q [T,H,hd]; k, v, v1 [T,Hkv,hd] (token-major, what the attention kernel reads).
-// Work item = 8 rotary pairs of one token, for all of its head slots in turn (the rotation of those pairs is the same for
-// every head, so its cos/sin are read once per token): a thread loads x[8j..8j+8) and x[hd/2+8j..] with 16-byte accesses,
-// the next head's data already in flight; hd/16 neighbouring lanes share a token and combine their sums of squares with
-// shuffles.  The backward
+// Work item = 8 rotary pairs of one (token, head slot): a thread loads x[8j..8j+8) and x[hd/2+8j..] with 16-byte
+// accesses, hd/16 neighbouring lanes share a head and combine their sums of squares with shuffles.  The backward
 // recomputes rotation and norms from qkv (the forward saves nothing extra) and reduces the four scalar gradients
 // deterministically: per-CTA partials, then a single-CTA finalize.
 #include "common.cuh"
@@ -36,7 +34,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
   constexpr int HALF = HD / 2;
   constexpr int LPH = HALF / 8;  // lanes per head
   const int nslots = p.H + 2 * p.Hkv;
-  const int64_t total = (int64_t)p.B * p.S * LPH;  // work item: 8 rotary pairs of one token, for every head slot in turn
+  const int64_t total = (int64_t)p.B * p.S * nslots * LPH;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t rounds = (total + stride - 1) / stride;
   const float a1 = *p.alpha1, a2 = *p.alpha2, vs = *p.vscale;
@@ -45,25 +43,35 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   for (int64_t it = 0; it < rounds; ++it, idx += stride) {
     const bool live = idx < total;
-    const int64_t li = live ? idx : 0;
-    const int sub = (int)(li % LPH);
-    const int64_t t = li / LPH;
-    const int s = (int)(t % p.S);
-    // the rotation of this thread's 8 pairs is the same for every head of the token: one table read per token
-    float cs[8], sn[8];
-    load8<float>(p.cos + (size_t)s * HALF + sub * 8, cs);
-    load8<float>(p.sin + (size_t)s * HALF + sub * 8, sn);
-    const T* row = qkv + (size_t)t * p.qkv_stride + sub * 8;
-    float x1[8], x2[8], y1[8], y2[8];
-    load8<T>(row, x1);
-    load8<T>(row + HALF, x2);
-    for (int slot = 0; slot < nslots; ++slot) {
-      if (slot + 1 < nslots) {  // next head's data is in flight while this one is processed
-        load8<T>(row + (size_t)(slot + 1) * HD, y1);
-        load8<T>(row + (size_t)(slot + 1) * HD + HALF, y2);
-      }
-      if (slot < p.H + p.Hkv) {
-        float ss = 0.f;
+    int sub, slot, s;
+    int64_t t;
+    if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values dominate otherwise
+      const uint32_t i32 = live ? (uint32_t)idx : 0u;
+      sub = (int)(i32 % LPH);
+      const uint32_t sg = i32 / LPH;
+      slot = (int)(sg % (uint32_t)nslots);
+      const uint32_t t32 = sg / (uint32_t)nslots;
+      s = (int)(t32 % (uint32_t)p.S);
+      t = t32;
+    } else {
+      sub = (int)(idx % LPH);
+      const int64_t sg = live ? idx / LPH : 0;
+      slot = (int)(sg % nslots);
+      t = sg / nslots;
+      s = (int)(t % p.S);
+    }
+    float x1[8], x2[8];
+    if (live) {
+      const T* src = qkv + (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
+      load8<T>(src, x1);
+      load8<T>(src + HALF, x2);
+    }
+    if (slot < p.H + p.Hkv) {
+      float ss = 0.f;
+      if (live) {
+        float cs[8], sn[8];
+        load8<float>(p.cos + (size_t)s * HALF + sub * 8, cs);
+        load8<float>(p.sin + (size_t)s * HALF + sub * 8, sn);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float r1 = x1[j] * cs[j] - x2[j] * sn[j], r2 = x1[j] * sn[j] + x2[j] * cs[j];
@@ -71,23 +79,25 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
           x2[j] = r2;
           ss += r1 * r1 + r2 * r2;
         }
-        float mul = 1.f;
-        if (p.qknorm) {
-          ss = group_sum<LPH>(ss);
-          mul = rsqrtf(ss / HD + kQkEps);
-          if (slot < p.H) mul *= qg;
-        }
-        if (live) {
-          T* dst = (slot < p.H) ? q + ((size_t)t * p.H + slot) * HD : k + ((size_t)t * p.Hkv + (slot - p.H)) * HD;
+      }
+      float mul = 1.f;
+      if (p.qknorm) {
+        ss = group_sum<LPH>(ss);
+        mul = rsqrtf(ss / HD + kQkEps);
+        if (slot < p.H) mul *= qg;
+      }
+      if (live) {
+        T* dst = (slot < p.H) ? q + ((size_t)t * p.H + slot) * HD : k + ((size_t)t * p.Hkv + (slot - p.H)) * HD;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            x1[j] *= mul;
-            x2[j] *= mul;
-          }
-          store8<T>(dst + sub * 8, x1);
-          store8<T>(dst + HALF + sub * 8, x2);
+        for (int j = 0; j < 8; ++j) {
+          x1[j] *= mul;
+          x2[j] *= mul;
         }
-      } else if (live) {
+        store8<T>(dst + sub * 8, x1);
+        store8<T>(dst + HALF + sub * 8, x2);
+      }
+    } else {
+      if (live) {
         const size_t off = ((size_t)t * p.Hkv + (slot - p.H - p.Hkv)) * HD + sub * 8;
         float w1[8], w2[8];
         if (v1 != nullptr) {
@@ -103,11 +113,6 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
         store8<T>(v + off, x1);
         store8<T>(v + off + HALF, x2);
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        x1[j] = y1[j];
-        x2[j] = y2[j];
-      }
     }
   }
 }
@@ -122,7 +127,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
   constexpr int LPH = HALF / 8;
   __shared__ float red[32];
   const int nslots = p.H + 2 * p.Hkv;
-  const int64_t total = (int64_t)p.B * p.S * LPH;  // work item: 8 rotary pairs of one token, for every head slot in turn
+  const int64_t total = (int64_t)p.B * p.S * nslots * LPH;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t rounds = (total + stride - 1) / stride;
   const float a1 = *p.alpha1, a2 = *p.alpha2, vs = *p.vscale;
@@ -132,30 +137,39 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   for (int64_t it = 0; it < rounds; ++it, idx += stride) {
     const bool live = idx < total;
-    const int64_t li = live ? idx : 0;
-    const int sub = (int)(li % LPH);
-    const int64_t t = li / LPH;
-    const int s = (int)(t % p.S);
-    float cs[8], sn[8];
-    load8<float>(p.cos + (size_t)s * HALF + sub * 8, cs);
-    load8<float>(p.sin + (size_t)s * HALF + sub * 8, sn);
-    const size_t row0 = (size_t)t * p.qkv_stride + sub * 8;
-    float x1[8], x2[8], y1[8], y2[8];
-    load8<T>(qkv + row0, x1);
-    load8<T>(qkv + row0 + HALF, x2);
-    for (int slot = 0; slot < nslots; ++slot) {
-      const size_t row_off = row0 + (size_t)slot * HD;
-      if (slot + 1 < nslots) {
-        load8<T>(qkv + row_off + HD, y1);
-        load8<T>(qkv + row_off + HD + HALF, y2);
-      }
-      if (slot < p.H + p.Hkv) {
-        const bool is_q = slot < p.H;
-        float g1[8], g2[8];
-        float ss = 0.f, dot = 0.f;
+    int sub, slot, s;
+    int64_t t;
+    if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values dominate otherwise
+      const uint32_t i32 = live ? (uint32_t)idx : 0u;
+      sub = (int)(i32 % LPH);
+      const uint32_t sg = i32 / LPH;
+      slot = (int)(sg % (uint32_t)nslots);
+      const uint32_t t32 = sg / (uint32_t)nslots;
+      s = (int)(t32 % (uint32_t)p.S);
+      t = t32;
+    } else {
+      sub = (int)(idx % LPH);
+      const int64_t sg = live ? idx / LPH : 0;
+      slot = (int)(sg % nslots);
+      t = sg / nslots;
+      s = (int)(t % p.S);
+    }
+    const size_t row_off = (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
+    float x1[8], x2[8];
+    if (live) {
+      load8<T>(qkv + row_off, x1);
+      load8<T>(qkv + row_off + HALF, x2);
+    }
+    if (slot < p.H + p.Hkv) {
+      const bool is_q = slot < p.H;
+      float g1[8], g2[8], cs[8], sn[8];
+      float ss = 0.f, dot = 0.f;
+      if (live) {
         const T* g = is_q ? dq + ((size_t)t * p.H + slot) * HD + sub * 8 : dk + ((size_t)t * p.Hkv + (slot - p.H)) * HD + sub * 8;
         load8<T>(g, g1);
         load8<T>(g + HALF, g2);
+        load8<float>(p.cos + (size_t)s * HALF + sub * 8, cs);
+        load8<float>(p.sin + (size_t)s * HALF + sub * 8, sn);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float r1 = x1[j] * cs[j] - x2[j] * sn[j], r2 = x1[j] * sn[j] + x2[j] * cs[j];
@@ -164,30 +178,32 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
           ss += r1 * r1 + r2 * r2;
           dot += r1 * g1[j] + r2 * g2[j];
         }
-        if (p.qknorm) {
-          ss = group_sum<LPH>(ss);
-          dot = group_sum<LPH>(dot);
-          const float r = rsqrtf(ss / HD + kQkEps);
-          const float gamma = is_q ? qg : 1.f;
-          if (live && is_q && sub == 0) acc_qg += r * dot;
-          const float ka = gamma * r, kb = gamma * r * r * r * dot / HD;
+      }
+      if (p.qknorm) {
+        ss = group_sum<LPH>(ss);
+        dot = group_sum<LPH>(dot);
+        const float r = rsqrtf(ss / HD + kQkEps);
+        const float gamma = is_q ? qg : 1.f;
+        if (live && is_q && sub == 0) acc_qg += r * dot;
+        const float ka = gamma * r, kb = gamma * r * r * r * dot / HD;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            g1[j] = ka * g1[j] - kb * x1[j];
-            g2[j] = ka * g2[j] - kb * x2[j];
-          }
+        for (int j = 0; j < 8; ++j) {
+          g1[j] = ka * g1[j] - kb * x1[j];
+          g2[j] = ka * g2[j] - kb * x2[j];
         }
-        if (live) {
-          float o1[8], o2[8];
+      }
+      if (live) {
+        float o1[8], o2[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {  // transpose of the rotation
-            o1[j] = g1[j] * cs[j] + g2[j] * sn[j];
-            o2[j] = -g1[j] * sn[j] + g2[j] * cs[j];
-          }
-          store8<T>(dqkv + row_off, o1);
-          store8<T>(dqkv + row_off + HALF, o2);
+        for (int j = 0; j < 8; ++j) {  // transpose of the rotation
+          o1[j] = g1[j] * cs[j] + g2[j] * sn[j];
+          o2[j] = -g1[j] * sn[j] + g2[j] * cs[j];
         }
-      } else if (live) {
+        store8<T>(dqkv + row_off, o1);
+        store8<T>(dqkv + row_off + HALF, o2);
+      }
+    } else {
+      if (live) {
         const size_t off = ((size_t)t * p.Hkv + (slot - p.H - p.Hkv)) * HD + sub * 8;
         const float kself = vs * c * (v1 ? a1 : (a1 + a2));
         const float kother = vs * c * a2;
@@ -216,11 +232,6 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
           store8<float>(dv1_out + off, e1);
           store8<float>(dv1_out + off + HALF, e2);
         }
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        x1[j] = y1[j];
-        x2[j] = y2[j];
       }
     }
   }
@@ -257,8 +268,7 @@ __global__ void __launch_bounds__(256) qkv_post_finalize(const float* __restrict
 }
 
 int qkv_post_bwd_grid(int64_t T, int nslots, int hd) {
-  (void)nslots;
-  const int64_t items = T * (hd / 16);
+  const int64_t items = T * nslots * (hd / 16);
   int64_t g = (items + kPostThreads - 1) / kPostThreads;
   return (int)(g < kQkvPostMaxGrid ? (g > 0 ? g : 1) : kQkvPostMaxGrid);
 }

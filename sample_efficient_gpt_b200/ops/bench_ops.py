@@ -220,7 +220,7 @@ def bench_moe(a):
     probs, idx, w, slot, totals = M.route(x, wr, k, cap)
     ex = M.PeerExchange(E, None, "cuda")
     xb, _ = ex.dispatch("x", x, idx, slot, totals, None, cap)
-    yb = ex.output_buffer("y", tuple(xb.shape), torch.bfloat16, "cuda")
+    yb = ex.expert_output("y", tuple(xb.shape), torch.bfloat16, "cuda")[0]
     yb.copy_(xb)
     kept = int((slot >= 0).sum())
     dw, aux = torch.randn(T, k, device="cuda"), torch.rand(E, device="cuda")
@@ -228,8 +228,8 @@ def bench_moe(a):
         ("moe_route (+scan +slots)", lambda: M.route(x, wr, k, cap), T * d * 2 + T * E * 4 + T * k * 12),
         ("moe_push (dispatch)", lambda: ex.dispatch("x", x, idx, slot, totals, None, cap), T * d * 2 + E * cap * d * 2),
         ("moe_push (scaled, backward)", lambda: ex.dispatch("x", x, idx, slot, totals, w, cap), T * d * 2 + E * cap * d * 2),
-        ("moe_pull (combine)", lambda: ex.collect(yb, idx, slot, w, cap, torch.bfloat16), kept * d * 2 + T * d * 2),
-        ("moe_pull (+dots, backward)", lambda: ex.collect(yb, idx, slot, None, cap, torch.float32, dot_buf=yb, g=x), 2 * kept * d * 2 + T * d * 2 + T * d * 4),
+        ("moe_pull (combine)", lambda: ex.collect("y", yb, idx, slot, w, cap, torch.bfloat16), kept * d * 2 + T * d * 2),
+        ("moe_pull (+dots, backward)", lambda: ex.collect("y", yb, idx, slot, None, cap, torch.float32, dot_buf=yb, g=x), 2 * kept * d * 2 + T * d * 2 + T * d * 4),
         ("moe_route_bwd", lambda: M.route_bwd(probs, idx, dw, aux), T * E * 8 + T * k * 8),
     ]
     report(rows, a.iters)

@@ -28,14 +28,19 @@ def usable(*tensors: Tensor) -> bool:
 
 
 def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, symmetric=False,
-         extra_dst: list[int] | None = None, wait: tuple | None = None) -> Tensor:
+         extra_dst: list[int] | None = None, wait: tuple | None = None, route: tuple | None = None) -> Tensor:
     """``extra_dst``: device addresses of up to 7 more buffers with the output's layout (peer memory of other ranks);
     every output tile is stored to all of them from the epilogue.
     ``wait`` = (flags int32 tensor, seq, region_rows): rows ``[r * region_rows, (r+1) * region_rows)`` of ``a`` are being
-    written by rank r and are complete once ``flags[r] >= seq``; the kernel's producer waits per tile (bounded)."""
+    written by rank r and are complete once ``flags[r] >= seq``; the kernel's producer waits per tile (bounded).
+    ``route`` = (addresses, route_rows, batch_stride, base, ld): the output is not stored locally; rows
+    ``[r * route_rows, (r+1) * route_rows)`` of batch entry ``b`` go to buffer ``addresses[r]`` (of rank r) at element offset
+    ``base + b * batch_stride + (row - r * route_rows) * ld + column``."""
     ops._count()
     flags, seq, rows = wait if wait is not None else (None, 0, 0)
-    return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric, extra_dst or [], flags, int(seq), int(rows))
+    rp, rr, rbs, rbase, rld = route if route is not None else ([], 0, 0, 0, 0)
+    return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric, extra_dst or [], flags, int(seq), int(rows),
+                          list(rp), int(rr), int(rbs), int(rbase), int(rld))
 
 
 def mm_nt(x: Tensor, w: Tensor, **kw) -> Tensor:

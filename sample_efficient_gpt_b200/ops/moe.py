@@ -5,9 +5,11 @@ statements below, which are also the oracle of the kernel tests.  Specification:
 Layout of an exchange buffer on its owner rank: ``[E_local, world, cap, d]`` - expert, source rank, slot.
 Exchanges:
   * ``TorchExchange``  - index ops + ``all_to_all_single`` (gloo on CPU, NCCL on GPUs): baseline and CPU path.
-  * ``PeerExchange``   - dispatch = permutation fused with peer *stores* into the owners' symmetric buffers, combine =
-    un-permutation fused with peer *loads* from them; ordering by the device-side flag barrier of ``parallel.symm``.
-    With one rank it degenerates to local buffers and no barrier.
+  * ``PeerExchange``   - dispatch = permutation fused with peer *stores* into the owners' symmetric buffers (the consumer
+    GEMM waits per source rank on arrival flags); combine = the down-projection GEMM's epilogue stores its tiles straight
+    into the source ranks' landing buffers (routed output), then a local un-permutation + weighted sum.  Without the
+    overlapped mode: barrier-ordered push, and a pull (peer *loads*) for the combine.  With one rank it degenerates to
+    local buffers and no barrier.
 """
 
 from __future__ import annotations
@@ -76,8 +78,9 @@ class TorchExchange:
     def begin_step(self):
         pass
 
-    def output_buffer(self, key, shape, dtype, device) -> Tensor | None:
-        return None
+    def expert_output(self, key, shape, dtype, device):
+        """(tensor the expert GEMM must write into or None for a fresh one, routing of its output or None)."""
+        return None, None
 
     def _a2a(self, t: Tensor) -> Tensor:
         if self.world == 1:
@@ -100,8 +103,8 @@ class TorchExchange:
         recv = self._a2a(buf.view(self.world, self.e_local, cap, d))  # [src, e_local, cap, d]
         return recv.permute(1, 0, 2, 3).reshape(self.e_local, self.world * cap, d).contiguous(), None
 
-    def collect(self, buf: Tensor, idx: Tensor, slot: Tensor, w: Tensor | None, cap: int, out_dtype, dot_buf: Tensor | None = None,
-                g: Tensor | None = None):
+    def collect(self, key, buf: Tensor, idx: Tensor, slot: Tensor, w: Tensor | None, cap: int, out_dtype, dot_key=None,
+                dot_buf: Tensor | None = None, g: Tensor | None = None):
         d = buf.size(-1)
         T, k = idx.shape
 
@@ -165,9 +168,23 @@ class PeerExchange:
     def _addresses(self, t: Tensor) -> list[int]:
         return self.comm.all_addresses(t) if self.comm is not None else [t.data_ptr()]
 
-    def output_buffer(self, key, shape, dtype, device) -> Tensor:
+    def _recv(self, key, cap: int, d: int) -> Tensor:
+        """This rank's landing buffer [E, cap, d] for expert outputs that the owners' GEMMs store straight into it."""
+        t = self._bufs.get(("recv", key))
+        if t is None or t.shape != (self.n_experts, cap, d):
+            t = self.comm.symm_zeros((self.n_experts, cap, d), torch.bfloat16)
+            self._bufs[("recv", key)] = t
+        return t
+
+    def expert_output(self, key, shape, dtype, device):
+        """Overlapped mode: the expert GEMM's epilogue stores every tile into the *source* rank's landing buffer (routed
+        output), so the combine exchange runs inside the GEMM.  Otherwise: a symmetric buffer on this rank for the pull."""
         e_local, rows, d = shape
-        return self._buffer(key, rows // self.world, d).view(e_local, rows, d)
+        cap = rows // self.world
+        if self.overlap:
+            recv = self._recv(key, cap, d)
+            return None, (self.comm.all_addresses(recv), cap, cap * d, self.rank * self.e_local * cap * d, d)
+        return self._buffer(key, cap, d).view(e_local, rows, d), None
 
     def dispatch(self, key, x: Tensor, idx: Tensor, slot: Tensor, totals: Tensor, w: Tensor | None, cap: int) -> Tensor:
         buf = self._buffer(key, cap, x.size(1))
@@ -182,12 +199,21 @@ class PeerExchange:
             self.comm.barrier()  # every rank's rows have landed before anybody's GEMMs read them
         return view, None
 
-    def collect(self, buf: Tensor, idx: Tensor, slot: Tensor, w: Tensor | None, cap: int, out_dtype, dot_buf: Tensor | None = None,
-                g: Tensor | None = None):
+    def collect(self, key, buf: Tensor | None, idx: Tensor, slot: Tensor, w: Tensor | None, cap: int, out_dtype, dot_key=None,
+                dot_buf: Tensor | None = None, g: Tensor | None = None):
+        """``key`` / ``dot_key`` name the buffers in the overlapped mode (the rows are already here, in landing buffers);
+        ``buf`` / ``dot_buf`` are the owner-side buffers of the pull mode."""
         if self.comm is not None:
-            self.comm.barrier()  # every owner's output rows are written before anybody pulls them
+            self.comm.barrier()  # every owner's output rows are written before anybody reads them
         ops._count()
-        res = ops.ext().moe_pull(self._addresses(buf), self._addresses(dot_buf) if dot_buf is not None else [], idx, slot, w,
-                                 g.contiguous() if g is not None else None, buf.size(-1), self.n_experts, cap, self.rank,
-                                 out_dtype == torch.float32)
-        return res[0], (res[1] if dot_buf is not None else None)
+        want_dots = dot_key is not None or dot_buf is not None
+        gg = g.contiguous() if g is not None else None
+        if self.overlap:
+            d = self._bufs[("recv", key)].size(-1)
+            src = [self._bufs[("recv", key)].data_ptr()]  # one local buffer [E, cap, d]: "world 1, rank 0" addressing
+            src2 = [self._bufs[("recv", dot_key)].data_ptr()] if want_dots else []
+            res = ops.ext().moe_pull(src, src2, idx, slot, w, gg, d, self.n_experts, cap, 0, out_dtype == torch.float32)
+        else:
+            res = ops.ext().moe_pull(self._addresses(buf), self._addresses(dot_buf) if want_dots else [], idx, slot, w, gg,
+                                     buf.size(-1), self.n_experts, cap, self.rank, out_dtype == torch.float32)
+        return res[0], (res[1] if want_dots else None)

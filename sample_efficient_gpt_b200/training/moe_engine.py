@@ -25,15 +25,15 @@ from sample_efficient_gpt_b200.ops import moe as M
 
 
 def _bmm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out: Tensor | None = None, out_f32: bool = False, accumulate: bool = False,
-         wait=None):
+         wait=None, route=None):
     """Batched ``op(a) @ op(b)``: a is [.., M, K] (or [.., K, M] with a_mn), b is [.., N, K] (or [.., K, N] with b_mn).
     ``wait``: per-source-region arrival flags of ``a`` (see ``ops.gemm.gemm``); only the tcgen05 GEMM can honour them."""
     from sample_efficient_gpt_b200.ops import gemm as G
 
     if a.dtype == torch.bfloat16 and G.usable(a, b, out) and ops.kernel_enabled("moe_gemm"):
         return G.gemm(a, b, c=out if accumulate else None, out=out, out_f32=out_f32, a_mn=a_mn, b_mn=b_mn, beta=1.0 if accumulate else 0.0,
-                      wait=wait)
-    assert wait is None, "arrival flags need the tcgen05 GEMM"
+                      wait=wait, route=route)
+    assert wait is None and route is None, "arrival flags and routed outputs need the tcgen05 GEMM"
     A = a.transpose(-1, -2) if a_mn else a
     B = b if b_mn else b.transpose(-1, -2)
     if out_f32 and a.is_cuda and a.dtype != torch.float32:
@@ -114,8 +114,9 @@ class MoEEngine:
         xb, arrival = self.ex.dispatch(("x", i), n2, idx, slot, totals, None, cap)  # [E_local, world * cap, d]
         u = _bmm(xb, self.up_w[i], False, False, wait=arrival)
         a = ops.swiglu_fwd(u.view(-1, u.size(-1))).view(u.size(0), u.size(1), self.f)
-        yb = _bmm(a, self.down_w[i], False, False, out=self.ex.output_buffer(("y", i), (xb.size(0), xb.size(1), d), n2.dtype, n2.device))
-        m, _ = self.ex.collect(yb, idx, slot, w, cap, n2.dtype)
+        out, route = self.ex.expert_output(("y", i), (xb.size(0), xb.size(1), d), n2.dtype, n2.device)
+        yb = _bmm(a, self.down_w[i], False, False, out=out, route=route)  # routed: lands in the source ranks' buffers
+        m, _ = self.ex.collect(("y", i), yb, idx, slot, w, cap, n2.dtype)
         saved = (probs, idx, w, slot, totals, frac, cap, xb, u, a, yb) if train else None
         return m, saved
 
@@ -131,7 +132,8 @@ class MoEEngine:
         acc = (not first) and self.grads_in_stacks
         _bmm(dyb, a, True, True, out=self.down_g[i], out_f32=True, accumulate=acc)
         du = ops.swiglu_bwd(da.view(-1, self.f), u.view(-1, u.size(-1))).view_as(u)
-        dxb = _bmm(du, self.up_w[i], False, True, out=self.ex.output_buffer("dx", (xb.size(0), xb.size(1), d), dm.dtype, dm.device))
+        out, route = self.ex.expert_output("dx", (xb.size(0), xb.size(1), d), dm.dtype, dm.device)
+        dxb = _bmm(du, self.up_w[i], False, True, out=out, route=route)
         _bmm(du, xb, True, True, out=self.up_g[i], out_f32=True, accumulate=acc)
         if not self.grads_in_stacks:
             ex = ffn.experts
@@ -140,7 +142,7 @@ class MoEEngine:
                     pu.grad.copy_(self.up_g[i][e]), pd.grad.copy_(self.down_g[i][e])
                 else:
                     pu.grad.add_(self.up_g[i][e]), pd.grad.add_(self.down_g[i][e])
-        dn2, dots = self.ex.collect(dxb, idx, slot, None, cap, torch.float32, dot_buf=yb, g=dm)
+        dn2, dots = self.ex.collect("dx", dxb, idx, slot, None, cap, torch.float32, dot_key=("y", i), dot_buf=yb, g=dm)
         aux_vec = frac * (loss_coef * ffn.aux_loss_weight * self.E / T)
         dlogits = M.route_bwd(probs, idx, dots, aux_vec)  # [T, E] fp32
         wr = ffn.router.linear.weight

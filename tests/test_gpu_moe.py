@@ -59,10 +59,10 @@ def test_push_pull_match_reference_single_rank(scaled):
     y2 = torch.randn_like(want)
     g = torch.randn(T, d, device="cuda").bfloat16()
     peer._bufs["y"], peer._bufs["y2"] = y.view(E, 1, cap, d).clone(), y2.view(E, 1, cap, d).clone()
-    out, dots = peer.collect(peer._bufs["y"].view(E, cap, d), idx, slot, ww, cap, torch.float32, dot_buf=peer._bufs["y2"].view(E, cap, d), g=g)
-    rout, rdots = ref.collect(y, idx, slot, ww, cap, torch.float32, dot_buf=y2, g=g)
+    out, dots = peer.collect("y", peer._bufs["y"].view(E, cap, d), idx, slot, ww, cap, torch.float32, dot_buf=peer._bufs["y2"].view(E, cap, d), g=g)
+    rout, rdots = ref.collect("y", y, idx, slot, ww, cap, torch.float32, dot_buf=y2, g=g)
     assert torch.allclose(out, rout, atol=1e-4, rtol=1e-4) and torch.allclose(dots, rdots, atol=2e-3, rtol=1e-3)
-    out_lp, none = peer.collect(peer._bufs["y"].view(E, cap, d), idx, slot, ww, cap, torch.bfloat16)
+    out_lp, none = peer.collect("y", peer._bufs["y"].view(E, cap, d), idx, slot, ww, cap, torch.bfloat16)
     assert none is None and torch.allclose(out_lp.float(), rout, atol=3e-2, rtol=2e-2)
 
 
