@@ -156,12 +156,14 @@ seg::QkvPostParams make_post(const Tensor& cos, const Tensor& sin, const Tensor&
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.hd = hd; p.qknorm = qknorm;
   p.cos = cos.data_ptr<float>(); p.sin = sin.data_ptr<float>(); p.qgain = qgain.data_ptr<float>();
   p.alpha1 = a1.data_ptr<float>(); p.alpha2 = a2.data_ptr<float>(); p.vscale = vs.data_ptr<float>();
+  p.qkv_stride = 0;
+  p.pos = nullptr;
   return p;
 }
 
 std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTensor& v1, const Tensor& cos, const Tensor& sin,
                                                 const Tensor& qgain, const Tensor& a1, const Tensor& a2, const Tensor& vs, int B,
-                                                int S, int H, int Hkv, int hd, bool qknorm) {
+                                                int S, int H, int Hkv, int hd, bool qknorm, const OptTensor& pos) {
   const bool bf16 = qkv.scalar_type() == at::kBFloat16;
   check_rows(qkv, bf16, "qkv");
   TORCH_CHECK(qkv.size(0) == (int64_t)B * S && qkv.size(1) == (int64_t)(H + 2 * Hkv) * hd, "qkv has the wrong shape");
@@ -169,6 +171,10 @@ std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTens
   c10::cuda::CUDAGuard guard(qkv.device());
   auto p = make_post(cos, sin, qgain, a1, a2, vs, B, S, H, Hkv, hd, qknorm);
   p.qkv_stride = qkv.stride(0);
+  if (pos.has_value()) {
+    TORCH_CHECK(pos->is_cuda() && pos->scalar_type() == at::kInt && pos->numel() == 1, "pos must be a CUDA int32 scalar");
+    p.pos = pos->data_ptr<int>();
+  }
   Tensor q = torch::empty({B, S, H, hd}, qkv.options());
   Tensor k = torch::empty({B, S, Hkv, hd}, qkv.options());
   Tensor v = torch::empty({B, S, Hkv, hd}, qkv.options());
@@ -404,7 +410,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("gate_fwd", &gate_fwd);
   m.def("gate_bwd", &gate_bwd);
-  m.def("qkv_post_fwd", &qkv_post_fwd);
+  m.def("qkv_post_fwd", &qkv_post_fwd, pybind11::arg("qkv"), pybind11::arg("v1"), pybind11::arg("cos"), pybind11::arg("sin"),
+        pybind11::arg("qgain"), pybind11::arg("a1"), pybind11::arg("a2"), pybind11::arg("vs"), pybind11::arg("B"), pybind11::arg("S"),
+        pybind11::arg("H"), pybind11::arg("Hkv"), pybind11::arg("hd"), pybind11::arg("qknorm"), pybind11::arg("pos") = std::nullopt);
   m.def("qkv_post_bwd", &qkv_post_bwd, pybind11::arg("dq"), pybind11::arg("dk"), pybind11::arg("dv"), pybind11::arg("qkv"),
         pybind11::arg("v1"), pybind11::arg("cos"), pybind11::arg("sin"), pybind11::arg("qgain"), pybind11::arg("a1"), pybind11::arg("a2"),
         pybind11::arg("vs"), pybind11::arg("B"), pybind11::arg("S"), pybind11::arg("H"), pybind11::arg("Hkv"), pybind11::arg("hd"),

@@ -33,6 +33,7 @@ struct QkvPostParams {
   const float* alpha2;  // [1]
   const float* vscale;  // [1]
   int64_t qkv_stride;   // row stride (elements) of qkv and dqkv: (H + 2 Hkv) * hd, or more when the projection is wider
+  const int* pos;       // optional device scalar added to every token's position (decode: S == 1, position = cache length)
 };
 void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st);
 // dv_is_f32: dv is fp32 (first block, after the v1 gradients were added); dv1_out fp32 [T,Hkv,hd] or nullptr;

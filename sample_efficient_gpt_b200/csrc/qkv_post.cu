@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
   const float a1 = *p.alpha1, a2 = *p.alpha2, vs = *p.vscale;
   const float c = rsqrtf(a1 * a1 + a2 * a2 + kMixEps);
   const float qg = *p.qgain;
+  const int pos_off = p.pos != nullptr ? *p.pos : 0;
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   for (int64_t it = 0; it < rounds; ++it, idx += stride) {
     const bool live = idx < total;
@@ -51,14 +52,14 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_fwd_kernel(const T* __r
       const uint32_t sg = i32 / LPH;
       slot = (int)(sg % (uint32_t)nslots);
       const uint32_t t32 = sg / (uint32_t)nslots;
-      s = (int)(t32 % (uint32_t)p.S);
+      s = (int)(t32 % (uint32_t)p.S) + pos_off;
       t = t32;
     } else {
       sub = (int)(idx % LPH);
       const int64_t sg = live ? idx / LPH : 0;
       slot = (int)(sg % nslots);
       t = sg / nslots;
-      s = (int)(t % p.S);
+      s = (int)(t % p.S) + pos_off;
     }
     float x1[8], x2[8];
     if (live) {
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
   const float a1 = *p.alpha1, a2 = *p.alpha2, vs = *p.vscale;
   const float c = rsqrtf(a1 * a1 + a2 * a2 + kMixEps);
   const float qg = *p.qgain;
+  const int pos_off = p.pos != nullptr ? *p.pos : 0;
   float acc_qg = 0.f, acc_dvU = 0.f, acc_dvv = 0.f, acc_dvv1 = 0.f;
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   for (int64_t it = 0; it < rounds; ++it, idx += stride) {
@@ -145,14 +147,14 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
       const uint32_t sg = i32 / LPH;
       slot = (int)(sg % (uint32_t)nslots);
       const uint32_t t32 = sg / (uint32_t)nslots;
-      s = (int)(t32 % (uint32_t)p.S);
+      s = (int)(t32 % (uint32_t)p.S) + pos_off;
       t = t32;
     } else {
       sub = (int)(idx % LPH);
       const int64_t sg = live ? idx / LPH : 0;
       slot = (int)(sg % nslots);
       t = sg / nslots;
-      s = (int)(t % p.S);
+      s = (int)(t % p.S) + pos_off;
     }
     const size_t row_off = (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
     float x1[8], x2[8];

@@ -8,6 +8,7 @@ evals/chat_web.py:89-110).
 * ``GraphDecoder``: the one-token decode step of a dense model as a CUDA graph over static buffers (token, position,
   per-layer K/V caches of ``max_len`` positions, a position mask): the ~12 small kernels per layer of a decode step are
   launch-bound, a graph replay issues them in one call.  The prompt is prefilled eagerly into the same buffers.
+* ``EngineDecoder``: the same step on the training engine's fused kernels and bf16 weight shadows (default on a GPU).
 * ``ChatEngine``: renders conversations (tokenizer chat template, else the ``<|user_start|>...`` special-token format,
   else a plain-text fallback), runs prompts of equal length as one batch (the model has no padding mask), samples on the
   device, and checks for "all rows finished" every few steps so the decode loop does not synchronise per token.
@@ -160,6 +161,111 @@ class GraphDecoder:
         return self.logits
 
 
+class EngineDecoder:
+    """Decode step on the fused kernels of the training engine (bf16 weight shadows, fused qkv+gate projection, one
+    kernel each for add+RMSNorm, RoPE/QK-norm/value-mix at the cache position, gate, SwiGLU) captured in a CUDA graph:
+    about a dozen launches per block instead of the several dozen of the module path.  Caches hold finished keys and values
+    token-major, ``[B, max_len, Hkv, hd]``; the prompt is prefilled with the engine's forward."""
+
+    def __init__(self, model, batch: int, max_len: int, device, engine=None):
+        import torch.nn.functional as F
+
+        from sample_efficient_gpt_b200.training.engine import FusedEngine
+
+        self.F, self.model, self.B, self.max_len, self.device = F, model, batch, max_len, torch.device(device)
+        self.eng = engine if engine is not None else FusedEngine(model, torch.bfloat16)  # bf16 copies of the weights
+        at = model.blocks[0].attn
+        self.H, self.Hkv, self.hd = at.n_heads, at.n_kv_heads, at.head_dim
+        mk = lambda: torch.zeros(batch, max_len, self.Hkv, self.hd, dtype=torch.bfloat16, device=self.device)  # noqa: E731
+        self.kc, self.vc = [mk() for _ in model.blocks], [mk() for _ in model.blocks]
+        self.token = torch.zeros(batch, dtype=torch.long, device=self.device)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.pos32 = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.arange = torch.arange(max_len, device=self.device)
+        self.logits: Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+
+    def _final(self, res, delta):
+        from sample_efficient_gpt_b200 import ops
+
+        fn = self.model.final_norm
+        _, hf, _, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, float(fn.position_scale), fn.eps, torch.bfloat16, False)
+        logits = ops.matmul_nt(hf, self.eng._w(self.model.lm_head.linear.weight)).float()
+        return logits * self.model.output_mult if self.model.output_mult != 1.0 else logits
+
+    @torch.inference_mode()
+    def prefill(self, prompt: Tensor) -> Tensor:
+        eng, model = self.eng, self.model
+        B, S = prompt.shape
+        res = model.embedding.weight.detach()[prompt.reshape(-1)].float()
+        delta, v1 = None, None
+        for i in range(model.n_layers):
+            res, delta, v, _, saved = eng._layer_fwd(i, res, delta, v1, B, S, want_kurt=False, train=False)
+            if v1 is None:
+                v1 = v
+            self.kc[i][:, :S].copy_(saved[6].view(B, S, self.Hkv, self.hd))  # finished keys / values of the prompt
+            self.vc[i][:, :S].copy_(saved[7].view(B, S, self.Hkv, self.hd))
+        last = torch.arange(B, device=self.device) * S + (S - 1)
+        self.pos.fill_(S)
+        self.pos32.fill_(S)
+        return self._final(res[last], delta[last])
+
+    def _step(self) -> Tensor:
+        from sample_efficient_gpt_b200 import ops
+
+        eng, model, F = self.eng, self.model, self.F
+        B, H, Hkv, hd, lp = self.B, self.H, self.Hkv, self.hd, torch.bfloat16
+        mask = (self.arange <= self.pos).view(1, 1, 1, self.max_len)
+        res = model.embedding.weight.detach()[self.token].float()
+        delta, v1 = None, None
+        for i, blk in enumerate(model.blocks):
+            at = blk.attn
+            scale = float(blk.ln1.position_scale)
+            x, n1, _, _ = ops.add_rmsnorm_fwd(res, delta, blk.ln1.gain, scale, blk.ln1.eps, lp, False)
+            if i in eng.qkvz_w:
+                n_qkv = at.qkv.linear.weight.size(0)
+                qkvz = ops.matmul_nt(n1, eng.qkvz_w[i])
+                qkv, z = qkvz[:, :n_qkv], qkvz[:, n_qkv : n_qkv + H].contiguous()
+            else:
+                qkv = ops.matmul_nt(n1, eng._w(at.qkv.linear.weight))
+                z = ops.matmul_nt(n1, eng._w(at.attn_gate.linear.weight)) if at.gating else None
+            qgain = at.sdpa_qknorm.gain if at.qknorm else eng._ones
+            q, k, v = ops.qkv_post_fwd(qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, 1, H, Hkv, hd, at.qknorm,
+                                       pos=self.pos32)
+            if v1 is None:
+                v1 = v
+            self.kc[i].index_copy_(1, self.pos, k)
+            self.vc[i].index_copy_(1, self.pos, v)
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), self.kc[i].transpose(1, 2), self.vc[i].transpose(1, 2), attn_mask=mask,
+                                               enable_gqa=True)
+            o = o.transpose(1, 2).reshape(B, H, hd)
+            g = ops.gate_fwd(o, z) if at.gating else o.reshape(B, H * hd)
+            a = ops.matmul_nt(g, eng._w(at.out.linear.weight))
+            y, n2, _, _ = ops.add_rmsnorm_fwd(x, a, blk.ln2.gain, scale, blk.ln2.eps, lp, False)
+            u = ops.matmul_nt(n2, eng._w(blk.ffn.up.linear.weight))
+            m = ops.matmul_nt(ops.swiglu_fwd(u), eng._w(blk.ffn.down.linear.weight))
+            res, delta = y, m
+        return self._final(res, delta)
+
+    @torch.inference_mode()
+    def step(self, tokens: Tensor) -> Tensor:
+        self.token.copy_(tokens.view(self.B))
+        if self.graph is None:
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step()
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = self._step()
+        self.graph.replay()
+        self.pos.add_(1)
+        self.pos32.add_(1)
+        return self.logits
+
+
 @dataclass
 class SamplingParams:
     n: int = 1
@@ -199,7 +305,8 @@ def _message_text(content) -> str:
 
 class ChatEngine:
     def __init__(self, model, tokenizer, device="cpu", max_model_len: int = 2048, chat_template: str | None = None,
-                 dtype: torch.dtype | None = None, sync_every: int = 16, cuda_graphs: bool | None = None, cast_weights: bool = False):
+                 dtype: torch.dtype | None = None, sync_every: int = 16, cuda_graphs: bool | None = None, cast_weights: bool = False,
+                 fused_decode: bool | None = None):
         self.model, self.tokenizer, self.device = model.to(device).eval(), tokenizer, torch.device(device)
         self.max_model_len, self.chat_template, self.sync_every = max_model_len, chat_template, sync_every
         self.autocast = (torch.autocast("cuda", dtype=dtype or torch.bfloat16) if self.device.type == "cuda" else nullcontext())
@@ -211,7 +318,13 @@ class ChatEngine:
         self._special = {t: vocab[t] for t in SPECIAL_FORMAT if t in vocab}
         dense = not any(b.is_moe for b in self.model.blocks) and self.model.blocks[0].attn.gating in (False, "per-head")
         self.cuda_graphs = (self.device.type == "cuda" and dense) if cuda_graphs is None else (cuda_graphs and self.device.type == "cuda")
-        self._decoders: dict[int, GraphDecoder] = {}  # batch size -> decoder (caches for max_model_len positions)
+        self._decoders: dict = {}  # batch size -> decoder (caches for max_model_len positions)
+        # decode on the engine's fused kernels when they are built and apply (bf16, dense, per-head or no gate)
+        from sample_efficient_gpt_b200 import ops as _ops
+
+        can_fuse = (self.cuda_graphs and (dtype or torch.bfloat16) == torch.bfloat16 and _ops.ext() is not None
+                    and self.model.blocks[0].attn.head_dim % 16 == 0)
+        self.fused_decode = can_fuse if fused_decode is None else (fused_decode and can_fuse)
 
     # ---- prompt rendering -------------------------------------------------------------------------------------------
     def render(self, messages: list[dict]) -> list[int]:
@@ -253,7 +366,11 @@ class ChatEngine:
         if self.cuda_graphs:
             decoder = self._decoders.get(B)
             if decoder is None:
-                decoder = self._decoders[B] = GraphDecoder(self.model, B, self.max_model_len, self.device, self.autocast)
+                if self.fused_decode:
+                    shared = next((d.eng for d in self._decoders.values() if isinstance(d, EngineDecoder)), None)
+                    decoder = self._decoders[B] = EngineDecoder(self.model, B, self.max_model_len, self.device, shared)
+                else:
+                    decoder = self._decoders[B] = GraphDecoder(self.model, B, self.max_model_len, self.device, self.autocast)
         else:
             caches = [StaticKVCache(S + budget) for _ in range(self.model.n_layers)]
         with self.autocast:
