@@ -9,16 +9,29 @@
 
 namespace seg {
 
-template <typename T>
+// VEC elements per thread and access: 8 (16-byte bf16 / 2 x 16-byte fp32 accesses) when F % 8 == 0, else 4.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ u, T* __restrict__ f, int64_t rows, int F) {
-  const int f4 = F >> 2;
-  const int64_t total = rows * f4;
+  const int fv = F / VEC;
+  const int64_t total = rows * fv;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / f4;
-    const int c = (int)(i - r * f4) * 4;
-    const float4 a = load4<T>(u + r * 2 * F + c), b = load4<T>(u + r * 2 * F + F + c);
-    store4<T>(f + r * F + c, make_float4(a.x * sigmoidf_(a.x) * b.x, a.y * sigmoidf_(a.y) * b.y, a.z * sigmoidf_(a.z) * b.z,
-                                          a.w * sigmoidf_(a.w) * b.w));
+    const int64_t r = i / fv;
+    const int c = (int)(i - r * fv) * VEC;
+    float a[8], b[8], o[8];
+    if (VEC == 8) {
+      load8<T>(u + r * 2 * F + c, a);
+      load8<T>(u + r * 2 * F + F + c, b);
+    } else {
+      const float4 a4 = load4<T>(u + r * 2 * F + c), b4 = load4<T>(u + r * 2 * F + F + c);
+      a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
+      b[0] = b4.x; b[1] = b4.y; b[2] = b4.z; b[3] = b4.w;
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = a[j] * sigmoidf_(a[j]) * b[j];
+    if (VEC == 8)
+      store8<T>(f + r * F + c, o);
+    else
+      store4<T>(f + r * F + c, make_float4(o[0], o[1], o[2], o[3]));
   }
 }
 
@@ -28,22 +41,34 @@ __device__ __forceinline__ void swiglu_grad(float a, float b, float df, float& d
   db = df * a * s;
 }
 
-template <typename T>
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const T* __restrict__ df, const T* __restrict__ u, T* __restrict__ du,
                                                        int64_t rows, int F) {
-  const int f4 = F >> 2;
-  const int64_t total = rows * f4;
+  const int fv = F / VEC;
+  const int64_t total = rows * fv;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / f4;
-    const int c = (int)(i - r * f4) * 4;
-    const float4 a = load4<T>(u + r * 2 * F + c), b = load4<T>(u + r * 2 * F + F + c), g = load4<T>(df + r * F + c);
-    float4 da, db;
-    swiglu_grad(a.x, b.x, g.x, da.x, db.x);
-    swiglu_grad(a.y, b.y, g.y, da.y, db.y);
-    swiglu_grad(a.z, b.z, g.z, da.z, db.z);
-    swiglu_grad(a.w, b.w, g.w, da.w, db.w);
-    store4<T>(du + r * 2 * F + c, da);
-    store4<T>(du + r * 2 * F + F + c, db);
+    const int64_t r = i / fv;
+    const int c = (int)(i - r * fv) * VEC;
+    float a[8], b[8], g[8], da[8], db[8];
+    if (VEC == 8) {
+      load8<T>(u + r * 2 * F + c, a);
+      load8<T>(u + r * 2 * F + F + c, b);
+      load8<T>(df + r * F + c, g);
+    } else {
+      const float4 a4 = load4<T>(u + r * 2 * F + c), b4 = load4<T>(u + r * 2 * F + F + c), g4 = load4<T>(df + r * F + c);
+      a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
+      b[0] = b4.x; b[1] = b4.y; b[2] = b4.z; b[3] = b4.w;
+      g[0] = g4.x; g[1] = g4.y; g[2] = g4.z; g[3] = g4.w;
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) swiglu_grad(a[j], b[j], g[j], da[j], db[j]);
+    if (VEC == 8) {
+      store8<T>(du + r * 2 * F + c, da);
+      store8<T>(du + r * 2 * F + F + c, db);
+    } else {
+      store4<T>(du + r * 2 * F + c, make_float4(da[0], da[1], da[2], da[3]));
+      store4<T>(du + r * 2 * F + F + c, make_float4(db[0], db[1], db[2], db[3]));
+    }
   }
 }
 
@@ -54,19 +79,21 @@ static int stream_grid(int64_t work_items, int block) {
 }
 
 void swiglu_fwd(const void* u, void* f, int64_t T, int F, bool bf16, cudaStream_t st) {
-  const int grid = stream_grid(T * (F / 4), 256);
-  if (bf16)
-    swiglu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)f, T, F);
-  else
-    swiglu_fwd_kernel<float><<<grid, 256, 0, st>>>((const float*)u, (float*)f, T, F);
+  const bool v8 = (F % 8 == 0);
+  const int grid = stream_grid(T * (F / (v8 ? 8 : 4)), 256);
+#define SEG_SW(TY, V) swiglu_fwd_kernel<TY, V><<<grid, 256, 0, st>>>((const TY*)u, (TY*)f, T, F)
+  if (bf16) { if (v8) SEG_SW(__nv_bfloat16, 8); else SEG_SW(__nv_bfloat16, 4); }
+  else { if (v8) SEG_SW(float, 8); else SEG_SW(float, 4); }
+#undef SEG_SW
 }
 
 void swiglu_bwd(const void* df, const void* u, void* du, int64_t T, int F, bool bf16, cudaStream_t st) {
-  const int grid = stream_grid(T * (F / 4), 256);
-  if (bf16)
-    swiglu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)df, (const __nv_bfloat16*)u, (__nv_bfloat16*)du, T, F);
-  else
-    swiglu_bwd_kernel<float><<<grid, 256, 0, st>>>((const float*)df, (const float*)u, (float*)du, T, F);
+  const bool v8 = (F % 8 == 0);
+  const int grid = stream_grid(T * (F / (v8 ? 8 : 4)), 256);
+#define SEG_SWB(TY, V) swiglu_bwd_kernel<TY, V><<<grid, 256, 0, st>>>((const TY*)df, (const TY*)u, (TY*)du, T, F)
+  if (bf16) { if (v8) SEG_SWB(__nv_bfloat16, 8); else SEG_SWB(__nv_bfloat16, 4); }
+  else { if (v8) SEG_SWB(float, 8); else SEG_SWB(float, 4); }
+#undef SEG_SWB
 }
 
 // One group of hd/4 threads per (token, head); hd/4 is 16 (hd 64) or 32 (hd 128), so a warp holds 2 or 1 heads.

@@ -182,6 +182,9 @@ class EngineDecoder:
         self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
         self.pos32 = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.arange = torch.arange(max_len, device=self.device)
+        # host copies of the per-block norm scales: reading a device scalar is not allowed while a graph is captured
+        self.scales = [float(b.ln1.position_scale) for b in model.blocks]
+        self.final_scale = float(model.final_norm.position_scale)
         self.logits: Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
 
@@ -189,7 +192,7 @@ class EngineDecoder:
         from sample_efficient_gpt_b200 import ops
 
         fn = self.model.final_norm
-        _, hf, _, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, float(fn.position_scale), fn.eps, torch.bfloat16, False)
+        _, hf, _, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, self.final_scale, fn.eps, torch.bfloat16, False)
         logits = ops.matmul_nt(hf, self.eng._w(self.model.lm_head.linear.weight)).float()
         return logits * self.model.output_mult if self.model.output_mult != 1.0 else logits
 
@@ -220,7 +223,7 @@ class EngineDecoder:
         delta, v1 = None, None
         for i, blk in enumerate(model.blocks):
             at = blk.attn
-            scale = float(blk.ln1.position_scale)
+            scale = self.scales[i]
             x, n1, _, _ = ops.add_rmsnorm_fwd(res, delta, blk.ln1.gain, scale, blk.ln1.eps, lp, False)
             if i in eng.qkvz_w:
                 n_qkv = at.qkv.linear.weight.size(0)
@@ -312,8 +315,9 @@ class ChatEngine:
         self.autocast = (torch.autocast("cuda", dtype=dtype or torch.bfloat16) if self.device.type == "cuda" else nullcontext())
         if cast_weights and self.device.type == "cuda" and (dtype or torch.bfloat16) != torch.float32:
             # serving: keep the weights in the compute dtype instead of re-casting fp32 masters on every decode step
-            for prm in self.model.parameters():  # parameters only: the fp32 rotary tables and norm scales stay as they are
-                prm.data = prm.data.to(dtype or torch.bfloat16)
+            for prm in self.model.parameters():  # matrices only: gains, scalars, rotary tables and norm scales stay fp32
+                if prm.ndim >= 2:
+                    prm.data = prm.data.to(dtype or torch.bfloat16)
         vocab = tokenizer.get_vocab() if hasattr(tokenizer, "get_vocab") else {}
         self._special = {t: vocab[t] for t in SPECIAL_FORMAT if t in vocab}
         dense = not any(b.is_moe for b in self.model.blocks) and self.model.blocks[0].attn.gating in (False, "per-head")
