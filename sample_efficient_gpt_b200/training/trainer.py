@@ -223,7 +223,8 @@ class Trainer:
             try:
                 from sample_efficient_gpt_b200.parallel.symm import SymmComm
 
-                return SymmComm.create(self.device, use_multimem=(backend == "nvls"))
+                blocks = int(os.environ.get("SEGPT_COMM_BLOCKS", "32"))  # CTAs per bucket kernel (they share the GPU with the backward pass)
+                return SymmComm.create(self.device, use_multimem=(backend == "nvls"), blocks=blocks)
             except Exception as e:
                 if backend != "auto":
                     raise
