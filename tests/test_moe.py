@@ -75,6 +75,29 @@ def _moe_model(seed=0, **kw):
                        n_kv_heads=2, weight_tying=True, moe=moe, **kw)
 
 
+def test_engine_moe_with_recompute_matches_autograd():
+    """First block recomputed in the backward sweep (activation checkpointing): routing is recomputed identically and the
+    load-balance terms are recorded once."""
+    from sample_efficient_gpt_b200.training.engine import FusedEngine
+    from sample_efficient_gpt_b200.training.loss import efficient_cross_entropy
+
+    m = _moe_model(num_grad_checkpoint_layers=1)
+    ids = torch.randint(0, 200, (2, 24))
+    tg = torch.randint(0, 200, (2, 24))
+    logits, _ = m(ids)
+    loss, _, _ = efficient_cross_entropy(logits, tg)
+    aux = m.aux_loss()
+    (loss + aux).backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters()}
+    for p in m.parameters():
+        p.grad = None
+    eng = FusedEngine(m, torch.float32)
+    out = eng.forward_backward(ids, tg, 1.0)
+    assert float(out.aux_loss) == pytest.approx(float(aux), rel=1e-5) and len(eng.moe.aux_terms) == 2
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, want[n], rtol=2e-3, atol=1e-6 + 1e-4 * float(want[n].abs().max())), n
+
+
 @pytest.mark.parametrize("cf", [1.25, 0.6])
 def test_engine_moe_matches_autograd(cf):
     """Hand-scheduled MoE forward/backward (routing, dispatch, grouped GEMMs, combine, router backward incl. the
