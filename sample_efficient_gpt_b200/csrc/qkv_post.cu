@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kPostThreads, 4) qkv_post_fwd_kernel(const T* 
 }
 
 template <typename T, typename DVT, int HD>
-__global__ void __launch_bounds__(kPostThreads, 3) qkv_post_bwd_kernel(const T* __restrict__ dq, const T* __restrict__ dk,
+__global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __restrict__ dq, const T* __restrict__ dk,
                                                                   const DVT* __restrict__ dv, const T* __restrict__ qkv,
                                                                   const T* __restrict__ v1, T* __restrict__ dqkv,
                                                                   float* __restrict__ dv1_out, float* __restrict__ partial,
