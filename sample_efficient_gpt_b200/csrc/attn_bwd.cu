@@ -14,10 +14,15 @@
 //   dQ_i = dS  K     (A = the dS^T tile read as an MN-major operand, B = K as MN-major; fresh accumulator per tile,
 //                     drained through swizzled shared-memory boxes and TMA reductions (cp.reduce.async.bulk.tensor ... add)
 //                     into an fp32 dQ buffer because other key tiles add to the same rows)
-// TMEM: S^T 128 + dP^T 128 + dV 64 + dK 64 + dQ 64 = 448 of 512 columns, one CTA per SM.
-// Roles (320 threads): warp 0 TMA producer (K/V once; Q and dO tiles through a 2-stage ring; 4-D tensor maps, no
-// multicast), warp 1 MMA issuer, warps 2-9 the element-wise stage (a key row and half of the query columns per thread); lse and D of the step's queries travel with the tiles as bulk copies.
-// Two small kernels frame it: `attn_bwd_prep` (D and lse in the exp2 domain) and `attn_bwd_finish` (dQ fp32 -> bf16).
+// TMEM: S^T 128 + dP^T 128 + dV 64 + dK 64 + dQ 2 x 64 = all 512 columns, one CTA per SM.
+// Schedule (software pipeline over the steps n of the walk): the element-wise warps copy S^T / dP^T of step n into registers and
+// release them at once, so the tensor core computes S^T / dP^T of step n+1 during the element-wise math of step n; P^T / dS^T
+// are kept in registers until the dV / dK / dQ products of step n-1 have finished reading the operand buffers, so that those
+// products also overlap the math; dQ alternates between two accumulators and step n-1's is drained while step n's products run.
+// Roles (384 threads in three warpgroups): warp 0 TMA producer (K/V once; Q and dO tiles through a 3-stage ring, so that a tile is requested a
+// whole step before its scores are issued; lse and D of the step's queries through a 2-stage ring of bulk copies; 4-D tensor
+// maps, no multicast), warp 1 MMA issuer, warps 4-11 the element-wise stage (a key row and half of the query columns per thread).
+// Two small kernels frame it: `attn_bwd_prep` (D and the negated lse in the exp2 domain) and `attn_bwd_finish` (dQ fp32 -> bf16).
 // The reference relies on PyTorch SDPA's backward or a Triton kernel with fp32 atomics for dQ
 // (transformer/ops/triton_flash_attn.py:104-201).  Every mbarrier wait is bounded.
 #include <cuda.h>
@@ -32,23 +37,37 @@ using namespace sm100;
 
 constexpr int kBT = 128;   // keys per CTA and queries per step
 constexpr int kBHD = 64;   // head dim
-constexpr int kBwdThreads = 320;  // producer warp, MMA warp, 8 element-wise warps
+constexpr int kBwdThreads = 384;  // warpgroup 0: producer warp, MMA warp, two idle warps; warpgroups 1-2: 8 element-wise warps
 constexpr int kBTile = kBT * kBHD * 2;   // 16 KB: one K, V, Q or dO tile
 constexpr int kBPds = kBT * kBT * 2;     // 32 KB: P^T or dS^T (two 64-column atoms)
 constexpr int kBDq = 8 * 32 * 32 * 4;     // 32 KB: one 32-row x 32-column fp32 box of dQ per element-wise warp
-constexpr int kBwdSmem = 2 * kBTile /*K,V*/ + 2 * 2 * kBTile /*Q,dO x 2 stages*/ + 2 * kBPds + kBDq + 2 * 2 * kBT * 4 /*lse2, D x 2*/ + 256 + 1024;
+constexpr int kBStages = 3;              // Q / dO ring
+// Register reallocation between the warpgroups.  The pool is what the CTA got at launch (three warpgroups at the kernel's
+// register count, 168 under its launch bound), NOT the whole register file: a request beyond it blocks forever, so the
+// launcher refuses to start the kernel unless kBRegsCtl + 2 * kBRegsEw fits into three times the compiled count.
+constexpr int kBRegsCtl = 56, kBRegsEw = 224;
+constexpr int kBwdSmem = 2 * kBTile /*K,V*/ + kBStages * 2 * kBTile /*Q,dO*/ + 2 * kBPds + kBDq + 2 * 2 * kBT * 4 /*lse2, D x 2*/ + 256;
+static_assert(kBwdSmem <= 232448, "shared memory of the attention backward exceeds the per-block limit");
 
 struct AttnBwdParams {
   int B, S, H, Hkv;
   float scale_log2;  // log2(e) / sqrt(hd)
   float scale;       // 1 / sqrt(hd)
-  const float* lse2;  // [B,H,S] lse * log2(e)
+  const float* lse2;  // [B,H,S] -lse * log2(e)
   const float* dsum;  // [B,H,S] rowsum(dO * o)
   float* dq_acc;      // [B,S,H,hd] fp32, zero-initialised
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   int* status;
+  long long* prof;  // optional [16]: cycles per stage of CTA (0,0), see the slot list at the launcher
 };
+
+#define SEG_PROF_ADD(slot, t)              \
+  if (prof_on) {                           \
+    const long long now_ = clock64();      \
+    prof_s[slot] += now_ - t;              \
+    t = now_;                              \
+  }
 
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
@@ -71,29 +90,67 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Eight consecutive queries of one key row: P^T = exp2(S^T * scale - lse2) and dS^T = P^T * (dP^T - D), as packed bf16.
+// nlse holds -lse2, so the exponent argument is one fused multiply-add on a pair; col0 is the first query of the eight and r
+// the key row (kDiag: tile on the diagonal, queries before the key are masked).
+template <bool kDiag>
+__device__ __forceinline__ void bwd_math8(const uint32_t* s8, const uint32_t* dp8, const float* nlse, const float* dsum, uint64_t scale2,
+                                          int col0, int r, bf16x8& pk, bf16x8& dk) {
+  const ulonglong2 la = *reinterpret_cast<const ulonglong2*>(nlse), lb = *reinterpret_cast<const ulonglong2*>(nlse + 4);
+  const ulonglong2 da = *reinterpret_cast<const ulonglong2*>(dsum), db = *reinterpret_cast<const ulonglong2*>(dsum + 4);
+  const uint64_t nl[4] = {la.x, la.y, lb.x, lb.y};
+  const uint64_t dd[4] = {da.x, da.y, db.x, db.y};
+  float pr[8], ds[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float x0, x1;
+    unpack2(fma2(pack2(s8[2 * i], s8[2 * i + 1]), scale2, nl[i]), x0, x1);
+    float p0 = ex2_fast(x0), p1 = ex2_fast(x1);
+    if (kDiag) {  // causal: the query must not precede the key
+      if (col0 + 2 * i < r) p0 = 0.f;
+      if (col0 + 2 * i + 1 < r) p1 = 0.f;
+    }
+    unpack2(mul2(pack2(p0, p1), sub2(pack2(dp8[2 * i], dp8[2 * i + 1]), dd[i])), ds[2 * i], ds[2 * i + 1]);
+    pr[2 * i] = p0;
+    pr[2 * i + 1] = p1;
+  }
+  pk = pack8(pr);
+  dk = pack8(ds);
+}
+
+// Three warpgroups start with 168 registers per thread; the first one (producer, MMA issuer) hands most of its registers to
+// the element-wise warpgroups, whose threads hold 128 accumulator values each (setmaxnreg: 56 + 2 x 224 = 3 x 168).
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const __grid_constant__ CUtensorMap map_dq, AttnBwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base: refuse instead of computing garbage
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 20);
+    return;
+  }
   uint8_t* sK = smem;
   uint8_t* sV = sK + kBTile;
   uint8_t* sQdO = sV + kBTile;            // stage s: Q at s*32K, dO at s*32K + 16K
-  uint8_t* sP = sQdO + 4 * kBTile;
+  uint8_t* sP = sQdO + kBStages * 2 * kBTile;
   uint8_t* sDS = sP + kBPds;
   uint8_t* sDQ = sDS + kBPds;  // [8 warps][32 rows][128 B], 128-byte swizzled boxes of the dQ tile
   float* sLse = reinterpret_cast<float*>(sDQ + kBDq);  // [2][128]
   float* sD = sLse + 2 * kBT;                            // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sD + 2 * kBT);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;   // [2]
-  uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;     // S^T and dP^T are in TMEM
-  uint64_t* pds_full = bars + 6;   // P^T and dS^T are in shared memory (and S^T/dP^T have been read)
-  uint64_t* mma_done = bars + 7;   // dV/dK/dQ MMAs of the step finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* qdo_full = bars + 1;    // [3]
+  uint64_t* qdo_empty = bars + 4;   // [3]
+  uint64_t* stat_full = bars + 7;   // [2]
+  uint64_t* stat_empty = bars + 9;  // [2]
+  uint64_t* s_full = bars + 11;     // S^T and dP^T are in TMEM
+  uint64_t* pds_full = bars + 12;   // P^T and dS^T are in shared memory
+  uint64_t* mma_done = bars + 13;   // dV/dK/dQ MMAs of the step finished
+  uint64_t* s_read = bars + 14;     // S^T and dP^T of the step are in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  long long* prof_s = reinterpret_cast<long long*>(bars + 16);
+  const bool prof_cta = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = p.S / kBT;
@@ -108,13 +165,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     mbar_init(smem_u32(kv_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kBStages; ++s) {
       mbar_init(smem_u32(&qdo_full[s]), 1);
       mbar_init(smem_u32(&qdo_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&stat_full[s]), 1);
+      mbar_init(smem_u32(&stat_empty[s]), 8);
     }
     mbar_init(smem_u32(s_full), 1);
     mbar_init(smem_u32(pds_full), 8);
     mbar_init(smem_u32(mma_done), 1);
+    mbar_init(smem_u32(s_read), 8);
+    for (int i = 0; i < 16; ++i) prof_s[i] = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -131,25 +194,53 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 320, tm_dq = tmem_base + 384;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 320, tm_dq = tmem_base + 384;  // dQ: two accumulators of 64 columns
 
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kBRegsCtl));
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // Two queues, served as their slots become free: the Q / dO tiles (three stages, released by the products that read them)
+    // and the per-query statistics (two stages, released by the element-wise warps).
     if (elect_one()) {
       mbar_expect_tx(smem_u32(kv_full), 2 * kBTile);
       tma_load_4d(smem_u32(sK), &map_k, smem_u32(kv_full), 0, g, jt * kBT, b);
       tma_load_4d(smem_u32(sV), &map_v, smem_u32(kv_full), 0, g, jt * kBT, b);
-      for (int n = 0; n < n_steps; ++n) {
-        const int st = n & 1;
-        if (!mbar_wait(smem_u32(&qdo_empty[st]), ((n >> 1) & 1) ^ 1, ab, 21)) break;
-        const int h = g * group + n / per_head, it = jt + n % per_head;
-        const uint32_t fb = smem_u32(&qdo_full[st]);
-        mbar_expect_tx(fb, 2 * kBTile + 2 * kBT * 4);
-        tma_load_4d(smem_u32(sQdO + st * 2 * kBTile), &map_q, fb, 0, h, it * kBT, b);
-        tma_load_4d(smem_u32(sQdO + st * 2 * kBTile + kBTile), &map_do, fb, 0, h, it * kBT, b);
-        const size_t stat = ((size_t)b * p.H + h) * p.S + (size_t)it * kBT;  // 128 floats: 512-byte aligned
-        bulk_load(smem_u32(sLse + st * kBT), p.lse2 + stat, kBT * 4, fb);
-        bulk_load(smem_u32(sD + st * kBT), p.dsum + stat, kBT * 4, fb);
+      int next_q = 0, next_s = 0;
+      long long t0 = clock64();
+      while (next_q < n_steps || next_s < n_steps) {
+        bool progress = false;
+        if (next_s < n_steps && mbar_test_wait(smem_u32(&stat_empty[next_s & 1]), ((next_s >> 1) & 1) ^ 1)) {
+          const int h = g * group + next_s / per_head, it = jt + next_s % per_head;
+          const size_t stat = ((size_t)b * p.H + h) * p.S + (size_t)it * kBT;  // 128 floats: 512-byte aligned
+          const uint32_t fb = smem_u32(&stat_full[next_s & 1]);
+          mbar_expect_tx(fb, 2 * kBT * 4);
+          bulk_load(smem_u32(sLse + (next_s & 1) * kBT), p.lse2 + stat, kBT * 4, fb);
+          bulk_load(smem_u32(sD + (next_s & 1) * kBT), p.dsum + stat, kBT * 4, fb);
+          ++next_s;
+          progress = true;
+        }
+        if (next_q < n_steps && mbar_test_wait(smem_u32(&qdo_empty[next_q % kBStages]), ((next_q / kBStages) & 1) ^ 1)) {
+          const int st = next_q % kBStages;
+          const int h = g * group + next_q / per_head, it = jt + next_q % per_head;
+          const uint32_t fb = smem_u32(&qdo_full[st]);
+          mbar_expect_tx(fb, 2 * kBTile);
+          tma_load_4d(smem_u32(sQdO + st * 2 * kBTile), &map_q, fb, 0, h, it * kBT, b);
+          tma_load_4d(smem_u32(sQdO + st * 2 * kBTile + kBTile), &map_do, fb, 0, h, it * kBT, b);
+          ++next_q;
+          progress = true;
+        }
+        if (progress) {
+          t0 = clock64();
+        } else {
+          if (*ab.cta_abort != 0) break;
+          if (clock64() - t0 > ab.limit) {
+            *ab.cta_abort = 1;
+            atomicCAS(ab.global_status, 0, 21);
+            break;
+          }
+          __nanosleep(40);
+        }
       }
     }
     __syncwarp();
@@ -160,130 +251,184 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       constexpr uint32_t id_kv = make_idesc_bf16(kBT, kBHD, false, true);   // P^T / dS^T (K-major) x dO / Q (MN-major)
       constexpr uint32_t id_dq = make_idesc_bf16(kBT, kBHD, true, true);    // dS (MN-major view of dS^T) x K (MN-major)
       const uint32_t sk = smem_u32(sK), sv = smem_u32(sV), sp = smem_u32(sP), sds = smem_u32(sDS);
+      // Descriptors advance by adding to their address field (units of 16 bytes); the loops are not unrolled so that this
+      // thread stays within the few registers its warpgroup keeps.
+      const uint64_t d_k = make_smem_desc(sk, 16, 1024), d_v = make_smem_desc(sv, 16, 1024);
       auto issue_s = [&](int n) {
-        const uint32_t sq = smem_u32(sQdO + (n & 1) * 2 * kBTile), sdo = sq + kBTile;
-#pragma unroll
-        for (int k = 0; k < kBHD / 16; ++k)
-          umma_bf16(tm_s, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + k * 32, 16, 1024), id_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < kBHD / 16; ++k)
-          umma_bf16(tm_dp, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + k * 32, 16, 1024), id_s, k > 0);
+        const uint32_t sq = smem_u32(sQdO + (n % kBStages) * 2 * kBTile);
+        const uint64_t d_q = make_smem_desc(sq, 16, 1024), d_do = make_smem_desc(sq + kBTile, 16, 1024);
+#pragma unroll 1
+        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_s, d_k + 2 * k, d_q + 2 * k, id_s, k > 0);
+#pragma unroll 1
+        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_dp, d_v + 2 * k, d_do + 2 * k, id_s, k > 0);
         umma_commit(smem_u32(s_full));
       };
+      const bool prof_on = prof_cta;
+      long long t = prof_on ? clock64() : 0;
       bool ok = mbar_wait(smem_u32(kv_full), 0, ab, 22) && mbar_wait(smem_u32(&qdo_full[0]), 0, ab, 23);
       if (ok) {
         tc_fence_after();
         issue_s(0);
       }
       for (int n = 0; n < n_steps && ok; ++n) {
-        const int st = n & 1;
+        const int st = n % kBStages;
         const uint32_t sq = smem_u32(sQdO + st * 2 * kBTile), sdo = sq + kBTile;
-        if (!mbar_wait(smem_u32(pds_full), n & 1, ab, 24)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
-          const uint64_t a_p = make_smem_desc(sp + (k >> 2) * (kBT * 128) + (k & 3) * 32, 16, 1024);
-          const uint64_t a_ds = make_smem_desc(sds + (k >> 2) * (kBT * 128) + (k & 3) * 32, 16, 1024);
-          umma_bf16(tm_dv, a_p, make_smem_desc(sdo + k * 2048, kBTile, 1024), id_kv, (n > 0 || k > 0) ? 1u : 0u);
-          umma_bf16(tm_dk, a_ds, make_smem_desc(sq + k * 2048, kBTile, 1024), id_kv, (n > 0 || k > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys: 16 key rows of 128 bytes per step
-          umma_bf16(tm_dq, make_smem_desc(sds + k * 2048, kBT * 128, 1024), make_smem_desc(sk + k * 2048, kBTile, 1024), id_dq, k > 0);
-        umma_commit(smem_u32(mma_done));
-        umma_commit(smem_u32(&qdo_empty[st]));
-        if (n + 1 < n_steps) {
-          if (!mbar_wait(smem_u32(&qdo_full[(n + 1) & 1]), ((n + 1) >> 1) & 1, ab, 25)) break;
-          tc_fence_after();
-          issue_s(n + 1);
+        // Two jobs per step, served in the order in which their inputs become ready: the scores of step n+1 (Q / dO landed
+        // and the element-wise warps hold step n's accumulators in registers) and the products of step n (operands written).
+        bool s_done = !(n + 1 < n_steps), p_done = false;
+        const long long t0 = clock64();
+        while (!(s_done && p_done)) {
+          if (!s_done && mbar_test_wait(smem_u32(&qdo_full[(n + 1) % kBStages]), ((n + 1) / kBStages) & 1) &&
+              mbar_test_wait(smem_u32(s_read), n & 1)) {
+            SEG_PROF_ADD(8, t)
+            tc_fence_after();
+            issue_s(n + 1);
+            s_done = true;
+            SEG_PROF_ADD(10, t)
+          }
+          if (!p_done && mbar_test_wait(smem_u32(pds_full), n & 1)) {
+            SEG_PROF_ADD(11, t)
+            tc_fence_after();
+            const uint32_t dq_acc = tm_dq + (n & 1) * kBHD;
+            const uint64_t d_p = make_smem_desc(sp, 16, 1024), d_ds = make_smem_desc(sds, 16, 1024);
+            const uint64_t d_do_mn = make_smem_desc(sdo, kBTile, 1024), d_q_mn = make_smem_desc(sq, kBTile, 1024);
+#pragma unroll 1
+            for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
+              const uint64_t a_off = (uint64_t)(((k >> 2) * (kBT * 128) + (k & 3) * 32) >> 4);
+              umma_bf16(tm_dv, d_p + a_off, d_do_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tm_dk, d_ds + a_off, d_q_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+            }
+            const uint64_t d_ds_mn = make_smem_desc(sds, kBT * 128, 1024), d_k_mn = make_smem_desc(sk, kBTile, 1024);
+#pragma unroll 1
+            for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys: 16 key rows of 128 bytes per step
+              umma_bf16(dq_acc, d_ds_mn + (uint64_t)(k * 128), d_k_mn + (uint64_t)(k * 128), id_dq, k > 0);
+            umma_commit(smem_u32(mma_done));
+            umma_commit(smem_u32(&qdo_empty[st]));
+            p_done = true;
+            SEG_PROF_ADD(12, t)
+          }
+          if (!(s_done && p_done)) {
+            if (*ab.cta_abort != 0) { ok = false; break; }
+            if (clock64() - t0 > ab.limit) {
+              *ab.cta_abort = 1;
+              atomicCAS(ab.global_status, 0, 24);
+              ok = false;
+              break;
+            }
+          }
         }
       }
     }
     __syncwarp();
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kBRegsEw));
     // ------------------------------------------------------------------ element-wise stage
     // Eight warps: warp % 4 selects the TMEM sub-partition (32 key rows), the two warps of a sub-partition split the
     // 128 query columns in halves, so that every scheduler has two warps to alternate between.
     const int sub = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 4) >> 2;
     const int r = sub * 32 + lane;  // key row inside the tile == TMEM lane; also the query row when draining dQ
     const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+    uint8_t* box = sDQ + (warp - 4) * 4096;
     bool ok = true;
+    const bool prof_on = prof_cta && threadIdx.x == 128;
+    long long t = prof_on ? clock64() : 0;
+    // dQ of step m (lane = query row; each half takes 32 of the 64 columns): TMEM -> registers -> this warp's swizzled 4 KB
+    // box in shared memory; after the next proxy fence one TMA reduction adds the box to the fp32 accumulator (other key
+    // tiles add to the same rows).
+    auto stage_dq = [&](int m) {
+      if (m > 0) {  // the previous reduction must have read the box
+        if (lane == 0) bulk_wait_read0();
+        __syncwarp();
+      }
+      uint32_t qv[32];
+      tmem_ld_32x32(tm_dq + (m & 1) * kBHD + lane_addr + half * 32, qv);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 f = make_float4(__uint_as_float(qv[c * 4]) * p.scale, __uint_as_float(qv[c * 4 + 1]) * p.scale,
+                                     __uint_as_float(qv[c * 4 + 2]) * p.scale, __uint_as_float(qv[c * 4 + 3]) * p.scale);
+        *reinterpret_cast<float4*>(box + lane * 128 + ((c ^ (lane & 7)) << 4)) = f;
+      }
+    };
+    auto reduce_dq = [&](int m) {  // by one lane, after the fence that follows stage_dq
+      const int h = g * group + m / per_head, it = jt + m % per_head;
+      tma_reduce_add_4d(&map_dq, smem_u32(box), half * 32, h, it * kBT + sub * 32, b);
+      bulk_commit();
+    };
     for (int n = 0; n < n_steps && ok; ++n) {
-      const int h = g * group + n / per_head, it = jt + n % per_head;
+      const int it = jt + n % per_head;
       const int st = n & 1;
-      // the per-query statistics arrive with the Q / dO tiles of the stage
-      if (!mbar_wait(smem_u32(&qdo_full[st]), (n >> 1) & 1, ab, 28)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&stat_full[st]), (n >> 1) & 1, ab, 28)) { ok = false; break; }
       if (!mbar_wait(smem_u32(s_full), n & 1, ab, 26)) { ok = false; break; }
+      SEG_PROF_ADD(0, t)
       tc_fence_after();
       const bool diag = (it == jt);
       const float* lse_s = sLse + st * kBT;
       const float* d_s = sD + st * kBT;
+      uint32_t sv_[64], dpv[64];  // this thread's key row, 64 query columns of S^T and dP^T
+      tmem_ld_32x32(tm_s + lane_addr + half * 64, sv_);
+      tmem_ld_32x32(tm_s + lane_addr + half * 64 + 32, sv_ + 32);
+      tmem_ld_32x32(tm_dp + lane_addr + half * 64, dpv);
+      tmem_ld_32x32(tm_dp + lane_addr + half * 64 + 32, dpv + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(s_read));  // the next S^T / dP^T may overwrite the accumulators
+      SEG_PROF_ADD(1, t)
+      bf16x8 pk[8], dk8[8];  // P^T and dS^T of the row as packed bf16, held until the operand buffers are free
+      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
+      if (diag) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        uint32_t sv_[32], dpv[32];
-        tmem_ld_32x32(tm_s + lane_addr + c * 32, sv_);
-        tmem_ld_32x32(tm_dp + lane_addr + c * 32, dpv);
-        tmem_ld_wait();
+        for (int c16 = 0; c16 < 8; ++c16)
+          bwd_math8<true>(sv_ + c16 * 8, dpv + c16 * 8, lse_s + half * 64 + c16 * 8, d_s + half * 64 + c16 * 8, scale2,
+                          half * 64 + c16 * 8, r, pk[c16], dk8[c16]);
+      } else {
 #pragma unroll
-        for (int c16 = 0; c16 < 4; ++c16) {
-          float pr[8], ds[8];
-          const int col0 = c * 32 + c16 * 8;  // query index inside the tile
-          const float4 la = *reinterpret_cast<const float4*>(lse_s + col0), lb = *reinterpret_cast<const float4*>(lse_s + col0 + 4);
-          const float4 da = *reinterpret_cast<const float4*>(d_s + col0), db = *reinterpret_cast<const float4*>(d_s + col0 + 4);
-          const float ls[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-          const float dd[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            float pe = ex2_fast(fmaf(__uint_as_float(sv_[c16 * 8 + e]), p.scale_log2, -ls[e]));
-            if (diag && col0 + e < r) pe = 0.f;  // causal: the query must not precede the key
-            pr[e] = pe;
-            ds[e] = pe * (__uint_as_float(dpv[c16 * 8 + e]) - dd[e]);
-          }
-          const int chunk = c * 4 + c16;  // 16-byte chunk index along the row (16 chunks of 8 columns)
-          const int off = (chunk >> 3) * (kBT * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<bf16x8*>(sP + off) = pack8(pr);
-          *reinterpret_cast<bf16x8*>(sDS + off) = pack8(ds);
-        }
+        for (int c16 = 0; c16 < 8; ++c16)
+          bwd_math8<false>(sv_ + c16 * 8, dpv + c16 * 8, lse_s + half * 64 + c16 * 8, d_s + half * 64 + c16 * 8, scale2,
+                           half * 64 + c16 * 8, r, pk[c16], dk8[c16]);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&stat_empty[st]));  // the statistics of the step have been read
+      SEG_PROF_ADD(2, t)
+      if (n > 0) {  // the products of step n-1 have read P^T / dS^T, and its dQ is complete
+        if (!mbar_wait(smem_u32(mma_done), (n - 1) & 1, ab, 27)) { ok = false; break; }
+        tc_fence_after();
+      }
+      SEG_PROF_ADD(3, t)
+#pragma unroll
+      for (int c16 = 0; c16 < 8; ++c16) {
+        const int chunk = half * 8 + c16;  // 16-byte chunk index along the row (16 chunks of 8 columns)
+        const int off = (chunk >> 3) * (kBT * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<bf16x8*>(sP + off) = pk[c16];
+        *reinterpret_cast<bf16x8*>(sDS + off) = dk8[c16];
+      }
+      if (n > 0) stage_dq(n - 1);  // same proxy fence as the operands
       tc_fence_before();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(pds_full));
-      // drain dQ of this step (lane = query row; each half takes 32 of the 64 columns) while the tensor core already
-      // works on the next S^T / dP^T
-      if (!mbar_wait(smem_u32(mma_done), n & 1, ab, 27)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_arrive(smem_u32(pds_full));
+        if (n > 0) reduce_dq(n - 1);  // runs while the tensor core works on this step's products
+      }
+      SEG_PROF_ADD(4, t)
+    }
+    if (ok && n_steps > 0) {
+      if (!mbar_wait(smem_u32(mma_done), (n_steps - 1) & 1, ab, 27)) ok = false;
       tc_fence_after();
-      // This warp's 32 rows x 32 columns of dQ: TMEM -> registers -> its swizzled 4 KB box in shared memory -> one TMA
-      // reduction into the fp32 accumulator (other key tiles add to the same rows).
-      {
-        uint8_t* box = sDQ + (warp - 2) * 4096;
-        if (n > 0) {  // the previous step's reduction must have read the box
-          if (lane == 0) bulk_wait_read0();
-          __syncwarp();
-        }
-        uint32_t qv[32];
-        tmem_ld_32x32(tm_dq + lane_addr + half * 32, qv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float4 f = make_float4(__uint_as_float(qv[c * 4]) * p.scale, __uint_as_float(qv[c * 4 + 1]) * p.scale,
-                                       __uint_as_float(qv[c * 4 + 2]) * p.scale, __uint_as_float(qv[c * 4 + 3]) * p.scale);
-          *reinterpret_cast<float4*>(box + lane * 128 + ((c ^ (lane & 7)) << 4)) = f;
-        }
+      if (ok) {
+        stage_dq(n_steps - 1);
+        tc_fence_before();
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_4d(&map_dq, smem_u32(box), half * 32, h, it * kBT + sub * 32, b);
-          bulk_commit();
-        }
+        if (lane == 0) reduce_dq(n_steps - 1);
       }
-      tc_fence_before();
+      SEG_PROF_ADD(6, t)
     }
     if (ok && n_steps > 0) {
       // dV (first four warps) and dK (the other four) of this key tile: the last mma_done has been waited for above
-      tc_fence_after();
       const size_t row = (((size_t)b * p.S + (size_t)jt * kBT + r) * p.Hkv + g) * kBHD;
       const uint32_t src = half == 0 ? tm_dv : tm_dk;
       __nv_bfloat16* dst = (half == 0 ? p.dv : p.dk) + row;
@@ -302,7 +447,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   }
 
-  if (warp >= 2 && lane == 0) bulk_wait0();  // outstanding dQ reductions of this warp are complete before the CTA ends
+  if (warp >= 4 && lane == 0) bulk_wait0();  // outstanding dQ reductions of this warp are complete before the CTA ends
   if (*cta_abort != 0) {
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
   }
@@ -310,9 +455,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (prof_cta && threadIdx.x == 0) {
+    for (int i = 0; i < 15; ++i) p.prof[i] = prof_s[i];
+    p.prof[15] = n_steps;
+  }
 }
 
-// D[b,h,s] = sum_hd dO * o, lse2 = lse * log2(e).  One warp per (token, head) row.
+// D[b,h,s] = sum_hd dO * o, lse2 = -lse * log2(e).  One warp per (token, head) row.
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                                           const float* __restrict__ lse, float* __restrict__ dsum,
                                                           float* __restrict__ lse2, int B, int S, int H) {
@@ -329,7 +478,7 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16*
     const int sidx = bs % S, b = bs / S;
     const size_t out = ((size_t)b * H + h) * S + sidx;
     dsum[out] = s;
-    lse2[out] = lse[out] * 1.4426950408889634f;
+    lse2[out] = -lse[out] * 1.4426950408889634f;  // negated: the exponent argument becomes one multiply-add
   }
 }
 
@@ -385,8 +534,13 @@ static int make_map_dq_acc(CUtensorMap* map, const float* base, int B, int S, in
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// prof (optional, 16 int64): cycles that one element-wise thread and the MMA thread of the CTA with the longest walk spent per
+// stage - element-wise: 0 wait S^T/dP^T, 1 accumulators -> registers, 2 math, 3 wait previous products, 4 store operands,
+// stage the previous dQ, fence, signal, 6 last dQ; MMA: 8 wait Q/dO, 9 wait accumulators read, 10 issue S^T/dP^T, 11 wait operands,
+// 12 issue dV/dK/dQ; 15 = steps walked.
 int attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-             float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st) {
+             float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st,
+             long long* prof) {
   if (hd != kBHD || S % kBT != 0 || H % Hkv != 0) return -10;
   CUtensorMap mq, mk, mv, mdo, mdq;
   int r = make_map_dq_acc(&mdq, dq_acc, B, S, H, hd);
@@ -398,6 +552,9 @@ int attn_bwd(const void* q, const void* k, const void* v, const void* o, const v
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem) != cudaSuccess) return -2;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, attn_bwd_kernel) != cudaSuccess) return -2;
+    if (kBRegsCtl + 2 * kBRegsEw > 3 * fa.numRegs) return -6;  // the register requests would never be granted
     configured = true;
   }
   const size_t n = (size_t)B * S * H * hd;
@@ -415,6 +572,7 @@ int attn_bwd(const void* q, const void* k, const void* v, const void* o, const v
   p.dk = static_cast<__nv_bfloat16*>(dk);
   p.dv = static_cast<__nv_bfloat16*>(dv);
   p.status = status;
+  p.prof = prof;
   dim3 grid(S / kBT, B * Hkv);
   attn_bwd_kernel<<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, p);
   attn_bwd_finish_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n / 8);

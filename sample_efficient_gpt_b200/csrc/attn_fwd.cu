@@ -2,17 +2,20 @@
 //
 //   S = Q K^T / sqrt(hd) (causal), P = softmax(S), O = P V, LSE = log sum exp(S)      per (batch, query head)
 // q [B,S,H,hd], k/v [B,S,Hkv,hd] (token-major, as written by the qkv post-processing kernel), o like q, lse [B,H,S].
+// Any S >= 1: the last 128-row tile may be partial (TMA fills rows beyond S with zeros; the causal mask keeps their
+// keys out of every real query's softmax; their outputs are not stored).
 //
-// One CTA per (128-query tile, batch, head); two CTAs share an SM (256 TMEM columns and ~100 KB of shared memory
-// each), so one CTA's tensor-core work overlaps the other's softmax.  Roles (192 threads):
-//   warp 0  : TMA producer - Q tile once, then K/V tiles (128 keys) into a 2-stage ring (4-D tensor maps, 128-byte
-//             swizzle, no multicast).
-//   warp 1  : MMA issuer - S(j) = Q K_j^T into TMEM (128x128 fp32), and, once the softmax warps have written P(j) to
-//             shared memory, PV(j) = P(j) V_j into a second TMEM accumulator (128x64 fp32).  V is consumed in place as
-//             an MN-major operand, K as a K-major one.
-//   warps 2-5: softmax - every thread owns one query row: reads S with tcgen05.ld into registers (and releases the S
-//             accumulator at once, so the next Q K^T overlaps the softmax), online max/sum in the exp2 domain, writes
-//             P as bf16 into the swizzled operand layout.  O accumulates in TMEM and is rescaled lazily.
+// One CTA per (128-query tile, batch, head); two CTAs share an SM (256 TMEM columns and ~112 KB of shared memory
+// each), so one CTA's tensor-core work overlaps the other's softmax.  Roles (160 threads, 200 registers each, which
+// together fill the register file: a softmax thread holds a whole row of S):
+//   warp 0   : control - one thread issues the TMA loads (Q tile once, K/V tiles of 128 keys into a 2-stage ring; 4-D
+//              tensor maps, 128-byte swizzle, no multicast) and the MMAs: S(j) = Q K_j^T into TMEM (128x128 fp32) and, once
+//              the softmax warps have written P(j) to shared memory, PV(j) = P(j) V_j into a second accumulator (128x64
+//              fp32).  V is consumed in place as an MN-major operand, K as a K-major one.  The three queues are served
+//              in the order their inputs become ready; Q K^T of tile j+1 runs ahead of the softmax of tile j.
+//   warps 1-4: softmax - every thread owns one query row: reads S with tcgen05.ld into registers (and releases the S
+//              accumulator at once), online max/sum in the exp2 domain with packed fp32-pair arithmetic, writes P as
+//              bf16 into the swizzled operand layout.  O accumulates in TMEM and is rescaled lazily.
 // The reference uses PyTorch SDPA on repeated K/V heads (transformer/attention.py:207-236) or a Triton kernel
 // (transformer/ops/triton_flash_attn.py:12-101).
 // Every mbarrier wait is bounded; on expiry the CTA unwinds, frees TMEM and sets the status word.
@@ -29,10 +32,10 @@ using namespace sm100;
 constexpr int kAQ = 128;   // queries per CTA
 constexpr int kAK = 128;   // keys per tile
 constexpr int kAHD = 64;   // head dim
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 160;  // control warp + four softmax warps
 constexpr int kTileBytes = kAK * kAHD * 2;  // 16 KB: one Q, K or V tile
 constexpr int kPBytes = kAQ * kAK * 2;      // 32 KB: P as two 64-column swizzle atoms
-constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * 2 * kTileBytes /*K,V x 2 stages*/ + kPBytes + 128;  // two CTAs per SM
+constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * 2 * kTileBytes /*K,V x 2 stages*/ + kPBytes + 128 + 128 /*stage timers*/;  // two CTAs per SM
 
 struct AttnParams {
   int B, S, H, Hkv;
@@ -40,7 +43,16 @@ struct AttnParams {
   __nv_bfloat16* o;
   float* lse;
   int* status;
+  long long* prof;  // optional [16]: cycles per stage of CTA (0,0), see the slot list at the launcher
 };
+
+// Stage timers: one thread per role of one CTA adds clock64() differences to shared-memory slots.
+#define SEG_PROF_ADD(slot, t)              \
+  if (prof_on) {                           \
+    const long long now_ = clock64();      \
+    prof_s[slot] += now_ - t;              \
+    t = now_;                              \
+  }
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -48,7 +60,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
+__global__ void __maxnreg__(200)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -70,9 +82,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* pv_empty = bars + 9;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  long long* prof_s = reinterpret_cast<long long*>(bars + 16);
+  const bool prof_cta = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qt = p.S / kAQ;
+  const int n_qt = (p.S + kAQ - 1) / kAQ;  // the last tile may be partial: rows beyond S load as zeros and are never stored
   const int qt = n_qt - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -82,6 +96,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
+    for (int i = 0; i < 16; ++i) prof_s[i] = 0;
     mbar_init(smem_u32(q_full), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
@@ -110,43 +125,70 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_pv = tmem_base + 128;  // columns [128,192): P V
 
   if (warp == 0) {
-    if (elect_one()) {
-      mbar_expect_tx(smem_u32(q_full), kTileBytes);
-      tma_load_4d(smem_u32(sQ), &map_q, smem_u32(q_full), 0, h, qt * kAQ, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1, ab, 11)) break;
-        const uint32_t fb = smem_u32(&kv_full[st]);
-        mbar_expect_tx(fb, 2 * kTileBytes);
-        tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes), &map_k, fb, 0, kvh, j * kAK, b);
-        tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes + kTileBytes), &map_v, fb, 0, kvh, j * kAK, b);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
+    // ------------------------------------------------------------------ control warp: one thread issues the TMA loads and the MMAs
+    // It serves three queues in whatever order their inputs become ready: K/V loads (a stage is free), Q K^T of the next tile
+    // (its K is in, and the softmax warps hold the previous S in registers, so it runs ahead of the softmax), and P V of the
+    // oldest tile whose probabilities are written.
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kAQ, kAK, false, false);   // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_pv = make_idesc_bf16(kAQ, kAHD, false, true);  // P (K-major) x V (MN-major)
-      bool ok = mbar_wait(smem_u32(q_full), 0, ab, 12);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t sk = smem_u32(sKV + st * 2 * kTileBytes), sv = sk + kTileBytes;
-        if (!mbar_wait(smem_u32(&kv_full[st]), (j >> 1) & 1, ab, 13)) break;
-        if (j > 0 && !mbar_wait(smem_u32(s_empty), (j - 1) & 1, ab, 14)) break;
-        tc_fence_after();
+      const bool prof_on = prof_cta;
+      long long t = prof_on ? clock64() : 0;
+      mbar_expect_tx(smem_u32(q_full), kTileBytes);
+      tma_load_4d(smem_u32(sQ), &map_q, smem_u32(q_full), 0, h, qt * kAQ, b);
+      int next_load = 0, next_qk = 0, next_pv = 0;
+      long long t0 = clock64();
+      while (next_pv < n_tiles) {
+        bool progress = false;
+        if (next_load < n_tiles && mbar_test_wait(smem_u32(&kv_empty[next_load & 1]), ((next_load >> 1) & 1) ^ 1)) {
+          const int st = next_load & 1;
+          const uint32_t fb = smem_u32(&kv_full[st]);
+          mbar_expect_tx(fb, 2 * kTileBytes);
+          tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes), &map_k, fb, 0, kvh, next_load * kAK, b);
+          tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes + kTileBytes), &map_v, fb, 0, kvh, next_load * kAK, b);
+          ++next_load;
+          progress = true;
+          SEG_PROF_ADD(8, t)
+        }
+        if (next_qk < next_load && (next_qk > 0 || mbar_test_wait(smem_u32(q_full), 0)) &&
+            mbar_test_wait(smem_u32(&kv_full[next_qk & 1]), (next_qk >> 1) & 1) &&
+            (next_qk == 0 || mbar_test_wait(smem_u32(s_empty), (next_qk - 1) & 1))) {
+          const uint32_t sk = smem_u32(sKV + (next_qk & 1) * 2 * kTileBytes);
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < kAHD / 16; ++k)
-          umma_bf16(tmem_s, make_smem_desc(smem_u32(sQ) + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s, k > 0);
-        umma_commit(smem_u32(s_full));
-        if (!mbar_wait(smem_u32(p_full), j & 1, ab, 15)) break;
-        tc_fence_after();
+          for (int k = 0; k < kAHD / 16; ++k)
+            umma_bf16(tmem_s, make_smem_desc(smem_u32(sQ) + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s, k > 0);
+          umma_commit(smem_u32(s_full));
+          ++next_qk;
+          progress = true;
+          SEG_PROF_ADD(10, t)
+        }
+        if (next_pv < next_qk && mbar_test_wait(smem_u32(p_full), next_pv & 1)) {
+          const int st = next_pv & 1;
+          const uint32_t sv = smem_u32(sKV + st * 2 * kTileBytes) + kTileBytes;
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < kAK / 16; ++k)
-          umma_bf16(tmem_pv, make_smem_desc(smem_u32(sP) + (k >> 2) * (kAQ * 128) + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(sv + k * 2048, kTileBytes, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(smem_u32(pv_full));
-        umma_commit(smem_u32(&kv_empty[st]));
+          for (int k = 0; k < kAK / 16; ++k)
+            umma_bf16(tmem_pv, make_smem_desc(smem_u32(sP) + (k >> 2) * (kAQ * 128) + (k & 3) * 32, 16, 1024),
+                      make_smem_desc(sv + k * 2048, kTileBytes, 1024), idesc_pv, (next_pv > 0 || k > 0) ? 1u : 0u);
+          umma_commit(smem_u32(pv_full));
+          umma_commit(smem_u32(&kv_empty[st]));
+          ++next_pv;
+          progress = true;
+          SEG_PROF_ADD(12, t)
+        }
+        if (progress) {
+          t0 = clock64();
+        } else {
+          if (*ab.cta_abort != 0) break;
+          if (clock64() - t0 > ab.limit) {
+            *ab.cta_abort = 1;
+            atomicCAS(ab.global_status, 0, 12);
+            break;
+          }
+          __nanosleep(20);
+          SEG_PROF_ADD(9, t)
+        }
       }
     }
     __syncwarp();
@@ -160,8 +202,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    const bool prof_on = prof_cta && threadIdx.x == 32;
+    long long t = prof_on ? clock64() : 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (!mbar_wait(smem_u32(s_full), j & 1, ab, 17)) { ok = false; break; }
+      SEG_PROF_ADD(0, t)
       tc_fence_after();
       uint32_t v[kAK];
 #pragma unroll
@@ -170,9 +215,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(s_empty));  // S is in registers: the next Q K^T may overwrite it
+      SEG_PROF_ADD(1, t)
       const bool diag = (j == qt);
-      // four independent chains for the maximum (and for the sum below): a single chain of 128 dependent operations
-      // would leave the two warps that share a scheduler stalled on instruction latency
+      // four independent chains of three-input maxima: a single chain of dependent operations would leave the warps that share
+      // a scheduler stalled on instruction latency
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (diag) {
 #pragma unroll
@@ -180,15 +226,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (e <= r) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
       } else {
 #pragma unroll
-        for (int e = 0; e < kAK; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
+        for (int e = 0; e < kAK; e += 8) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], __uint_as_float(v[e + 2 * c]), __uint_as_float(v[e + 2 * c + 1]));
+        }
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx * p.scale_log2);
       const bool need = (m_new - m_ref) > 8.f;  // true on the first tile (m_ref = -inf)
+      SEG_PROF_ADD(2, t)
       if (j > 0) {  // P V(j-1) must have finished reading the P tile (and O) before either is touched
         if (!mbar_wait(smem_u32(pv_full), (j - 1) & 1, ab, 18)) { ok = false; break; }
         tc_fence_after();
       }
+      SEG_PROF_ADD(3, t)
       if (__any_sync(0xffffffffu, need)) {
         const float m_tgt = need ? m_new : m_ref;
         if (j > 0) {
@@ -207,34 +258,49 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         m_ref = m_tgt;
       }
+      SEG_PROF_ADD(4, t)
       // probabilities -> bf16 operand tile (row r, 16-byte chunk c16 stored at c16 ^ (r & 7) inside its 64-column atom)
-      const float neg_m = -m_ref;
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_ref, -m_ref);
+      uint64_t l2[2] = {0ull, 0ull};  // four running sums as two packed pairs
 #pragma unroll
       for (int c16 = 0; c16 < kAK / 8; ++c16) {
         float pr[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int col = c16 * 8 + e;
-          float pe = ex2_approx(fmaf(__uint_as_float(v[col]), p.scale_log2, neg_m));
-          if (diag && col > r) pe = 0.f;
-          pr[e] = pe;
-          l4[e & 3] += pe;
+        for (int i = 0; i < 4; ++i) {
+          const int col = c16 * 8 + 2 * i;
+          float x0, x1;
+          unpack2(fma2(pack2(v[col], v[col + 1]), scale2, neg_m2), x0, x1);
+          float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+          if (diag) {
+            if (col > r) p0 = 0.f;
+            if (col + 1 > r) p1 = 0.f;
+          }
+          pr[2 * i] = p0;
+          pr[2 * i + 1] = p1;
+          l2[i & 1] = add2(l2[i & 1], pack2(p0, p1));
         }
         uint8_t* atom = sP + (c16 >> 3) * (kAQ * 128) + r * 128;
         *reinterpret_cast<bf16x8*>(atom + (((c16 & 7) ^ (r & 7)) << 4)) = pack8(pr);
       }
-      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      {
+        float a0, a1, a2, a3;
+        unpack2(l2[0], a0, a1);
+        unpack2(l2[1], a2, a3);
+        l += (a0 + a1) + (a2 + a3);
+      }
+      SEG_PROF_ADD(5, t)
       tc_fence_before();
       fence_proxy_async();  // make the P tile visible to the tensor core's shared-memory reads
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(p_full));
+      SEG_PROF_ADD(6, t)
     }
     if (ok && mbar_wait(smem_u32(pv_full), (n_tiles - 1) & 1, ab, 19)) {
       tc_fence_after();
       const float inv = 1.f / l;
       const int row = qt * kAQ + r;
-      __nv_bfloat16* orow = p.o + (((size_t)b * p.S + row) * p.H + h) * kAHD;
+      const bool in_range = row < p.S;  // TMEM loads are warp-collective: every lane loads, only rows of the sequence store
+      __nv_bfloat16* orow = p.o + (((size_t)b * p.S + (in_range ? row : 0)) * p.H + h) * kAHD;
 #pragma unroll
       for (int c = 0; c < kAHD / 32; ++c) {
         uint32_t o[32];
@@ -243,10 +309,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         float f[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(o[e]) * inv;
+        if (in_range) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(orow + c * 32)[q4] = pack8(f + q4 * 8);
+          for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(orow + c * 32)[q4] = pack8(f + q4 * 8);
+        }
       }
-      p.lse[((size_t)b * p.H + h) * p.S + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      if (in_range) p.lse[((size_t)b * p.H + h) * p.S + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      SEG_PROF_ADD(7, t)
     }
   }
 
@@ -257,6 +326,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (prof_cta && threadIdx.x == 0) {
+    for (int i = 0; i < 15; ++i) p.prof[i] = prof_s[i];
+    p.prof[15] = n_tiles;
+  }
 }
 
 // 4-D bf16 tensor map over [B, S, heads, hd] with a {64, 1, 128, 1} box and 128-byte swizzle.
@@ -284,9 +357,12 @@ static int make_map_bshd(CUtensorMap* map, const void* base, int B, int S, int h
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// prof (optional, 16 int64): cycles that one softmax thread and the MMA thread of the CTA with the longest walk spent per
+// stage - softmax: 0 wait S, 1 S -> registers, 2 row max, 3 wait previous P V, 4 rescale O, 5 exp + store P, 6 fence + signal,
+// 7 epilogue; control thread: 8 issue K/V loads, 9 nothing ready, 10 issue Q K^T, 12 issue P V; 15 = key tiles walked.
 int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, int Hkv, int hd, int* status,
-             cudaStream_t st) {
-  if (hd != kAHD || S % kAQ != 0 || H % Hkv != 0) return -10;
+             cudaStream_t st, long long* prof) {
+  if (hd != kAHD || S < 1 || H % Hkv != 0) return -10;
   CUtensorMap mq, mk, mv;
   int r = make_map_bshd(&mq, q, B, S, H, hd);
   if (r == 0) r = make_map_bshd(&mk, k, B, S, Hkv, hd);
@@ -303,7 +379,8 @@ int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   p.o = (__nv_bfloat16*)o;
   p.lse = lse;
   p.status = status;
-  dim3 grid(S / kAQ, B * H);
+  p.prof = prof;
+  dim3 grid((S + kAQ - 1) / kAQ, B * H);
   attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -112,7 +112,13 @@ void gemm_reset_status(int64_t device_index) {
 }
 
 // Causal GQA flash attention forward on the tcgen05 kernel: returns (o, lse).
-std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
+static long long* prof_ptr(const std::optional<Tensor>& prof) {
+  if (!prof.has_value()) return nullptr;
+  TORCH_CHECK(prof->is_cuda() && prof->scalar_type() == at::kLong && prof->is_contiguous() && prof->numel() >= 16, "prof must be a CUDA int64 tensor of at least 16 elements");
+  return reinterpret_cast<long long*>(prof->data_ptr<int64_t>());
+}
+
+std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal, const std::optional<Tensor>& prof) {
   TORCH_CHECK(causal, "only causal attention is implemented");
   for (const Tensor* t : {&q, &k, &v}) {
     TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->dim() == 4, "q/k/v must be contiguous CUDA bf16 [B,S,H,hd]");
@@ -125,14 +131,14 @@ std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor
   Tensor lse = torch::empty({B, H, S}, q.options().dtype(at::kFloat));
   auto& st = device_state(q.device());
   const int rc = seg::attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, S, H, Hkv, hd,
-                               st.status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+                               st.status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream(), prof_ptr(prof));
   TORCH_CHECK(rc == 0, "attn_fwd: unsupported shape or launch failure (code ", rc, ")");
   return {o, lse};
 }
 
 // Backward of fa_fwd on the tcgen05 kernel: returns (dq, dk, dv).
 std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
-                                          const Tensor& lse, bool causal) {
+                                          const Tensor& lse, bool causal, const std::optional<Tensor>& prof) {
   TORCH_CHECK(causal, "only causal attention is implemented");
   for (const Tensor* t : {&d_o, &q, &k, &v, &o}) {
     TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->dim() == 4, "dO/q/k/v/o must be contiguous CUDA bf16 [B,S,H,hd]");
@@ -150,7 +156,7 @@ std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, co
   auto& st = device_state(q.device());
   const int rc = seg::attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(), dq.data_ptr(),
                                dk.data_ptr(), dv.data_ptr(), acc.data_ptr<float>(), dsum.data_ptr<float>(), lse2.data_ptr<float>(), B, S, H,
-                               Hkv, hd, st.status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+                               Hkv, hd, st.status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream(), prof_ptr(prof));
   TORCH_CHECK(rc == 0, "attn_bwd: unsupported shape or launch failure (code ", rc, ")");
   return {dq, dk, dv};
 }
@@ -164,8 +170,9 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("extra_dst") = std::vector<int64_t>(), pybind11::arg("wait_flags") = std::nullopt, pybind11::arg("wait_seq") = 0,
         pybind11::arg("region_rows") = 0, pybind11::arg("route_ptrs") = std::vector<int64_t>(), pybind11::arg("route_rows") = 0,
         pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0);
-  m.def("fa_fwd", &fa_fwd);
-  m.def("fa_bwd", &fa_bwd);
+  m.def("fa_fwd", &fa_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
+  m.def("fa_bwd", &fa_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("lse"),
+        pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
   m.def("gemm_status", &gemm_status);
   m.def("gemm_reset_status", &gemm_reset_status);
 }

@@ -134,13 +134,15 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
 // ---- attn_bwd.cu (tcgen05 flash attention, backward)
 // q, o, d_o, dq [B,S,H,hd]; k, v, dk, dv [B,S,Hkv,hd] bf16; lse [B,H,S] fp32 from the forward.  Scratch: dq_acc fp32 like q
 // (zeroed here), dsum and lse2 fp32 [B,H,S].  Causal; hd == 64, S % 128 == 0.  Returns 0 when launched.
+// prof (both kernels, optional): 16 int64 on the device that receive per-stage cycle counts of one CTA.
 int attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-             float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st);
+             float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st,
+             long long* prof = nullptr);
 
 // ---- attn_fwd.cu (tcgen05 flash attention, forward)
-// q [B,S,H,hd], k/v [B,S,Hkv,hd] bf16, o like q, lse fp32 [B,H,S]; causal; hd == 64, S % 128 == 0.
+// q [B,S,H,hd], k/v [B,S,Hkv,hd] bf16, o like q, lse fp32 [B,H,S]; causal; hd == 64, any S >= 1.
 // Returns 0 when launched, a negative code for unsupported shapes.
 int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, int Hkv, int hd, int* status,
-             cudaStream_t st);
+             cudaStream_t st, long long* prof = nullptr);
 
 }  // namespace seg

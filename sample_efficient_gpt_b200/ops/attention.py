@@ -1,7 +1,7 @@
 """Causal GQA attention on CUDA tensors: forward returning (O, ctx) and backward from ctx.
 
 Two implementations: this package's tcgen05 flash-attention kernels (``fa_fwd`` / ``fa_bwd`` in the extension; causal,
-head_dim 64, sequence a multiple of 128) and the library path: PyTorch's fused SDPA (flash / cuDNN backend, native GQA),
+head_dim 64; the backward needs a sequence that is a multiple of 128) and the library path: PyTorch's fused SDPA (flash / cuDNN backend, native GQA),
 differentiated through a private autograd tape so that the caller needs no autograd graph of its own.
 ``SEGPT_ATTN_IMPL=native|library|auto``: ``auto`` (default) runs the native forward where no backward follows
 (evaluation, generation) and the library pair in training, where the library is currently the faster of the two;
@@ -37,7 +37,8 @@ def _native_ok(q: Tensor, k: Tensor, v: Tensor, q_start: int, for_backward: bool
     if for_backward and (impl != "native" or not ops.has_kernel("fa_bwd")):
         return False  # the library backward needs the library forward's tape
     hd = q.size(-1)
-    return (q.dtype == torch.bfloat16 and hd == 64 and q_start == 0 and q.size(1) == k.size(1) and q.size(1) % 128 == 0
+    seq_ok = (q.size(1) % 128 == 0) if for_backward else True  # the backward kernel needs whole 128-row tiles
+    return (q.dtype == torch.bfloat16 and hd == 64 and q_start == 0 and q.size(1) == k.size(1) and seq_ok
             and q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
 
 

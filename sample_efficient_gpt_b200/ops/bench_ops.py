@@ -115,10 +115,17 @@ def bench_attention(a):
 
         t_n = timeit(lambda: ops.attention_fwd(q, k, v, True, 0, for_backward=False), a.iters)
         out.update({"native_fwd_ms": t_n, "native_fwd_tflops": fl_f / t_n})
+        print(json.dumps(out), flush=True)
         if ops.has_kernel("fa_bwd"):
             o_n, lse_n = ops.ext().fa_fwd(q, k, v, True)
             t_nb = timeit(lambda: ops.ext().fa_bwd(do, q, k, v, o_n, lse_n, True), a.iters)
             out.update({"native_bwd_ms": t_nb, "native_bwd_tflops": 2.5 * fl_f / t_nb})
+            # per-stage cycles of the CTA with the longest walk (slot meanings: csrc/attn_fwd.cu, csrc/attn_bwd.cu)
+            pf = torch.zeros(16, dtype=torch.int64, device="cuda")
+            pb = torch.zeros(16, dtype=torch.int64, device="cuda")
+            ops.ext().fa_fwd(q, k, v, True, pf)
+            ops.ext().fa_bwd(do, q, k, v, o_n, lse_n, True, pb)
+            out["fwd_stage_cycles"], out["bwd_stage_cycles"] = pf.tolist(), pb.tolist()
         out["status"] = G.status()
     print(json.dumps(out))
 

@@ -166,7 +166,7 @@ def test_multi_tensor_adamw_ema_cast():
         assert torch.equal(d_, p.to(torch.bfloat16))
 
 
-@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 6, 2), (2, 1024, 3, 1)])
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 6, 2), (2, 1024, 3, 1), (2, 200, 4, 2), (1, 77, 2, 1), (3, 129, 2, 2)])
 def test_native_attention_forward(B, S, H, Hkv):
     from sample_efficient_gpt_b200.ops import gemm as G
 
@@ -208,3 +208,24 @@ def test_native_attention_backward(B, S, H, Hkv):
     close(dq, qf.grad, 3e-2, 3e-2, name="dQ")
     close(dk, kf.grad, 3e-2, 3e-2, name="dK")
     close(dv, vf.grad, 3e-2, 3e-2, name="dV")
+
+
+def test_native_attention_stage_timers():
+    """The optional stage timers report the walk length of the profiled CTA and leave the results unchanged."""
+    torch.manual_seed(5)
+    B, S, H, Hkv = 1, 512, 2, 1
+    q = torch.randn(B, S, H, 64, device=DEV).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, 64, device=DEV).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, 64, device=DEV).to(torch.bfloat16)
+    do = torch.randn(B, S, H, 64, device=DEV).to(torch.bfloat16)
+    pf = torch.zeros(16, dtype=torch.int64, device=DEV)
+    pb = torch.zeros(16, dtype=torch.int64, device=DEV)
+    o, lse = _ext().fa_fwd(q, k, v, True)
+    o2, lse2 = _ext().fa_fwd(q, k, v, True, pf)
+    g = _ext().fa_bwd(do, q, k, v, o, lse, True)
+    g2 = _ext().fa_bwd(do, q, k, v, o, lse, True, pb)
+    torch.cuda.synchronize()
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    assert torch.equal(g[1], g2[1]) and torch.equal(g[2], g2[2])  # dQ sums in an order that may differ from run to run
+    assert pf[15].item() == S // 128 and pb[15].item() == (H // Hkv) * (S // 128)
+    assert pf[:8].sum().item() > 0 and pb[:8].sum().item() > 0
