@@ -5,17 +5,19 @@
 // Any S >= 1: the last 128-row tile may be partial (TMA fills rows beyond S with zeros; the causal mask keeps their
 // keys out of every real query's softmax; their outputs are not stored).
 //
-// One CTA per (128-query tile, batch, head); two CTAs share an SM (256 TMEM columns and ~112 KB of shared memory
-// each), so one CTA's tensor-core work overlaps the other's softmax.  Roles (160 threads, 200 registers each, which
-// together fill the register file: a softmax thread holds a whole row of S):
-//   warp 0   : control - one thread issues the TMA loads (Q tile once, K/V tiles of 128 keys into a 2-stage ring; 4-D
-//              tensor maps, 128-byte swizzle, no multicast) and the MMAs: S(j) = Q K_j^T into TMEM (128x128 fp32) and, once
-//              the softmax warps have written P(j) to shared memory, PV(j) = P(j) V_j into a second accumulator (128x64
-//              fp32).  V is consumed in place as an MN-major operand, K as a K-major one.  The three queues are served
-//              in the order their inputs become ready; Q K^T of tile j+1 runs ahead of the softmax of tile j.
-//   warps 1-4: softmax - every thread owns one query row: reads S with tcgen05.ld into registers (and releases the S
-//              accumulator at once), online max/sum in the exp2 domain with packed fp32-pair arithmetic, writes P as
-//              bf16 into the swizzled operand layout.  O accumulates in TMEM and is rescaled lazily.
+// One CTA per (256 queries, batch, head), one CTA per SM.  The 256 queries are two tiles of 128 rows, each with its own
+// score accumulator S (128x128 fp32) and output accumulator O (128x64 fp32) in TMEM and its own softmax warpgroup; both
+// tiles walk over the same K/V tiles, which are loaded once.  While one warpgroup runs the softmax of its tile, the tensor
+// core computes the other tile's products.  Roles (384 threads in three warpgroups):
+//   warpgroup 0, warps 0 and 1: control - one thread per query tile x issues its MMAs: S_x(j) = Q_x K_j^T and, once the
+//              warpgroup has written P_x(j) to shared memory, O_x += P_x(j) V_j; the thread of warp 0 also issues the TMA
+//              loads (both Q tiles once, K/V tiles of 128 keys into a 3-stage ring; 4-D tensor maps, 128-byte swizzle, no
+//              multicast).  V is consumed in place as an MN-major operand,
+//              K as a K-major one.  The queues are served in the order their inputs become ready; Q K^T of tile j+1 runs
+//              ahead of the softmax of tile j.  The warpgroup gives most of its registers to the other two (setmaxnreg).
+//   warpgroups 1, 2: softmax of query tile 0 / 1 - every thread owns one query row: reads S with tcgen05.ld into registers
+//              (and releases the accumulator at once), online max/sum in the exp2 domain with packed fp32-pair arithmetic,
+//              writes P as bf16 into the swizzled operand layout.  O is rescaled lazily.
 // The reference uses PyTorch SDPA on repeated K/V heads (transformer/attention.py:207-236) or a Triton kernel
 // (transformer/ops/triton_flash_attn.py:12-101).
 // Every mbarrier wait is bounded; on expiry the CTA unwinds, frees TMEM and sets the status word.
@@ -29,13 +31,18 @@ namespace seg {
 
 using namespace sm100;
 
-constexpr int kAQ = 128;   // queries per CTA
+constexpr int kAQ = 128;   // queries per softmax warpgroup (two per CTA)
 constexpr int kAK = 128;   // keys per tile
 constexpr int kAHD = 64;   // head dim
-constexpr int kAttnThreads = 160;  // control warp + four softmax warps
+constexpr int kAStages = 3;  // K/V ring
+constexpr int kAttnThreads = 384;
 constexpr int kTileBytes = kAK * kAHD * 2;  // 16 KB: one Q, K or V tile
 constexpr int kPBytes = kAQ * kAK * 2;      // 32 KB: P as two 64-column swizzle atoms
-constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * 2 * kTileBytes /*K,V x 2 stages*/ + kPBytes + 128 + 128 /*stage timers*/;  // two CTAs per SM
+constexpr int kAttnSmem = 2 * kTileBytes /*Q x 2*/ + kAStages * 2 * kTileBytes /*K,V*/ + 2 * kPBytes + 256;
+// Register reallocation between the warpgroups.  The pool is what the CTA got at launch (three warpgroups at the kernel's
+// register count, 168 under its launch bound): a request beyond it blocks forever, so the launcher refuses to start the
+// kernel unless kARegsCtl + 2 * kARegsSm fits into three times the compiled count.
+constexpr int kARegsCtl = 56, kARegsSm = 224;
 
 struct AttnParams {
   int B, S, H, Hkv;
@@ -60,7 +67,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__global__ void __maxnreg__(200)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -68,45 +75,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (threadIdx.x == 0) atomicCAS(p.status, 0, 10);
     return;
   }
-  uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + kTileBytes;            // stage s: K at s*32K, V at s*32K + 16K
-  uint8_t* sP = sKV + 4 * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+  uint8_t* sQ = smem;                        // tile x at x*16K
+  uint8_t* sKV = sQ + 2 * kTileBytes;        // stage s: K at s*32K, V at s*32K + 16K
+  uint8_t* sP = sKV + kAStages * 2 * kTileBytes;  // tile x at x*32K
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_empty = bars + 6;
-  uint64_t* p_full = bars + 7;
-  uint64_t* pv_full = bars + 8;
-  uint64_t* pv_empty = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_full = bars + 1;   // [3]
+  uint64_t* kv_empty = bars + 4;  // [3]
+  uint64_t* s_full = bars + 7;    // [2] per query tile
+  uint64_t* s_empty = bars + 9;   // [2]
+  uint64_t* p_full = bars + 11;   // [2]
+  uint64_t* pv_full = bars + 13;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   long long* prof_s = reinterpret_cast<long long*>(bars + 16);
   const bool prof_cta = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qt = (p.S + kAQ - 1) / kAQ;  // the last tile may be partial: rows beyond S load as zeros and are never stored
-  const int qt = n_qt - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
+  const int n_qb = (p.S + 2 * kAQ - 1) / (2 * kAQ);
+  const int qb = n_qb - 1 - (int)blockIdx.x;  // heavy (late) query blocks first
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int kvh = h / (p.H / p.Hkv);
-  const int n_tiles = qt + 1;  // causal: key tiles 0..qt
+  // causal: query tile x (rows (2 qb + x) * 128 ...) walks over key tiles 0 .. 2 qb + x; a second tile that starts beyond the
+  // sequence does not exist
+  const int n_a = 2 * qb + 1;
+  const int n_b = ((2 * qb + 1) * kAQ < p.S) ? 2 * qb + 2 : 0;
   const AbortState ab{cta_abort, p.status};
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     for (int i = 0; i < 16; ++i) prof_s[i] = 0;
     mbar_init(smem_u32(q_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kAStages; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), n_b > 0 ? 2 : 1);  // released by the P V of every tile that reads the stage
     }
-    mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_empty), 4);
-    mbar_init(smem_u32(p_full), 4);
-    mbar_init(smem_u32(pv_full), 1);
-    mbar_init(smem_u32(pv_empty), 4);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&s_full[x]), 1);
+      mbar_init(smem_u32(&s_empty[x]), 4);
+      mbar_init(smem_u32(&p_full[x]), 4);
+      mbar_init(smem_u32(&pv_full[x]), 1);
+    }
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -114,34 +124,43 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   if (warp == 0) {
     __syncwarp();
-    tmem_alloc(smem_u32(tmem_slot), 256);
+    tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;         // columns [0,128): S
-  const uint32_t tmem_pv = tmem_base + 128;  // columns [128,192): P V
+  const uint32_t tmem_base = *tmem_slot;  // columns [0,256): S of tile 0 / 1; [256,384): O of tile 0 / 1
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ control warp: one thread issues the TMA loads and the MMAs
-    // It serves three queues in whatever order their inputs become ready: K/V loads (a stage is free), Q K^T of the next tile
-    // (its K is in, and the softmax warps hold the previous S in registers, so it runs ahead of the softmax), and P V of the
-    // oldest tile whose probabilities are written.
-    if (elect_one()) {
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kARegsCtl));
+    // ------------------------------------------------------------------ control threads: warp x serves query tile x
+    // (warp 0 also the loads); two warps so that the issue work of the two tiles sits on two schedulers
+    const int x = warp;
+    const int n_x = x == 0 ? n_a : n_b;
+    if (warp < 2 && (x == 0 || n_x > 0) && elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kAQ, kAK, false, false);   // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_pv = make_idesc_bf16(kAQ, kAHD, false, true);  // P (K-major) x V (MN-major)
-      const bool prof_on = prof_cta;
+      const bool prof_on = prof_cta && x == 0;
       long long t = prof_on ? clock64() : 0;
-      mbar_expect_tx(smem_u32(q_full), kTileBytes);
-      tma_load_4d(smem_u32(sQ), &map_q, smem_u32(q_full), 0, h, qt * kAQ, b);
+      const int n_load = x == 0 ? (n_a > n_b ? n_a : n_b) : 0;
+      if (x == 0) {
+        mbar_expect_tx(smem_u32(q_full), 2 * kTileBytes);
+        tma_load_4d(smem_u32(sQ), &map_q, smem_u32(q_full), 0, h, 2 * qb * kAQ, b);
+        tma_load_4d(smem_u32(sQ) + kTileBytes, &map_q, smem_u32(q_full), 0, h, (2 * qb + 1) * kAQ, b);  // zeros beyond the sequence
+      }
+      const uint64_t d_q = make_smem_desc(smem_u32(sQ) + x * kTileBytes, 16, 1024);
+      const uint64_t d_p = make_smem_desc(smem_u32(sP) + x * kPBytes, 16, 1024);
+      const uint32_t t_s = tmem_base + x * kAK, t_o = tmem_base + 2 * kAK + x * kAHD;
+      const uint32_t b_s_full = smem_u32(&s_full[x]), b_s_empty = smem_u32(&s_empty[x]), b_p_full = smem_u32(&p_full[x]),
+                     b_pv_full = smem_u32(&pv_full[x]);
       int next_load = 0, next_qk = 0, next_pv = 0;
+      bool q_in = false;
       long long t0 = clock64();
-      while (next_pv < n_tiles) {
+      while (next_pv < n_x || next_load < n_load) {
         bool progress = false;
-        if (next_load < n_tiles && mbar_test_wait(smem_u32(&kv_empty[next_load & 1]), ((next_load >> 1) & 1) ^ 1)) {
-          const int st = next_load & 1;
+        if (next_load < n_load && mbar_test_wait(smem_u32(&kv_empty[next_load % kAStages]), ((next_load / kAStages) & 1) ^ 1)) {
+          const int st = next_load % kAStages;
           const uint32_t fb = smem_u32(&kv_full[st]);
           mbar_expect_tx(fb, 2 * kTileBytes);
           tma_load_4d(smem_u32(sKV + st * 2 * kTileBytes), &map_k, fb, 0, kvh, next_load * kAK, b);
@@ -150,28 +169,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           progress = true;
           SEG_PROF_ADD(8, t)
         }
-        if (next_qk < next_load && (next_qk > 0 || mbar_test_wait(smem_u32(q_full), 0)) &&
-            mbar_test_wait(smem_u32(&kv_full[next_qk & 1]), (next_qk >> 1) & 1) &&
-            (next_qk == 0 || mbar_test_wait(smem_u32(s_empty), (next_qk - 1) & 1))) {
-          const uint32_t sk = smem_u32(sKV + (next_qk & 1) * 2 * kTileBytes);
+        if (!q_in) q_in = mbar_test_wait(smem_u32(q_full), 0);
+        if (next_qk < n_x && q_in && mbar_test_wait(smem_u32(&kv_full[next_qk % kAStages]), (next_qk / kAStages) & 1) &&
+            (next_qk == 0 || mbar_test_wait(b_s_empty, (next_qk - 1) & 1))) {
+          const uint64_t d_k = make_smem_desc(smem_u32(sKV + (next_qk % kAStages) * 2 * kTileBytes), 16, 1024);
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < kAHD / 16; ++k)
-            umma_bf16(tmem_s, make_smem_desc(smem_u32(sQ) + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s, k > 0);
-          umma_commit(smem_u32(s_full));
+          for (int k = 0; k < kAHD / 16; ++k) umma_bf16(t_s, d_q + 2 * k, d_k + 2 * k, idesc_s, k > 0);
+          umma_commit(b_s_full);
           ++next_qk;
           progress = true;
           SEG_PROF_ADD(10, t)
         }
-        if (next_pv < next_qk && mbar_test_wait(smem_u32(p_full), next_pv & 1)) {
-          const int st = next_pv & 1;
-          const uint32_t sv = smem_u32(sKV + st * 2 * kTileBytes) + kTileBytes;
+        if (next_pv < next_qk && mbar_test_wait(b_p_full, next_pv & 1)) {
+          const int st = next_pv % kAStages;
+          const uint64_t d_v = make_smem_desc(smem_u32(sKV + st * 2 * kTileBytes) + kTileBytes, kTileBytes, 1024);
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kAK / 16; ++k)
-            umma_bf16(tmem_pv, make_smem_desc(smem_u32(sP) + (k >> 2) * (kAQ * 128) + (k & 3) * 32, 16, 1024),
-                      make_smem_desc(sv + k * 2048, kTileBytes, 1024), idesc_pv, (next_pv > 0 || k > 0) ? 1u : 0u);
-          umma_commit(smem_u32(pv_full));
+            umma_bf16(t_o, d_p + (uint64_t)(((k >> 2) * (kAQ * 128) + (k & 3) * 32) >> 4), d_v + (uint64_t)(k * 128), idesc_pv,
+                      (next_pv > 0 || k > 0) ? 1u : 0u);
+          umma_commit(b_pv_full);
           umma_commit(smem_u32(&kv_empty[st]));
           ++next_pv;
           progress = true;
@@ -186,26 +204,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             atomicCAS(ab.global_status, 0, 12);
             break;
           }
-          __nanosleep(20);
           SEG_PROF_ADD(9, t)
         }
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ softmax warps: one query row per thread
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kARegsSm));
+    // ------------------------------------------------------------------ softmax warpgroups: one query row per thread
     // O accumulates in TMEM across key tiles.  It is rescaled only when the running maximum grew by more than 2^8
     // since the last rescale (probabilities are then at most 256, harmless for bf16 operands and fp32 sums), which
     // after the first tiles is rare; the decision is taken per warp because TMEM loads/stores are warp-collective.
+    const int x = (warp >> 2) - 1;  // query tile of this warpgroup
+    const int n_tiles = x == 0 ? n_a : n_b;
+    const int qt = 2 * qb + x;
     const int sub = warp & 3;
     const int r = sub * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+    const uint32_t tmem_s = tmem_base + x * kAK, tmem_pv = tmem_base + 2 * kAK + x * kAHD;
+    uint8_t* sPx = sP + x * kPBytes;
+    const uint32_t b_s_full = smem_u32(&s_full[x]), b_s_empty = smem_u32(&s_empty[x]), b_p_full = smem_u32(&p_full[x]),
+                   b_pv_full = smem_u32(&pv_full[x]);
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    const bool prof_on = prof_cta && threadIdx.x == 32;
+    const bool prof_on = prof_cta && threadIdx.x == 128;
     long long t = prof_on ? clock64() : 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(smem_u32(s_full), j & 1, ab, 17)) { ok = false; break; }
+      if (!mbar_wait(b_s_full, j & 1, ab, 17)) { ok = false; break; }
       SEG_PROF_ADD(0, t)
       tc_fence_after();
       uint32_t v[kAK];
@@ -214,7 +239,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(s_empty));  // S is in registers: the next Q K^T may overwrite it
+      if (lane == 0) mbar_arrive(b_s_empty);  // S is in registers: the next Q K^T may overwrite it
       SEG_PROF_ADD(1, t)
       const bool diag = (j == qt);
       // four independent chains of three-input maxima: a single chain of dependent operations would leave the warps that share
@@ -236,7 +261,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const bool need = (m_new - m_ref) > 8.f;  // true on the first tile (m_ref = -inf)
       SEG_PROF_ADD(2, t)
       if (j > 0) {  // P V(j-1) must have finished reading the P tile (and O) before either is touched
-        if (!mbar_wait(smem_u32(pv_full), (j - 1) & 1, ab, 18)) { ok = false; break; }
+        if (!mbar_wait(b_pv_full, (j - 1) & 1, ab, 18)) { ok = false; break; }
         tc_fence_after();
       }
       SEG_PROF_ADD(3, t)
@@ -279,7 +304,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           pr[2 * i + 1] = p1;
           l2[i & 1] = add2(l2[i & 1], pack2(p0, p1));
         }
-        uint8_t* atom = sP + (c16 >> 3) * (kAQ * 128) + r * 128;
+        uint8_t* atom = sPx + (c16 >> 3) * (kAQ * 128) + r * 128;
         *reinterpret_cast<bf16x8*>(atom + (((c16 & 7) ^ (r & 7)) << 4)) = pack8(pr);
       }
       {
@@ -292,10 +317,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before();
       fence_proxy_async();  // make the P tile visible to the tensor core's shared-memory reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(p_full));
+      if (lane == 0) mbar_arrive(b_p_full);
       SEG_PROF_ADD(6, t)
     }
-    if (ok && mbar_wait(smem_u32(pv_full), (n_tiles - 1) & 1, ab, 19)) {
+    if (ok && n_tiles > 0 && mbar_wait(b_pv_full, (n_tiles - 1) & 1, ab, 19)) {
       tc_fence_after();
       const float inv = 1.f / l;
       const int row = qt * kAQ + r;
@@ -325,10 +350,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
   if (prof_cta && threadIdx.x == 0) {
     for (int i = 0; i < 15; ++i) p.prof[i] = prof_s[i];
-    p.prof[15] = n_tiles;
+    p.prof[15] = n_a;
   }
 }
 
@@ -357,9 +382,9 @@ static int make_map_bshd(CUtensorMap* map, const void* base, int B, int S, int h
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-// prof (optional, 16 int64): cycles that one softmax thread and the MMA thread of the CTA with the longest walk spent per
-// stage - softmax: 0 wait S, 1 S -> registers, 2 row max, 3 wait previous P V, 4 rescale O, 5 exp + store P, 6 fence + signal,
-// 7 epilogue; control thread: 8 issue K/V loads, 9 nothing ready, 10 issue Q K^T, 12 issue P V; 15 = key tiles walked.
+// prof (optional, 16 int64): cycles that one softmax thread (first query tile) and the control thread of the CTA with the
+// longest walk spent per stage - softmax: 0 wait S, 1 S -> registers, 2 row max, 3 wait previous P V, 4 rescale O, 5 exp + store P, 6 fence + signal,
+// 7 epilogue; control thread: 8 issue K/V loads, 9 nothing ready, 10 issue Q K^T, 12 issue P V; 15 = key tiles walked by the first query tile.
 int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, int Hkv, int hd, int* status,
              cudaStream_t st, long long* prof) {
   if (hd != kAHD || S < 1 || H % Hkv != 0) return -10;
@@ -371,6 +396,9 @@ int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) return -2;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, attn_fwd_kernel) != cudaSuccess) return -2;
+    if (kARegsCtl + 2 * kARegsSm > 3 * fa.numRegs) return -6;  // the register requests would never be granted
     configured = true;
   }
   AttnParams p;
@@ -380,7 +408,7 @@ int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   p.lse = lse;
   p.status = status;
   p.prof = prof;
-  dim3 grid((S + kAQ - 1) / kAQ, B * H);
+  dim3 grid((S + 2 * kAQ - 1) / (2 * kAQ), B * H);
   attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

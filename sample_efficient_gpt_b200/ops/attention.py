@@ -3,9 +3,11 @@
 Two implementations: this package's tcgen05 flash-attention kernels (``fa_fwd`` / ``fa_bwd`` in the extension; causal,
 head_dim 64; the backward needs a sequence that is a multiple of 128) and the library path: PyTorch's fused SDPA (flash / cuDNN backend, native GQA),
 differentiated through a private autograd tape so that the caller needs no autograd graph of its own.
-``SEGPT_ATTN_IMPL=native|library|auto``: ``auto`` (default) runs the native forward where no backward follows
-(evaluation, generation) and the library pair in training, where the library is currently the faster of the two;
-``native`` trains on the tcgen05 forward + backward kernels.
+``SEGPT_ATTN_IMPL=native|library|auto``: ``auto`` (default) runs the native kernels wherever they apply - in training the
+tcgen05 forward + backward pair (inside the training step it is within a few percent of the library pair, which needs
+transposed copies of its operands and result), in evaluation and generation the forward - and the library elsewhere
+(head_dim other than 64, decoding against a cache, training sequences that are not a multiple of 128);
+``native`` raises where ``auto`` would fall back because the kernels are missing; ``library`` forces the library pair.
 """
 
 from __future__ import annotations
@@ -34,7 +36,7 @@ def _native_ok(q: Tensor, k: Tensor, v: Tensor, q_start: int, for_backward: bool
         if impl == "native":
             raise RuntimeError("SEGPT_ATTN_IMPL=native but the flash-attention kernels are not built")
         return False
-    if for_backward and (impl != "native" or not ops.has_kernel("fa_bwd")):
+    if for_backward and not ops.has_kernel("fa_bwd"):
         return False  # the library backward needs the library forward's tape
     hd = q.size(-1)
     seq_ok = (q.size(1) % 128 == 0) if for_backward else True  # the backward kernel needs whole 128-row tiles

@@ -227,5 +227,6 @@ def test_native_attention_stage_timers():
     torch.cuda.synchronize()
     assert torch.equal(o, o2) and torch.equal(lse, lse2)
     assert torch.equal(g[1], g2[1]) and torch.equal(g[2], g2[2])  # dQ sums in an order that may differ from run to run
-    assert pf[15].item() == S // 128 and pb[15].item() == (H // Hkv) * (S // 128)
+    # the forward's profiled CTA holds the last two query tiles and reports the walk of the first of them
+    assert pf[15].item() == S // 128 - 1 and pb[15].item() == (H // Hkv) * (S // 128)
     assert pf[:8].sum().item() > 0 and pb[:8].sum().item() > 0
