@@ -461,22 +461,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
-// D[b,h,s] = sum_hd dO * o, lse2 = -lse * log2(e).  One warp per (token, head) row.
+// D[b,h,s] = sum_hd dO * o, lse2 = -lse * log2(e).  Eight lanes per (token, head) row of 64 elements: one 16-byte load per
+// lane and tensor, four consecutive rows (512 contiguous bytes) per warp.
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                                           const float* __restrict__ lse, float* __restrict__ dsum,
                                                           float* __restrict__ lse2, int B, int S, int H) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int rows = B * S * H;
-  if (warp >= rows) return;
-  // row index over [B,S,H]; 64 elements per row: 2 per lane
-  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + (size_t)warp * kBHD)[lane];
-  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(d_o + (size_t)warp * kBHD)[lane];
-  const float2 fa = __bfloat1622float2(a), fg = __bfloat1622float2(g);
-  const float s = warp_sum(fa.x * fg.x + fa.y * fg.y);
-  if (lane == 0) {
-    const int h = warp % H, bs = warp / H;
-    const int sidx = bs % S, b = bs / S;
-    const size_t out = ((size_t)b * H + h) * S + sidx;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t row = tid >> 3;  // index over [B,S,H]
+  const int part = (int)(tid & 7);
+  const size_t rows = (size_t)B * S * H;
+  float s = 0.f;
+  if (row < rows) {
+    float fa[8], fg[8];
+    load8<__nv_bfloat16>(o + row * kBHD + part * 8, fa);
+    load8<__nv_bfloat16>(d_o + row * kBHD + part * 8, fg);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s = fmaf(fa[e], fg[e], s);
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if (row < rows && part == 0) {
+    const int h = (int)(row % H);
+    const size_t bs = row / H;
+    const size_t sidx = bs % S, b = bs / S;
+    const size_t out = (b * H + h) * S + sidx;
     dsum[out] = s;
     lse2[out] = -lse[out] * 1.4426950408889634f;  // negated: the exponent argument becomes one multiply-add
   }
@@ -560,7 +569,7 @@ int attn_bwd(const void* q, const void* k, const void* v, const void* o, const v
   const size_t n = (size_t)B * S * H * hd;
   if (cudaMemsetAsync(dq_acc, 0, n * sizeof(float), st) != cudaSuccess) return -4;
   const int rows = B * S * H;
-  attn_bwd_prep_kernel<<<(rows * 32 + 255) / 256, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o),
+  attn_bwd_prep_kernel<<<(unsigned)(((size_t)rows * 8 + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o),
                                                                 lse, dsum, lse2, B, S, H);
   AttnBwdParams p;
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;

@@ -105,9 +105,19 @@ def bench_attention(a):
     def bwd():
         ops.attention_bwd(do, q, k, v, state["o"], state["ctx"], True, 0)
 
-    t_f = timeit(fwd, a.iters)
-    fwd()
-    t_b = timeit(lambda: (fwd(), bwd()), a.iters) - t_f
+    import os
+
+    prev = os.environ.get("SEGPT_ATTN_IMPL")
+    os.environ["SEGPT_ATTN_IMPL"] = "library"  # the dispatch's default is the native pair
+    try:
+        t_f = timeit(fwd, a.iters)
+        fwd()
+        t_b = timeit(lambda: (fwd(), bwd()), a.iters) - t_f
+    finally:
+        if prev is None:
+            del os.environ["SEGPT_ATTN_IMPL"]
+        else:
+            os.environ["SEGPT_ATTN_IMPL"] = prev
     out = {"op": "attention", "seq": S, "library_fwd_ms": t_f, "library_fwd_tflops": fl_f / t_f, "library_bwd_ms": t_b,
            "library_bwd_tflops": 2.5 * fl_f / t_b}
     if ops.has_kernel("fa_fwd"):
