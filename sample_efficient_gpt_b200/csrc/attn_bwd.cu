@@ -5,16 +5,16 @@
 //   dV = P^T dO,   dP = dO V^T,   dS = P * (dP - D),   dQ = dS K / sqrt(hd),   dK = dS^T Q / sqrt(hd).
 //
 // One CTA owns one key tile (128 keys) of one (batch, kv head) and walks over the query heads that share the kv head and
-// the query tiles at or after the key tile (causal).  It works on the *transposed* tiles, so that the thread that owns a
-// TMEM lane (= a key row) writes whole operand rows:
-//   S^T  = K Q^T   and  dP^T = V dO^T      (both K-major x K-major, 128x128 fp32 accumulators in TMEM)
-//   P^T, dS^T -> bf16 into shared memory in the 128-byte-swizzled K-major operand layout
-//   dV  += P^T  dO   (A K-major,  B = dO as MN-major operand, accumulates in TMEM over the whole walk)
+// the query tiles at or after the key tile (causal).  Per step (one query tile of one head):
+//   S  = Q K^T   and  dP = dO V^T          (both K-major x K-major, 128x128 fp32 accumulators in TMEM; TMEM lane = query, so the
+//                                           thread that owns a lane holds the query's lse and D as two scalars)
+//   P, dS -> bf16 into shared memory, rows = queries, in the 128-byte-swizzled layout
+//   dV  += P^T  dO   (A = the P tile read as an MN-major operand, B = dO as MN-major operand; accumulates in TMEM over the walk)
 //   dK  += dS^T Q    (same shapes, accumulates in TMEM over the whole walk)
-//   dQ_i = dS  K     (A = the dS^T tile read as an MN-major operand, B = K as MN-major; fresh accumulator per tile,
-//                     drained through swizzled shared-memory boxes and TMA reductions (cp.reduce.async.bulk.tensor ... add)
-//                     into an fp32 dQ buffer because other key tiles add to the same rows)
-// TMEM: S^T 128 + dP^T 128 + dV 64 + dK 64 + dQ 2 x 64 = all 512 columns, one CTA per SM.
+//   dQ_i = dS  K     (A = the dS tile as a K-major operand, B = K as MN-major; fresh accumulator per step, drained through
+//                     swizzled shared-memory boxes and TMA reductions (cp.reduce.async.bulk.tensor ... add) into an fp32 dQ
+//                     buffer because other key tiles add to the same rows)
+// TMEM: S 128 + dP 128 + dV 64 + dK 64 + dQ 2 x 64 = all 512 columns, one CTA per SM.
 // Schedule (software pipeline over the steps n of the walk): the element-wise warps copy S^T / dP^T of step n into registers and
 // release them at once, so the tensor core computes S^T / dP^T of step n+1 during the element-wise math of step n; P^T / dS^T
 // are kept in registers until the dV / dK / dQ products of step n-1 have finished reading the operand buffers, so that those
@@ -90,27 +90,23 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// Eight consecutive queries of one key row: P^T = exp2(S^T * scale - lse2) and dS^T = P^T * (dP^T - D), as packed bf16.
-// nlse holds -lse2, so the exponent argument is one fused multiply-add on a pair; col0 is the first query of the eight and r
-// the key row (kDiag: tile on the diagonal, queries before the key are masked).
+// Eight consecutive keys of one query row: P = exp2(S * scale - lse2) and dS = P * (dP - D), as packed bf16.  nlse2 holds
+// (-lse2, -lse2), so the exponent argument is one fused multiply-add on a pair; col0 is the first key of the eight and r the
+// query row (kDiag: tile on the diagonal, keys after the query are masked).
 template <bool kDiag>
-__device__ __forceinline__ void bwd_math8(const uint32_t* s8, const uint32_t* dp8, const float* nlse, const float* dsum, uint64_t scale2,
-                                          int col0, int r, bf16x8& pk, bf16x8& dk) {
-  const ulonglong2 la = *reinterpret_cast<const ulonglong2*>(nlse), lb = *reinterpret_cast<const ulonglong2*>(nlse + 4);
-  const ulonglong2 da = *reinterpret_cast<const ulonglong2*>(dsum), db = *reinterpret_cast<const ulonglong2*>(dsum + 4);
-  const uint64_t nl[4] = {la.x, la.y, lb.x, lb.y};
-  const uint64_t dd[4] = {da.x, da.y, db.x, db.y};
+__device__ __forceinline__ void bwd_math8(const uint32_t* s8, const uint32_t* dp8, uint64_t nlse2, uint64_t d2, uint64_t scale2, int col0, int r,
+                                          bf16x8& pk, bf16x8& dk) {
   float pr[8], ds[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float x0, x1;
-    unpack2(fma2(pack2(s8[2 * i], s8[2 * i + 1]), scale2, nl[i]), x0, x1);
+    unpack2(fma2(pack2(s8[2 * i], s8[2 * i + 1]), scale2, nlse2), x0, x1);
     float p0 = ex2_fast(x0), p1 = ex2_fast(x1);
-    if (kDiag) {  // causal: the query must not precede the key
-      if (col0 + 2 * i < r) p0 = 0.f;
-      if (col0 + 2 * i + 1 < r) p1 = 0.f;
+    if (kDiag) {  // causal: the key must not follow the query
+      if (col0 + 2 * i > r) p0 = 0.f;
+      if (col0 + 2 * i + 1 > r) p1 = 0.f;
     }
-    unpack2(mul2(pack2(p0, p1), sub2(pack2(dp8[2 * i], dp8[2 * i + 1]), dd[i])), ds[2 * i], ds[2 * i + 1]);
+    unpack2(mul2(pack2(p0, p1), sub2(pack2(dp8[2 * i], dp8[2 * i + 1]), d2)), ds[2 * i], ds[2 * i + 1]);
     pr[2 * i] = p0;
     pr[2 * i + 1] = p1;
   }
@@ -120,6 +116,8 @@ __device__ __forceinline__ void bwd_math8(const uint32_t* s8, const uint32_t* dp
 
 // Three warpgroups start with 168 registers per thread; the first one (producer, MMA issuer) hands most of its registers to
 // the element-wise warpgroups, whose threads hold 128 accumulator values each (setmaxnreg: 56 + 2 x 224 = 3 x 168).
+// kProf: with the stage timers (a separate instantiation, so that the production kernel carries none of their branches).
+template <bool kProf>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -150,7 +148,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   long long* prof_s = reinterpret_cast<long long*>(bars + 16);
-  const bool prof_cta = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+  const bool prof_cta = kProf && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = p.S / kBT;
@@ -247,9 +245,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t id_s = make_idesc_bf16(kBT, kBT, false, false);    // K (K-major) x Q (K-major)
-      constexpr uint32_t id_kv = make_idesc_bf16(kBT, kBHD, false, true);   // P^T / dS^T (K-major) x dO / Q (MN-major)
-      constexpr uint32_t id_dq = make_idesc_bf16(kBT, kBHD, true, true);    // dS (MN-major view of dS^T) x K (MN-major)
+      constexpr uint32_t id_s = make_idesc_bf16(kBT, kBT, false, false);    // Q / dO (K-major) x K / V (K-major)
+      constexpr uint32_t id_kv = make_idesc_bf16(kBT, kBHD, true, true);    // P^T / dS^T (MN-major views of P / dS) x dO / Q (MN-major)
+      constexpr uint32_t id_dq = make_idesc_bf16(kBT, kBHD, false, true);   // dS (K-major) x K (MN-major)
       const uint32_t sk = smem_u32(sK), sv = smem_u32(sV), sp = smem_u32(sP), sds = smem_u32(sDS);
       // Descriptors advance by adding to their address field (units of 16 bytes); the loops are not unrolled so that this
       // thread stays within the few registers its warpgroup keeps.
@@ -258,9 +256,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t sq = smem_u32(sQdO + (n % kBStages) * 2 * kBTile);
         const uint64_t d_q = make_smem_desc(sq, 16, 1024), d_do = make_smem_desc(sq + kBTile, 16, 1024);
 #pragma unroll 1
-        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_s, d_k + 2 * k, d_q + 2 * k, id_s, k > 0);
+        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_s, d_q + 2 * k, d_k + 2 * k, id_s, k > 0);
 #pragma unroll 1
-        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_dp, d_v + 2 * k, d_do + 2 * k, id_s, k > 0);
+        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_dp, d_do + 2 * k, d_v + 2 * k, id_s, k > 0);
         umma_commit(smem_u32(s_full));
       };
       const bool prof_on = prof_cta;
@@ -290,18 +288,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             SEG_PROF_ADD(11, t)
             tc_fence_after();
             const uint32_t dq_acc = tm_dq + (n & 1) * kBHD;
-            const uint64_t d_p = make_smem_desc(sp, 16, 1024), d_ds = make_smem_desc(sds, 16, 1024);
+            // P / dS tiles: rows = queries (128 bytes per 64 keys, two 64-key atoms 16 KB apart).  As A^T operands (M = keys, contraction
+            // over queries) they are MN-major: 16 query rows = 2048 bytes per k-step; as the A operand of dQ (M = queries, contraction
+            // over keys) K-major: 16 keys = 32 bytes per k-step inside an atom.
+            const uint64_t d_p_mn = make_smem_desc(sp, kBT * 128, 1024), d_ds_mn = make_smem_desc(sds, kBT * 128, 1024);
             const uint64_t d_do_mn = make_smem_desc(sdo, kBTile, 1024), d_q_mn = make_smem_desc(sq, kBTile, 1024);
 #pragma unroll 1
             for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
-              const uint64_t a_off = (uint64_t)(((k >> 2) * (kBT * 128) + (k & 3) * 32) >> 4);
-              umma_bf16(tm_dv, d_p + a_off, d_do_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
-              umma_bf16(tm_dk, d_ds + a_off, d_q_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tm_dv, d_p_mn + (uint64_t)(k * 128), d_do_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tm_dk, d_ds_mn + (uint64_t)(k * 128), d_q_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
             }
-            const uint64_t d_ds_mn = make_smem_desc(sds, kBT * 128, 1024), d_k_mn = make_smem_desc(sk, kBTile, 1024);
+            const uint64_t d_ds = make_smem_desc(sds, 16, 1024), d_k_mn = make_smem_desc(sk, kBTile, 1024);
 #pragma unroll 1
-            for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys: 16 key rows of 128 bytes per step
-              umma_bf16(dq_acc, d_ds_mn + (uint64_t)(k * 128), d_k_mn + (uint64_t)(k * 128), id_dq, k > 0);
+            for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys
+              umma_bf16(dq_acc, d_ds + (uint64_t)(((k >> 2) * (kBT * 128) + (k & 3) * 32) >> 4), d_k_mn + (uint64_t)(k * 128), id_dq, k > 0);
             umma_commit(smem_u32(mma_done));
             umma_commit(smem_u32(&qdo_empty[st]));
             p_done = true;
@@ -324,11 +324,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kBRegsEw));
     // ------------------------------------------------------------------ element-wise stage
-    // Eight warps: warp % 4 selects the TMEM sub-partition (32 key rows), the two warps of a sub-partition split the
-    // 128 query columns in halves, so that every scheduler has two warps to alternate between.
+    // Eight warps: warp % 4 selects the TMEM sub-partition (32 query rows), the two warps of a sub-partition split the
+    // 128 key columns in halves, so that every scheduler has two warps to alternate between.
     const int sub = warp & 3;
     const int half = (warp - 4) >> 2;
-    const int r = sub * 32 + lane;  // key row inside the tile == TMEM lane; also the query row when draining dQ
+    const int r = sub * 32 + lane;  // query row inside the tile == TMEM lane; the key row in the dV / dK epilogue
     const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
     uint8_t* box = sDQ + (warp - 4) * 4096;
     bool ok = true;
@@ -337,14 +337,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // dQ of step m (lane = query row; each half takes 32 of the 64 columns): TMEM -> registers -> this warp's swizzled 4 KB
     // box in shared memory; after the next proxy fence one TMA reduction adds the box to the fp32 accumulator (other key
     // tiles add to the same rows).
+    uint32_t qv[32];
+    auto load_dq = [&](int m) {  // issue the TMEM load of this warp's 32 x 32 piece of dQ of step m; stage_dq waits for it
+      tmem_ld_32x32(tm_dq + (m & 1) * kBHD + lane_addr + half * 32, qv);
+    };
     auto stage_dq = [&](int m) {
       if (m > 0) {  // the previous reduction must have read the box
         if (lane == 0) bulk_wait_read0();
         __syncwarp();
       }
-      uint32_t qv[32];
-      tmem_ld_32x32(tm_dq + (m & 1) * kBHD + lane_addr + half * 32, qv);
-      tmem_ld_wait();
+      tmem_ld_wait_regs(qv);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const float4 f = make_float4(__uint_as_float(qv[c * 4]) * p.scale, __uint_as_float(qv[c * 4 + 1]) * p.scale,
@@ -365,9 +367,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       SEG_PROF_ADD(0, t)
       tc_fence_after();
       const bool diag = (it == jt);
-      const float* lse_s = sLse + st * kBT;
-      const float* d_s = sD + st * kBT;
-      uint32_t sv_[64], dpv[64];  // this thread's key row, 64 query columns of S^T and dP^T
+      const float nlse = sLse[st * kBT + r], dq_row = sD[st * kBT + r];  // this query's -lse2 and D
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&stat_empty[st]));  // the statistics of the step have been read
+      uint32_t sv_[64], dpv[64];  // this thread's query row, 64 key columns of S and dP
       tmem_ld_32x32(tm_s + lane_addr + half * 64, sv_);
       tmem_ld_32x32(tm_s + lane_addr + half * 64 + 32, sv_ + 32);
       tmem_ld_32x32(tm_dp + lane_addr + half * 64, dpv);
@@ -375,29 +378,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(s_read));  // the next S^T / dP^T may overwrite the accumulators
+      if (lane == 0) mbar_arrive(smem_u32(s_read));  // the next S / dP may overwrite the accumulators
       SEG_PROF_ADD(1, t)
-      bf16x8 pk[8], dk8[8];  // P^T and dS^T of the row as packed bf16, held until the operand buffers are free
-      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
+      bf16x8 pk[8], dk8[8];  // P and dS of the row as packed bf16, held until the operand buffers are free
+      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), nlse2 = pack2(nlse, nlse), d2 = pack2(dq_row, dq_row);
       if (diag) {
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16)
-          bwd_math8<true>(sv_ + c16 * 8, dpv + c16 * 8, lse_s + half * 64 + c16 * 8, d_s + half * 64 + c16 * 8, scale2,
-                          half * 64 + c16 * 8, r, pk[c16], dk8[c16]);
+          bwd_math8<true>(sv_ + c16 * 8, dpv + c16 * 8, nlse2, d2, scale2, half * 64 + c16 * 8, r, pk[c16], dk8[c16]);
       } else {
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16)
-          bwd_math8<false>(sv_ + c16 * 8, dpv + c16 * 8, lse_s + half * 64 + c16 * 8, d_s + half * 64 + c16 * 8, scale2,
-                           half * 64 + c16 * 8, r, pk[c16], dk8[c16]);
+          bwd_math8<false>(sv_ + c16 * 8, dpv + c16 * 8, nlse2, d2, scale2, half * 64 + c16 * 8, r, pk[c16], dk8[c16]);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&stat_empty[st]));  // the statistics of the step have been read
       SEG_PROF_ADD(2, t)
       if (n > 0) {  // the products of step n-1 have read P^T / dS^T, and its dQ is complete
         if (!mbar_wait(smem_u32(mma_done), (n - 1) & 1, ab, 27)) { ok = false; break; }
         tc_fence_after();
       }
       SEG_PROF_ADD(3, t)
+      if (n > 0) load_dq(n - 1);  // in flight during the operand stores
 #pragma unroll
       for (int c16 = 0; c16 < 8; ++c16) {
         const int chunk = half * 8 + c16;  // 16-byte chunk index along the row (16 chunks of 8 columns)
@@ -419,6 +419,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!mbar_wait(smem_u32(mma_done), (n_steps - 1) & 1, ab, 27)) ok = false;
       tc_fence_after();
       if (ok) {
+        load_dq(n_steps - 1);
         stage_dq(n_steps - 1);
         tc_fence_before();
         fence_proxy_async();
@@ -544,8 +545,8 @@ static int make_map_dq_acc(CUtensorMap* map, const float* base, int B, int S, in
 }
 
 // prof (optional, 16 int64): cycles that one element-wise thread and the MMA thread of the CTA with the longest walk spent per
-// stage - element-wise: 0 wait S^T/dP^T, 1 accumulators -> registers, 2 math, 3 wait previous products, 4 store operands,
-// stage the previous dQ, fence, signal, 6 last dQ; MMA: 8 wait Q/dO, 9 wait accumulators read, 10 issue S^T/dP^T, 11 wait operands,
+// stage - element-wise: 0 wait S/dP, 1 accumulators -> registers, 2 math, 3 wait previous products, 4 store operands, stage
+// the previous dQ, fence, signal, issue the dQ reduction (about a third each), 6 last dQ; MMA: 8 wait Q/dO, 9 wait accumulators read, 10 issue S^T/dP^T, 11 wait operands,
 // 12 issue dV/dK/dQ; 15 = steps walked.
 int attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
              float* dq_acc, float* dsum, float* lse2, int B, int S, int H, int Hkv, int hd, int* status, cudaStream_t st,
@@ -560,10 +561,12 @@ int attn_bwd(const void* q, const void* k, const void* v, const void* o, const v
   if (r != 0) return 100 + r;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem) != cudaSuccess) return -2;
-    cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, attn_bwd_kernel) != cudaSuccess) return -2;
-    if (kBRegsCtl + 2 * kBRegsEw > 3 * fa.numRegs) return -6;  // the register requests would never be granted
+    if (cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem) != cudaSuccess) return -2;
+    cudaFuncAttributes fa, fb;
+    if (cudaFuncGetAttributes(&fa, attn_bwd_kernel<false>) != cudaSuccess || cudaFuncGetAttributes(&fb, attn_bwd_kernel<true>) != cudaSuccess) return -2;
+    const int regs = fa.numRegs < fb.numRegs ? fa.numRegs : fb.numRegs;
+    if (kBRegsCtl + 2 * kBRegsEw > 3 * regs) return -6;  // the register requests would never be granted
     configured = true;
   }
   const size_t n = (size_t)B * S * H * hd;
@@ -583,7 +586,10 @@ int attn_bwd(const void* q, const void* k, const void* v, const void* o, const v
   p.status = status;
   p.prof = prof;
   dim3 grid(S / kBT, B * Hkv);
-  attn_bwd_kernel<<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, p);
+  if (prof != nullptr)
+    attn_bwd_kernel<true><<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, p);
+  else
+    attn_bwd_kernel<false><<<grid, kBwdThreads, kBwdSmem, st>>>(mq, mk, mv, mdo, mdq, p);
   attn_bwd_finish_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n / 8);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -67,6 +67,8 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// kProf: with the stage timers (a separate instantiation, so that the production kernel carries none of their branches).
+template <bool kProf>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnParams p) {
@@ -89,7 +91,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   long long* prof_s = reinterpret_cast<long long*>(bars + 16);
-  const bool prof_cta = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+  const bool prof_cta = kProf && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (p.S + 2 * kAQ - 1) / (2 * kAQ);
@@ -395,10 +397,12 @@ int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   if (r != 0) return 100 + r;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) return -2;
-    cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, attn_fwd_kernel) != cudaSuccess) return -2;
-    if (kARegsCtl + 2 * kARegsSm > 3 * fa.numRegs) return -6;  // the register requests would never be granted
+    if (cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess) return -2;
+    cudaFuncAttributes fa, fb;
+    if (cudaFuncGetAttributes(&fa, attn_fwd_kernel<false>) != cudaSuccess || cudaFuncGetAttributes(&fb, attn_fwd_kernel<true>) != cudaSuccess) return -2;
+    const int regs = fa.numRegs < fb.numRegs ? fa.numRegs : fb.numRegs;
+    if (kARegsCtl + 2 * kARegsSm > 3 * regs) return -6;  // the register requests would never be granted
     configured = true;
   }
   AttnParams p;
@@ -409,7 +413,10 @@ int attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   p.status = status;
   p.prof = prof;
   dim3 grid((S + 2 * kAQ - 1) / (2 * kAQ), B * H);
-  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(mq, mk, mv, p);
+  if (prof != nullptr)
+    attn_fwd_kernel<true><<<grid, kAttnThreads, kAttnSmem, st>>>(mq, mk, mv, p);
+  else
+    attn_fwd_kernel<false><<<grid, kAttnThreads, kAttnSmem, st>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
