@@ -240,6 +240,26 @@ __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ void unpack2(uint64_t v, uint32_t& a, uint32_t& b) { asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v)); }
+// 2^x for a pair of values on the FMA and integer pipes instead of the special-function unit: x = n + f with n the nearest
+// integer (magic-number rounding) and |f| <= 0.5, a cubic for 2^f (relative error 8e-5, below the rounding of a bf16 result),
+// n added to the exponent field.  Any x <= 64; values below -126 give 2^-126.
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const uint64_t xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = pack2(12582912.f, 12582912.f);  // 1.5 * 2^23: the sum's low mantissa bits hold the integer
+  const uint64_t t = add2(xc, magic);
+  const uint64_t fr = sub2(xc, sub2(t, magic));
+  uint64_t q = fma2(pack2(0.05508868396282196f, 0.05508868396282196f), fr, pack2(0.24260404706001282f, 0.24260404706001282f));
+  q = fma2(q, fr, pack2(0.6932762265205383f, 0.6932762265205383f));
+  q = fma2(q, fr, pack2(0.9999289512634277f, 0.9999289512634277f));
+  uint32_t tl, th, ql, qh;
+  unpack2(t, tl, th);
+  unpack2(q, ql, qh);
+  p0 = __uint_as_float(ql + (tl << 23));
+  p1 = __uint_as_float(qh + (th << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
