@@ -196,131 +196,131 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kBRegsCtl));
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    // Two queues, served as their slots become free: the Q / dO tiles (three stages, released by the products that read them)
-    // and the per-query statistics (two stages, released by the element-wise warps).
-    if (elect_one()) {
-      mbar_expect_tx(smem_u32(kv_full), 2 * kBTile);
-      tma_load_4d(smem_u32(sK), &map_k, smem_u32(kv_full), 0, g, jt * kBT, b);
-      tma_load_4d(smem_u32(sV), &map_v, smem_u32(kv_full), 0, g, jt * kBT, b);
-      int next_q = 0, next_s = 0;
-      long long t0 = clock64();
-      while (next_q < n_steps || next_s < n_steps) {
-        bool progress = false;
-        if (next_s < n_steps && mbar_test_wait(smem_u32(&stat_empty[next_s & 1]), ((next_s >> 1) & 1) ^ 1)) {
-          const int h = g * group + next_s / per_head, it = jt + next_s % per_head;
-          const size_t stat = ((size_t)b * p.H + h) * p.S + (size_t)it * kBT;  // 128 floats: 512-byte aligned
-          const uint32_t fb = smem_u32(&stat_full[next_s & 1]);
-          mbar_expect_tx(fb, 2 * kBT * 4);
-          bulk_load(smem_u32(sLse + (next_s & 1) * kBT), p.lse2 + stat, kBT * 4, fb);
-          bulk_load(smem_u32(sD + (next_s & 1) * kBT), p.dsum + stat, kBT * 4, fb);
-          ++next_s;
-          progress = true;
-        }
-        if (next_q < n_steps && mbar_test_wait(smem_u32(&qdo_empty[next_q % kBStages]), ((next_q / kBStages) & 1) ^ 1)) {
-          const int st = next_q % kBStages;
-          const int h = g * group + next_q / per_head, it = jt + next_q % per_head;
-          const uint32_t fb = smem_u32(&qdo_full[st]);
-          mbar_expect_tx(fb, 2 * kBTile);
-          tma_load_4d(smem_u32(sQdO + st * 2 * kBTile), &map_q, fb, 0, h, it * kBT, b);
-          tma_load_4d(smem_u32(sQdO + st * 2 * kBTile + kBTile), &map_do, fb, 0, h, it * kBT, b);
-          ++next_q;
-          progress = true;
-        }
-        if (progress) {
-          t0 = clock64();
-        } else {
-          if (*ab.cta_abort != 0) break;
-          if (clock64() - t0 > ab.limit) {
-            *ab.cta_abort = 1;
-            atomicCAS(ab.global_status, 0, 21);
-            break;
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      // Two queues, served as their slots become free: the Q / dO tiles (three stages, released by the products that read them)
+      // and the per-query statistics (two stages, released by the element-wise warps).
+      if (elect_one()) {
+        mbar_expect_tx(smem_u32(kv_full), 2 * kBTile);
+        tma_load_4d(smem_u32(sK), &map_k, smem_u32(kv_full), 0, g, jt * kBT, b);
+        tma_load_4d(smem_u32(sV), &map_v, smem_u32(kv_full), 0, g, jt * kBT, b);
+        int next_q = 0, next_s = 0;
+        long long t0 = clock64();
+        while (next_q < n_steps || next_s < n_steps) {
+          bool progress = false;
+          if (next_s < n_steps && mbar_test_wait(smem_u32(&stat_empty[next_s & 1]), ((next_s >> 1) & 1) ^ 1)) {
+            const int h = g * group + next_s / per_head, it = jt + next_s % per_head;
+            const size_t stat = ((size_t)b * p.H + h) * p.S + (size_t)it * kBT;  // 128 floats: 512-byte aligned
+            const uint32_t fb = smem_u32(&stat_full[next_s & 1]);
+            mbar_expect_tx(fb, 2 * kBT * 4);
+            bulk_load(smem_u32(sLse + (next_s & 1) * kBT), p.lse2 + stat, kBT * 4, fb);
+            bulk_load(smem_u32(sD + (next_s & 1) * kBT), p.dsum + stat, kBT * 4, fb);
+            ++next_s;
+            progress = true;
           }
-          __nanosleep(40);
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t id_s = make_idesc_bf16(kBT, kBT, false, false);    // Q / dO (K-major) x K / V (K-major)
-      constexpr uint32_t id_kv = make_idesc_bf16(kBT, kBHD, true, true);    // P^T / dS^T (MN-major views of P / dS) x dO / Q (MN-major)
-      constexpr uint32_t id_dq = make_idesc_bf16(kBT, kBHD, false, true);   // dS (K-major) x K (MN-major)
-      const uint32_t sk = smem_u32(sK), sv = smem_u32(sV), sp = smem_u32(sP), sds = smem_u32(sDS);
-      // Descriptors advance by adding to their address field (units of 16 bytes); the loops are not unrolled so that this
-      // thread stays within the few registers its warpgroup keeps.
-      const uint64_t d_k = make_smem_desc(sk, 16, 1024), d_v = make_smem_desc(sv, 16, 1024);
-      auto issue_s = [&](int n) {
-        const uint32_t sq = smem_u32(sQdO + (n % kBStages) * 2 * kBTile);
-        const uint64_t d_q = make_smem_desc(sq, 16, 1024), d_do = make_smem_desc(sq + kBTile, 16, 1024);
-#pragma unroll 1
-        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_s, d_q + 2 * k, d_k + 2 * k, id_s, k > 0);
-#pragma unroll 1
-        for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_dp, d_do + 2 * k, d_v + 2 * k, id_s, k > 0);
-        umma_commit(smem_u32(s_full));
-      };
-      const bool prof_on = prof_cta;
-      long long t = prof_on ? clock64() : 0;
-      bool ok = mbar_wait(smem_u32(kv_full), 0, ab, 22) && mbar_wait(smem_u32(&qdo_full[0]), 0, ab, 23);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-      }
-      for (int n = 0; n < n_steps && ok; ++n) {
-        const int st = n % kBStages;
-        const uint32_t sq = smem_u32(sQdO + st * 2 * kBTile), sdo = sq + kBTile;
-        // Two jobs per step, served in the order in which their inputs become ready: the scores of step n+1 (Q / dO landed
-        // and the element-wise warps hold step n's accumulators in registers) and the products of step n (operands written).
-        bool s_done = !(n + 1 < n_steps), p_done = false;
-        const long long t0 = clock64();
-        while (!(s_done && p_done)) {
-          if (!s_done && mbar_test_wait(smem_u32(&qdo_full[(n + 1) % kBStages]), ((n + 1) / kBStages) & 1) &&
-              mbar_test_wait(smem_u32(s_read), n & 1)) {
-            SEG_PROF_ADD(8, t)
-            tc_fence_after();
-            issue_s(n + 1);
-            s_done = true;
-            SEG_PROF_ADD(10, t)
+          if (next_q < n_steps && mbar_test_wait(smem_u32(&qdo_empty[next_q % kBStages]), ((next_q / kBStages) & 1) ^ 1)) {
+            const int st = next_q % kBStages;
+            const int h = g * group + next_q / per_head, it = jt + next_q % per_head;
+            const uint32_t fb = smem_u32(&qdo_full[st]);
+            mbar_expect_tx(fb, 2 * kBTile);
+            tma_load_4d(smem_u32(sQdO + st * 2 * kBTile), &map_q, fb, 0, h, it * kBT, b);
+            tma_load_4d(smem_u32(sQdO + st * 2 * kBTile + kBTile), &map_do, fb, 0, h, it * kBT, b);
+            ++next_q;
+            progress = true;
           }
-          if (!p_done && mbar_test_wait(smem_u32(pds_full), n & 1)) {
-            SEG_PROF_ADD(11, t)
-            tc_fence_after();
-            const uint32_t dq_acc = tm_dq + (n & 1) * kBHD;
-            // P / dS tiles: rows = queries (128 bytes per 64 keys, two 64-key atoms 16 KB apart).  As A^T operands (M = keys, contraction
-            // over queries) they are MN-major: 16 query rows = 2048 bytes per k-step; as the A operand of dQ (M = queries, contraction
-            // over keys) K-major: 16 keys = 32 bytes per k-step inside an atom.
-            const uint64_t d_p_mn = make_smem_desc(sp, kBT * 128, 1024), d_ds_mn = make_smem_desc(sds, kBT * 128, 1024);
-            const uint64_t d_do_mn = make_smem_desc(sdo, kBTile, 1024), d_q_mn = make_smem_desc(sq, kBTile, 1024);
-#pragma unroll 1
-            for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
-              umma_bf16(tm_dv, d_p_mn + (uint64_t)(k * 128), d_do_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
-              umma_bf16(tm_dk, d_ds_mn + (uint64_t)(k * 128), d_q_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
-            }
-            const uint64_t d_ds = make_smem_desc(sds, 16, 1024), d_k_mn = make_smem_desc(sk, kBTile, 1024);
-#pragma unroll 1
-            for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys
-              umma_bf16(dq_acc, d_ds + (uint64_t)(((k >> 2) * (kBT * 128) + (k & 3) * 32) >> 4), d_k_mn + (uint64_t)(k * 128), id_dq, k > 0);
-            umma_commit(smem_u32(mma_done));
-            umma_commit(smem_u32(&qdo_empty[st]));
-            p_done = true;
-            SEG_PROF_ADD(12, t)
-          }
-          if (!(s_done && p_done)) {
-            if (*ab.cta_abort != 0) { ok = false; break; }
+          if (progress) {
+            t0 = clock64();
+          } else {
+            if (*ab.cta_abort != 0) break;
             if (clock64() - t0 > ab.limit) {
               *ab.cta_abort = 1;
-              atomicCAS(ab.global_status, 0, 24);
-              ok = false;
+              atomicCAS(ab.global_status, 0, 21);
               break;
+            }
+            __nanosleep(40);
+          }
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (elect_one()) {
+        constexpr uint32_t id_s = make_idesc_bf16(kBT, kBT, false, false);    // Q / dO (K-major) x K / V (K-major)
+        constexpr uint32_t id_kv = make_idesc_bf16(kBT, kBHD, true, true);    // P^T / dS^T (MN-major views of P / dS) x dO / Q (MN-major)
+        constexpr uint32_t id_dq = make_idesc_bf16(kBT, kBHD, false, true);   // dS (K-major) x K (MN-major)
+        const uint32_t sk = smem_u32(sK), sv = smem_u32(sV), sp = smem_u32(sP), sds = smem_u32(sDS);
+        // Descriptors advance by adding to their address field (units of 16 bytes); the loops are not unrolled so that this
+        // thread stays within the few registers its warpgroup keeps.
+        const uint64_t d_k = make_smem_desc(sk, 16, 1024), d_v = make_smem_desc(sv, 16, 1024);
+        auto issue_s = [&](int n) {
+          const uint32_t sq = smem_u32(sQdO + (n % kBStages) * 2 * kBTile);
+          const uint64_t d_q = make_smem_desc(sq, 16, 1024), d_do = make_smem_desc(sq + kBTile, 16, 1024);
+#pragma unroll 1
+          for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_s, d_q + 2 * k, d_k + 2 * k, id_s, k > 0);
+#pragma unroll 1
+          for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_dp, d_do + 2 * k, d_v + 2 * k, id_s, k > 0);
+          umma_commit(smem_u32(s_full));
+        };
+        const bool prof_on = prof_cta;
+        long long t = prof_on ? clock64() : 0;
+        bool ok = mbar_wait(smem_u32(kv_full), 0, ab, 22) && mbar_wait(smem_u32(&qdo_full[0]), 0, ab, 23);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+        }
+        for (int n = 0; n < n_steps && ok; ++n) {
+          const int st = n % kBStages;
+          const uint32_t sq = smem_u32(sQdO + st * 2 * kBTile), sdo = sq + kBTile;
+          // Two jobs per step, served in the order in which their inputs become ready: the scores of step n+1 (Q / dO landed
+          // and the element-wise warps hold step n's accumulators in registers) and the products of step n (operands written).
+          bool s_done = !(n + 1 < n_steps), p_done = false;
+          const long long t0 = clock64();
+          while (!(s_done && p_done)) {
+            if (!s_done && mbar_test_wait(smem_u32(&qdo_full[(n + 1) % kBStages]), ((n + 1) / kBStages) & 1) &&
+                mbar_test_wait(smem_u32(s_read), n & 1)) {
+              SEG_PROF_ADD(8, t)
+              tc_fence_after();
+              issue_s(n + 1);
+              s_done = true;
+              SEG_PROF_ADD(10, t)
+            }
+            if (!p_done && mbar_test_wait(smem_u32(pds_full), n & 1)) {
+              SEG_PROF_ADD(11, t)
+              tc_fence_after();
+              const uint32_t dq_acc = tm_dq + (n & 1) * kBHD;
+              // P / dS tiles: rows = queries (128 bytes per 64 keys, two 64-key atoms 16 KB apart).  As A^T operands (M = keys, contraction
+              // over queries) they are MN-major: 16 query rows = 2048 bytes per k-step; as the A operand of dQ (M = queries, contraction
+              // over keys) K-major: 16 keys = 32 bytes per k-step inside an atom.
+              const uint64_t d_p_mn = make_smem_desc(sp, kBT * 128, 1024), d_ds_mn = make_smem_desc(sds, kBT * 128, 1024);
+              const uint64_t d_do_mn = make_smem_desc(sdo, kBTile, 1024), d_q_mn = make_smem_desc(sq, kBTile, 1024);
+#pragma unroll 1
+              for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
+                umma_bf16(tm_dv, d_p_mn + (uint64_t)(k * 128), d_do_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+                umma_bf16(tm_dk, d_ds_mn + (uint64_t)(k * 128), d_q_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
+              }
+              const uint64_t d_ds = make_smem_desc(sds, 16, 1024), d_k_mn = make_smem_desc(sk, kBTile, 1024);
+#pragma unroll 1
+              for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys
+                umma_bf16(dq_acc, d_ds + (uint64_t)(((k >> 2) * (kBT * 128) + (k & 3) * 32) >> 4), d_k_mn + (uint64_t)(k * 128), id_dq, k > 0);
+              umma_commit(smem_u32(mma_done));
+              umma_commit(smem_u32(&qdo_empty[st]));
+              p_done = true;
+              SEG_PROF_ADD(12, t)
+            }
+            if (!(s_done && p_done)) {
+              if (*ab.cta_abort != 0) { ok = false; break; }
+              if (clock64() - t0 > ab.limit) {
+                *ab.cta_abort = 1;
+                atomicCAS(ab.global_status, 0, 24);
+                ok = false;
+                break;
+              }
             }
           }
         }
       }
+      __syncwarp();
     }
-    __syncwarp();
-  }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kBRegsEw));
     // ------------------------------------------------------------------ element-wise stage
