@@ -1,7 +1,7 @@
 """CUDA path of the fused head projection + cross-entropy.
 
 The [tokens, vocab] logits are produced chunk by chunk into one reused bf16 buffer, turned into losses and
-(in place) into logit gradients by ``ce_chunk_fwd_bwd`` (one read and one write of the chunk), and
+(in place) into logit gradients by ``ce_chunk_fwd_bwd`` (DRAM sees one read and one write of the chunk), and
 immediately consumed by the two gradient GEMMs, so the only full-size tensors are the inputs and outputs.
 The three GEMMs of a chunk run on this package's tcgen05 GEMM (``x W^T``, ``dlogits W`` and ``dlogits^T x`` read their
 operands in place through K-major / MN-major tensor maps; the weight gradient accumulates in fp32 through the GEMM's
