@@ -265,14 +265,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float m_new = fmaxf(m_ref, mx * p.scale_log2);
       const bool need = (m_new - m_ref) > 8.f;  // true on the first tile (m_ref = -inf)
       SEG_PROF_ADD(2, t)
-      if (j > 0) {  // P V(j-1) must have finished reading the P tile (and O) before either is touched
-        if (!mbar_wait(b_pv_full, (j - 1) & 1, ab, 18)) { ok = false; break; }
-        tc_fence_after();
-      }
+      // P V(j-1) must have finished before O is rescaled or the P tile is overwritten.  The rescale is rare after the first
+      // tiles, so the wait normally comes after the exponentials, which are kept in registers meanwhile.
+      bool pv_waited = (j == 0);
       SEG_PROF_ADD(3, t)
       if (__any_sync(0xffffffffu, need)) {
         const float m_tgt = need ? m_new : m_ref;
         if (j > 0) {
+          if (!mbar_wait(b_pv_full, (j - 1) & 1, ab, 18)) { ok = false; break; }
+          tc_fence_after();
+          pv_waited = true;
           const float alpha = ex2_approx(m_ref - m_tgt);
 #pragma unroll
           for (int c = 0; c < kAHD / 32; ++c) {
@@ -294,6 +296,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint64_t l2[2] = {0ull, 0ull};  // four running sums as two packed pairs
       // The special-function unit delivers one exp2 per 8 cycles and warp, the bound of this stage; kAEmu of every four pairs
       // take the polynomial route over the otherwise idle FMA pipe instead.
+      bf16x8 pk[kAK / 8];  // the row of P as packed bf16
       auto exp_row = [&](auto dg) {
         constexpr bool kDiag = decltype(dg)::value;
 #pragma unroll
@@ -320,8 +323,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             pr[2 * i + 1] = p1;
             l2[i & 1] = add2(l2[i & 1], pack2(p0, p1));
           }
-          uint8_t* atom = sPx + (c16 >> 3) * (kAQ * 128) + r * 128;
-          *reinterpret_cast<bf16x8*>(atom + (((c16 & 7) ^ (r & 7)) << 4)) = pack8(pr);
+          pk[c16] = pack8(pr);
         }
       };
       if (diag)
@@ -335,6 +337,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         l += (a0 + a1) + (a2 + a3);
       }
       SEG_PROF_ADD(5, t)
+      if (!pv_waited) {
+        if (!mbar_wait(b_pv_full, (j - 1) & 1, ab, 18)) { ok = false; break; }
+        tc_fence_after();
+      }
+      // bf16 operand tile: row r, 16-byte chunk c16 stored at c16 ^ (r & 7) inside its 64-column atom
+#pragma unroll
+      for (int c16 = 0; c16 < kAK / 8; ++c16) {
+        uint8_t* atom = sPx + (c16 >> 3) * (kAQ * 128) + r * 128;
+        *reinterpret_cast<bf16x8*>(atom + (((c16 & 7) ^ (r & 7)) << 4)) = pk[c16];
+      }
       tc_fence_before();
       fence_proxy_async();  // make the P tile visible to the tensor core's shared-memory reads
       __syncwarp();
