@@ -255,9 +255,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         auto issue_s = [&](int n) {
           const uint32_t sq = smem_u32(sQdO + (n % kBStages) * 2 * kBTile);
           const uint64_t d_q = make_smem_desc(sq, 16, 1024), d_do = make_smem_desc(sq + kBTile, 16, 1024);
-#pragma unroll 1
+#pragma unroll 2
           for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_s, d_q + 2 * k, d_k + 2 * k, id_s, k > 0);
-#pragma unroll 1
+#pragma unroll 2
           for (int k = 0; k < kBHD / 16; ++k) umma_bf16(tm_dp, d_do + 2 * k, d_v + 2 * k, id_s, k > 0);
           umma_commit(smem_u32(s_full));
         };
@@ -293,13 +293,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               // over keys) K-major: 16 keys = 32 bytes per k-step inside an atom.
               const uint64_t d_p_mn = make_smem_desc(sp, kBT * 128, 1024), d_ds_mn = make_smem_desc(sds, kBT * 128, 1024);
               const uint64_t d_do_mn = make_smem_desc(sdo, kBTile, 1024), d_q_mn = make_smem_desc(sq, kBTile, 1024);
-#pragma unroll 1
+#pragma unroll 2
               for (int k = 0; k < kBT / 16; ++k) {  // contraction over the 128 queries of the step
                 umma_bf16(tm_dv, d_p_mn + (uint64_t)(k * 128), d_do_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
                 umma_bf16(tm_dk, d_ds_mn + (uint64_t)(k * 128), d_q_mn + (uint64_t)(k * 128), id_kv, (n > 0 || k > 0) ? 1u : 0u);
               }
               const uint64_t d_ds = make_smem_desc(sds, 16, 1024), d_k_mn = make_smem_desc(sk, kBTile, 1024);
-#pragma unroll 1
+#pragma unroll 2
               for (int k = 0; k < kBT / 16; ++k)  // contraction over the 128 keys
                 umma_bf16(dq_acc, d_ds + (uint64_t)(((k >> 2) * (kBT * 128) + (k & 3) * 32) >> 4), d_k_mn + (uint64_t)(k * 128), id_dq, k > 0);
               umma_commit(smem_u32(mma_done));
