@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm_params.cuh"
 #include "kernels.h"
 #include "sm100.cuh"
 
@@ -47,47 +48,6 @@ struct GemmSmem {
   static constexpr int kStagingBytes = 8 * 32 * 32 * 4;  // one 32x32 fp32 transposition tile per epilogue warp
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
-
-struct GemmParams {
-  int M, N, K, batch;
-  float alpha, beta;
-  const void* C;  // optional addend, same layout and dtype as D
-  void* D;
-  int64_t ldd;       // row stride of D and C in elements
-  int64_t batch_stride_d;
-  int* status;
-  int symmetric;  // 1: D is symmetric (A == B, square): tiles wholly below the diagonal are skipped and mirrored
-  void* D_extra[7];  // further destinations with D's layout (peer-mapped buffers of other ranks): every tile is
-  int n_extra;       // stored to all of them, which turns the epilogue into the all-gather of the result
-  // Rows of A arrive from other ranks (expert-parallel dispatch): rows [r * region_rows, (r + 1) * region_rows) of every
-  // batch entry are complete once wait_flags[r] >= wait_seq (written by rank r with a system-scope release after its
-  // stores).  The producer waits, bounded, for the regions a tile touches before it issues the tile's first load.
-  const uint32_t* wait_flags;
-  uint32_t wait_seq;
-  int region_rows;
-  // Routed output (expert-parallel combine): instead of D, rows [r * route_rows, (r + 1) * route_rows) of every batch entry
-  // are stored into D_route[r] (peer-mapped buffer of rank r) at element offset
-  //   route_base + batch * route_batch_stride + (row - r * route_rows) * ldd + column.
-  void* D_route[8];
-  int route_rows;  // 0: plain output
-  int64_t route_batch_stride, route_base;
-};
-
-__device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t seq, const AbortState& ab, int code) {
-  uint32_t v;
-  const long long t0 = clock64();
-  while (true) {
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if ((int32_t)(v - seq) >= 0) return true;
-    if (*ab.cta_abort != 0) return false;
-    if (clock64() - t0 > ab.limit) {
-      *ab.cta_abort = 1;
-      atomicCAS(ab.global_status, 0, code);
-      return false;
-    }
-    __nanosleep(100);
-  }
-}
 
 // Tile enumeration shared by the three roles: tile t -> (batch, m_tile, n_tile), n fastest.
 struct TileCoord {
@@ -122,7 +82,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles * p.batch;
   const int k_blocks = (p.K + kBK - 1) / kBK;
-  const AbortState ab{cta_abort, p.status, p.wait_flags != nullptr ? kPeerWaitCycles : kWaitCycles};
+  const AbortState ab{cta_abort, p.status, p.wait_limit > 0 ? p.wait_limit : (p.wait_flags != nullptr ? kPeerWaitCycles : kWaitCycles)};
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
@@ -416,19 +376,24 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 3-D bf16 tensor map {inner, outer, batch} with a {64, box_outer, 1} box and 128-byte swizzle.
-int make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t outer_stride_elems,
-                         uint64_t batch_stride_elems, uint32_t box_outer) {
+int make_tensor_map_3d(CUtensorMap* map, const void* base, bool f32, uint64_t inner, uint64_t outer, uint64_t batch,
+                       uint64_t outer_stride_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
+  const uint64_t esz = f32 ? 4 : 2;
   cuuint64_t dims[3] = {inner, outer, batch};
-  cuuint64_t strides[2] = {outer_stride_elems * 2, (batch > 1 ? batch_stride_elems : outer_stride_elems * outer) * 2};
-  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint64_t strides[2] = {outer_stride_elems * esz, (batch > 1 ? batch_stride_elems : outer_stride_elems * outer) * esz};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+static int make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t batch,
+                                uint64_t outer_stride_elems, uint64_t batch_stride_elems, uint32_t box_outer) {
+  return make_tensor_map_3d(map, base, false, inner, outer, batch, outer_stride_elems, batch_stride_elems, 64, box_outer);
 }
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
@@ -451,7 +416,11 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
               const uint32_t* wait_flags, uint32_t wait_seq, int region_rows, void* const* d_route, int n_route, int route_rows,
-              int64_t route_batch_stride, int64_t route_base) {
+              int64_t route_batch_stride, int64_t route_base, long long wait_limit, int impl, int splits) {
+  if (impl != 0)
+    return gemm_bf16_pair(A, B, C, D, M, N, K, batch, lda, ldb, ldd, bsa, bsb, bsd, a_mn_major, b_mn_major, out_f32, alpha, beta, symmetric,
+                          d_extra, n_extra, status, sm_count, st, wait_flags, wait_seq, region_rows, d_route, n_route, route_rows,
+                          route_batch_stride, route_base, wait_limit, splits);
   const int BN = (N <= 128) ? 128 : 256;
   if (n_route > 0 && (C != nullptr || symmetric || n_extra > 0 || route_rows <= 0 || (int64_t)n_route * route_rows < M || n_route > 8))
     return -5;  // routed output excludes the addend, the mirrored output and the extra destinations
@@ -481,6 +450,9 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.route_rows = n_route > 0 ? route_rows : 0;
   p.route_batch_stride = route_batch_stride;
   p.route_base = route_base;
+  p.wait_limit = wait_limit;
+  p.splits = 1;
+  p.reduce = 0;
   for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;
 #define SEG_GEMM(BNv, AM, BM_)                                                                      \
   (out_f32 ? launch_gemm<BNv, AM, BM_, float>(ma, mb, p, sm_count, st)                              \

@@ -44,7 +44,8 @@ void check_operand(const Tensor& t, const char* name) {
 Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, std::optional<Tensor> out, bool out_f32, bool a_mn,
             bool b_mn, double alpha, double beta, bool symmetric, std::vector<int64_t> extra_dst,
             const std::optional<Tensor>& wait_flags, int64_t wait_seq, int64_t region_rows, std::vector<int64_t> route_ptrs,
-            int64_t route_rows, int64_t route_batch_stride, int64_t route_base, int64_t route_ld) {
+            int64_t route_rows, int64_t route_batch_stride, int64_t route_base, int64_t route_ld, int64_t impl, int64_t splits,
+            int64_t wait_limit) {
   check_operand(a, "a");
   check_operand(b, "b");
   TORCH_CHECK(a.dim() == b.dim(), "a and b must have the same rank");
@@ -95,7 +96,8 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
                                 routed ? route_ld : d.stride(-2), bsa, bsb, bsd, a_mn, b_mn, out_f32, (float)alpha, (float)beta, symmetric, extras,
                                 (int)extra_dst.size(), st.status.data_ptr<int>(), st.sm_count,
                                 at::cuda::getCurrentCUDAStream().stream(), wf, (uint32_t)wait_seq, (int)region_rows, routes,
-                                (int)route_ptrs.size(), (int)route_rows, route_batch_stride, route_base);
+                                (int)route_ptrs.size(), (int)route_rows, route_batch_stride, route_base, (long long)wait_limit, (int)impl,
+                                (int)splits);
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
   return d;
 }
@@ -169,7 +171,8 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("beta") = 0.0, pybind11::arg("symmetric") = false,
         pybind11::arg("extra_dst") = std::vector<int64_t>(), pybind11::arg("wait_flags") = std::nullopt, pybind11::arg("wait_seq") = 0,
         pybind11::arg("region_rows") = 0, pybind11::arg("route_ptrs") = std::vector<int64_t>(), pybind11::arg("route_rows") = 0,
-        pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0);
+        pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0,
+        pybind11::arg("impl") = 1, pybind11::arg("splits") = 0, pybind11::arg("wait_limit") = 0);
   m.def("fa_fwd", &fa_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
   m.def("fa_bwd", &fa_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("lse"),
         pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);

@@ -1,0 +1,600 @@
+// bf16 GEMM for sm_100a on CTA pairs: one 256 x 256 output tile per pair of SMs (tcgen05 cta_group::2).
+//
+//   D[b] = alpha * A[b] * B[b]^T(or B[b]) + beta * C[b]        fp32 accumulation in tensor memory
+//
+// A cluster of two CTAs (the two SMs of a TPC) owns a tile.  CTA r of the pair holds rows [128 r, 128 r + 128) of the
+// tile's A operand and columns [r nt/2, (r+1) nt/2) of its B operand (nt = the tile's width: 256, or the rounded-up
+// remainder for the last column tile) in its own shared memory - each CTA loads its own halves with plain, non-multicast
+// TMA loads whose completion bytes are counted on the leader's barrier - and one tcgen05.mma.cta_group::2 instruction of
+// the leader (M 256, N nt, K 16) reads both halves and accumulates 128 rows into each CTA's tensor memory.  Against one
+// CTA per 128-row tile this halves the B bytes a CTA has to stage and read per FLOP, and the ring gets six stages.
+//
+// Roles (320 threads per CTA): warp 0 TMA producer (both CTAs), warp 1 MMA issuer (leader only), warps 2-9 epilogue
+// (both CTAs, each on its own 128 accumulator rows; two accumulators of 256 columns so that a tile's epilogue overlaps
+// the next tile's mainloop).  Two epilogues:
+//   EPI_TMA     : plain outputs.  tcgen05.ld -> registers -> 128-byte-swizzled staging tile -> TMA store, or TMA
+//                 reduce-add for fp32 outputs that accumulate into themselves (weight gradients) or are cut along K.
+//   EPI_GENERIC : addend C, symmetric (mirrored) outputs, extra destinations in peer memory, routed outputs.
+// Tiles are dealt round-robin to the pairs, all full-width tiles first, then the narrower last-column tiles, ranges of
+// a split contraction outermost.  Every wait on an mbarrier or a flag is bounded (sm100.cuh); the two cluster barriers
+// are reached by every thread after a bounded time.
+//
+// The reference runs these products through cuBLAS (transformer/core.py:9-29 nn.Linear, torch.addmm) and Triton
+// (training/optimizers/muon_triton.py:58-252).
+#include <cuda.h>
+
+#include <vector>
+
+#include "common.cuh"
+#include "gemm_params.cuh"
+#include "kernels.h"
+#include "sm100.cuh"
+
+namespace seg {
+
+using namespace sm100;
+
+constexpr int kPairM = 256;  // rows of a pair tile, 128 per CTA
+constexpr int kPairN = 256;  // widest tile
+constexpr int kPairK = 64;   // contraction elements per stage
+constexpr int kPairThreads = 320;
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = 128 * kPairK * 2;
+constexpr int kPairBBytes = 128 * kPairK * 2;
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairStagingBytes = 8 * 4096;  // one 4 KB transposition / store tile per epilogue warp
+constexpr int kPairBarrierBytes = 256;
+constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes + kPairBarrierBytes + 1024;
+constexpr int kEpiTma = 1, kEpiGeneric = 0;
+// cost (in stages) that the schedule model adds to every tile for pipeline fill, accumulator hand-over and the epilogue
+constexpr int kTileOverheadStages = 6;
+
+struct PairSched {
+  int m_tiles, n_full, tail_nt, batch, splits, kb_total, kb_per, full_count, total;
+};
+__host__ __device__ inline PairSched make_pair_sched(int M, int N, int K, int batch, int splits) {
+  PairSched s;
+  s.m_tiles = (M + kPairM - 1) / kPairM;
+  s.n_full = N / kPairN;
+  const int rem = N - s.n_full * kPairN;
+  s.tail_nt = rem > 0 ? ((rem + 31) / 32) * 32 : 0;
+  s.batch = batch;
+  s.splits = splits;
+  s.kb_total = (K + kPairK - 1) / kPairK;
+  s.kb_per = (s.kb_total + splits - 1) / splits;
+  s.full_count = batch * s.m_tiles * s.n_full * splits;
+  s.total = s.full_count + (rem > 0 ? batch * s.m_tiles * splits : 0);
+  return s;
+}
+struct PairTile {
+  int b, m, n, nt, kb0, kb1;
+};
+__host__ __device__ inline PairTile pair_tile(const PairSched& s, int t) {
+  PairTile c;
+  int r;
+  if (t < s.full_count) {
+    c.n = t % s.n_full;
+    r = t / s.n_full;
+    c.nt = kPairN;
+  } else {
+    r = t - s.full_count;
+    c.n = s.n_full;
+    c.nt = s.tail_nt;
+  }
+  c.m = r % s.m_tiles;
+  r /= s.m_tiles;
+  c.b = r % s.batch;
+  const int ks = r / s.batch;
+  c.kb0 = ks * s.kb_per;
+  c.kb1 = c.kb0 + s.kb_per < s.kb_total ? c.kb0 + s.kb_per : s.kb_total;
+  return c;
+}
+
+template <bool A_MN, bool B_MN, typename OutT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_d, GemmParams p) {
+  constexpr int kStages = kPairStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_area = smem + kStages * kPairStageBytes;
+  uint8_t* bar_area = stage_area + kPairStagingBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);  // leader's: bytes of both CTAs' loads
+  uint64_t* empty_bar = full_bar + kStages;                     // each CTA's: its stage has been read by the MMAs
+  uint64_t* acc_full = empty_bar + kStages;                     // each CTA's: the accumulator is complete
+  uint64_t* acc_empty = acc_full + 2;                           // leader's: 16 epilogue warps have drained it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const PairSched sch = make_pair_sched(p.M, p.N, p.K, p.batch, p.splits);
+  const AbortState ab{cta_abort, p.status, p.wait_limit > 0 ? p.wait_limit : (p.wait_flags != nullptr ? kPeerWaitCycles : kWaitCycles)};
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 16);  // one arrival per epilogue warp of either CTA
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    if (EPI == kEpiTma) prefetch_tensormap(&map_d);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc_pair(smem_u32(tmem_slot), 2 * kPairN);
+    tmem_relinquish_pair();
+  }
+  // barrier initialisation and the allocation of both CTAs become visible to the whole pair
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[0]), 0);
+      int it = 0;
+      bool ok = true;
+      uint32_t regions_ready = 0;
+      for (int t = pair; t < sch.total && ok; t += n_pairs) {
+        const PairTile tl = pair_tile(sch, t);
+        if (p.symmetric && tl.n < tl.m) continue;  // wholly below the diagonal: mirrored from its twin
+        const int a_row0 = tl.m * kPairM + (int)rank * 128;
+        const int b_row0 = tl.n * kPairN + (int)rank * (tl.nt >> 1);
+        if (!A_MN && p.wait_flags != nullptr && a_row0 < p.M) {
+          const int r0 = a_row0 / p.region_rows;
+          const int last_row = min(a_row0 + 128, p.M) - 1;
+          for (int r = r0; r <= last_row / p.region_rows && ok; ++r) {
+            if (r < 32 && ((regions_ready >> r) & 1u)) continue;
+            ok = wait_region_flag(p.wait_flags + r, p.wait_seq, ab, 4);
+            if (r < 32) regions_ready |= 1u << r;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // rows written through the generic proxy, read by TMA
+        }
+        for (int kb = tl.kb0; kb < tl.kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, ab, 1)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * kPairStageBytes);
+          const uint32_t fb = full_leader + s * 8;
+          const uint32_t sa = smem_u32(smem + s * kPairStageBytes);
+          const uint32_t sb = sa + kPairABytes;
+          if (A_MN) {
+            tma_load_3d_pair(sa, &map_a, fb, a_row0, kb * kPairK, tl.b);
+            tma_load_3d_pair(sa + 64 * kPairK * 2, &map_a, fb, a_row0 + 64, kb * kPairK, tl.b);
+          } else {
+            tma_load_3d_pair(sa, &map_a, fb, kb * kPairK, a_row0, tl.b);
+          }
+          if (B_MN) {
+            tma_load_3d_pair(sb, &map_b, fb, b_row0, kb * kPairK, tl.b);
+            tma_load_3d_pair(sb + 64 * kPairK * 2, &map_b, fb, b_row0 + 64, kb * kPairK, tl.b);
+          } else {
+            tma_load_3d_pair(sb, &map_b, fb, kb * kPairK, b_row0, tl.b);
+          }
+        }
+      }
+      // Drain: every stage this CTA filled has been read (the commits of the leader have arrived here), so neither CTA
+      // leaves while the other can still signal into its shared memory.
+      for (int i = 0; i < kStages && ok; ++i, ++it) ok = mbar_wait(smem_u32(&empty_bar[it % kStages]), ((it / kStages) & 1) ^ 1, ab, 5);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t empty_peer = mapa_shared(smem_u32(&empty_bar[0]), 1);
+      const uint32_t accfull_peer = mapa_shared(smem_u32(&acc_full[0]), 1);
+      int it = 0, local_tile = 0;
+      bool ok = true;
+      for (int t = pair; t < sch.total && ok; t += n_pairs) {
+        const PairTile tl = pair_tile(sch, t);
+        if (p.symmetric && tl.n < tl.m) continue;
+        const int acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_ph ^ 1, ab, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kPairN;
+        const uint32_t idesc = make_idesc_bf16(kPairM, tl.nt, A_MN, B_MN);
+        for (int kb = tl.kb0; kb < tl.kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, ab, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kPairStageBytes);
+          const uint32_t sb = sa + kPairABytes;
+#pragma unroll
+          for (int k = 0; k < kPairK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 64 * kPairK * 2, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 64 * kPairK * 2, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16_pair(d_tmem, da, db, idesc, (kb > tl.kb0 || k > 0) ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(smem_u32(&empty_bar[s]));
+          umma_commit_pair(empty_peer + s * 8);
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&acc_full[acc]));
+          umma_commit_pair(accfull_peer + acc * 8);
+        }
+        ++local_tile;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (8 warps per CTA)
+    // warp % 4 selects the TMEM sub-partition (32 lanes = 32 rows of this CTA's 128); warps 2-5 take columns [0, 128) of the
+    // tile, warps 6-9 columns [128, 256), 32 at a time.  tcgen05.ld hands every lane one row of a chunk.
+    const int sub = warp & 3;
+    const int ep = warp - 2;
+    const int half = ep >> 2;
+    const uint32_t accempty_leader = mapa_shared(smem_u32(&acc_empty[0]), 0);
+    uint8_t* stage_raw = stage_area + ep * 4096;
+    int local_tile = 0;
+    bool ok = true;
+
+    if (EPI == kEpiTma) {
+      // One 4 KB staging tile per warp in the 128-byte-swizzle layout of the output's tensor map: 32 rows x 128 bytes
+      // (64 bf16 = two chunks, or 32 fp32 = one chunk); the 16-byte piece j of row r sits at slot j ^ (r & 7).
+      constexpr bool kBf16 = sizeof(OutT) == 2;
+      const uint32_t stage_u32 = smem_u32(stage_raw);
+      uint4* row_slots = reinterpret_cast<uint4*>(stage_raw + lane * 128);
+      for (int t = pair; t < sch.total && ok; t += n_pairs) {
+        const PairTile tl = pair_tile(sch, t);
+        const int acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6)) { ok = false; break; }
+        tc_fence_after();
+        const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;
+        if (row0 < p.M) {
+#pragma unroll 1
+          for (int ci = 0; ci < 4; ++ci) {
+            const int c0 = half * 128 + ci * 32;
+            const int col = tl.n * kPairN + c0;
+            if (c0 >= tl.nt || col >= p.N) break;  // warp-uniform
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN + c0, v);
+            if (!kBf16 || (ci & 1) == 0) {  // a new staging tile: the previous store has finished reading it
+              if (lane == 0) bulk_wait_group_read0();
+              __syncwarp();
+            }
+            tmem_ld_wait_regs(v);
+            if (kBf16) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 u;
+                __nv_bfloat162 h;
+                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j]), p.alpha * __uint_as_float(v[8 * j + 1]));
+                u.x = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 2]), p.alpha * __uint_as_float(v[8 * j + 3]));
+                u.y = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 4]), p.alpha * __uint_as_float(v[8 * j + 5]));
+                u.z = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 6]), p.alpha * __uint_as_float(v[8 * j + 7]));
+                u.w = *reinterpret_cast<uint32_t*>(&h);
+                row_slots[((ci & 1) * 4 + j) ^ (lane & 7)] = u;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint4 u;
+                u.x = __float_as_uint(p.alpha * __uint_as_float(v[4 * j]));
+                u.y = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 1]));
+                u.z = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 2]));
+                u.w = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 3]));
+                row_slots[j ^ (lane & 7)] = u;
+              }
+            }
+            const bool last_chunk = (ci == 3) || (c0 + 32 >= tl.nt) || (col + 32 >= p.N);
+            if (!kBf16 || (ci & 1) == 1 || last_chunk) {
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                const int col_store = kBf16 ? tl.n * kPairN + half * 128 + (ci & ~1) * 32 : col;
+                if (p.reduce)
+                  tma_reduce_add_3d(&map_d, stage_u32, col_store, row0, tl.b);
+                else
+                  tma_store_3d(&map_d, stage_u32, col_store, row0, tl.b);
+                bulk_commit_group();
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(accempty_leader + acc * 8);
+        ++local_tile;
+      }
+      if (lane == 0) bulk_wait_group0();  // this warp's stores have left its staging tile and are complete
+    } else {
+      // Generic path: the chunk is transposed through the XOR-swizzled staging tile so that global accesses are coalesced
+      // (8 consecutive lanes cover one row, 4 values each); the addend C is read in that layout one chunk ahead.
+      float* stage = reinterpret_cast<float*>(stage_raw);
+      const int q = lane & 7, rsub = lane >> 3;
+      OutT* D = reinterpret_cast<OutT*>(p.D);
+      const OutT* C = reinterpret_cast<const OutT*>(p.C);
+      bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+                    (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
+      for (int d = 0; d < p.n_extra; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_extra[d]) & 15) == 0);
+      if (p.route_rows > 0) {
+        vec_ok = (p.ldd % 8 == 0) && ((p.route_base * sizeof(OutT)) % 16 == 0) && ((p.route_batch_stride * sizeof(OutT)) % 16 == 0);
+        for (int d = 0; d < 8; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_route[d]) & 15) == 0);
+      }
+      for (int t = pair; t < sch.total && ok; t += n_pairs) {
+        const PairTile tl = pair_tile(sch, t);
+        if (p.symmetric && tl.n < tl.m) continue;
+        const int acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6)) { ok = false; break; }
+        tc_fence_after();
+        const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;  // first row of this warp's 32-row band
+        const int64_t boff = (int64_t)tl.b * p.batch_stride_d;
+        OutT* rbase[8];
+        if (p.route_rows > 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = row0 + rsub + 4 * i;
+            const int reg = r / p.route_rows;
+            rbase[i] = reinterpret_cast<OutT*>(p.D_route[reg < 8 ? reg : 7]) + p.route_base + (int64_t)tl.b * p.route_batch_stride +
+                       (int64_t)(r - reg * p.route_rows) * p.ldd;
+          }
+        }
+        float4 cnext[8];
+        bool have_next = false;
+        auto fetch_c = [&](int col, float4* dst) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = row0 + rsub + 4 * i;
+            dst[i] = (r < p.M) ? load4<OutT>(C + boff + (int64_t)r * p.ldd + col + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        };
+        if (row0 < p.M) {
+          {
+            const int col = tl.n * kPairN + half * 128;
+            if (C != nullptr && vec_ok && half * 128 < tl.nt && col + 32 <= p.N) {
+              fetch_c(col, cnext);
+              have_next = true;
+            }
+          }
+#pragma unroll 1
+          for (int ci = 0; ci < 4; ++ci) {
+            const int c0 = half * 128 + ci * 32;
+            const int col = tl.n * kPairN + c0;
+            if (c0 >= tl.nt || col >= p.N) break;  // warp-uniform
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN + c0, v);
+            float4 ccur[8];
+            const bool have_cur = have_next;
+            if (have_cur) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) ccur[i] = cnext[i];
+            }
+            have_next = false;
+            if (ci + 1 < 4 && c0 + 32 < tl.nt && C != nullptr && vec_ok && col + 64 <= p.N) {
+              fetch_c(col + 32, cnext);
+              have_next = true;
+            }
+            tmem_ld_wait_regs(v);
+            const int ncols = (p.N - col) < 32 ? (p.N - col) : 32;
+            const bool fast = vec_ok && ncols == 32 && (C == nullptr || have_cur);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              reinterpret_cast<float4*>(stage + lane * 32)[j ^ (lane & 7)] =
+                  make_float4(p.alpha * __uint_as_float(v[4 * j]), p.alpha * __uint_as_float(v[4 * j + 1]),
+                              p.alpha * __uint_as_float(v[4 * j + 2]), p.alpha * __uint_as_float(v[4 * j + 3]));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rl = rsub + 4 * i, r = row0 + rl;
+              float4 f = reinterpret_cast<const float4*>(stage + rl * 32)[q ^ (rl & 7)];
+              if (r < p.M) {
+                const int64_t off = boff + (int64_t)r * p.ldd + col + 4 * q;
+                if (fast) {
+                  if (C != nullptr) {
+                    f.x += p.beta * ccur[i].x; f.y += p.beta * ccur[i].y; f.z += p.beta * ccur[i].z; f.w += p.beta * ccur[i].w;
+                  }
+                  if (p.route_rows > 0) {
+                    store4<OutT>(rbase[i] + col + 4 * q, f);
+                  } else {
+                    store4<OutT>(D + off, f);
+                    for (int d = 0; d < p.n_extra; ++d) store4<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + off, f);
+                  }
+                } else {
+                  const float fv[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (4 * q + e < ncols) {
+                      float val = fv[e];
+                      if (C != nullptr) val += p.beta * to_f<OutT>(C[off + e]);
+                      if (p.route_rows > 0) {
+                        rbase[i][col + 4 * q + e] = from_f<OutT>(val);
+                      } else {
+                        D[off + e] = from_f<OutT>(val);
+                        for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[off + e] = from_f<OutT>(val);
+                      }
+                      if (e == 0) f.x = val; else if (e == 1) f.y = val; else if (e == 2) f.z = val; else f.w = val;
+                    }
+                  }
+                }
+              }
+              if (p.symmetric) reinterpret_cast<float4*>(stage + rl * 32)[q ^ (rl & 7)] = f;  // final values for the mirror pass
+            }
+            // symmetric outputs: the twin tile (this chunk's columns as rows) is skipped by the schedule when it lies wholly
+            // below the diagonal, so its elements are written from here, consecutive lanes on consecutive addresses
+            const int row = row0 + lane;
+            const bool mirror = p.symmetric && (row0 / kPairN) < (col / kPairM);
+            if (mirror) {
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 f = reinterpret_cast<const float4*>(stage + lane * 32)[j ^ (lane & 7)];
+                const float fv[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int cc = 4 * j + e;
+                  if (row < p.M && cc < ncols) {
+                    const OutT val = from_f<OutT>(fv[e]);
+                    const int64_t moff = boff + (int64_t)(col + cc) * p.ldd + row;
+                    D[moff] = val;
+                    for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+                  }
+                }
+              }
+            }
+            __syncwarp();  // the staging tile is rewritten by the next chunk
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(accempty_leader + acc * 8);
+        ++local_tile;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown (also reached after an abort)
+  if (*cta_abort != 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);  // loads that may still be in flight land before shared memory is released
+  }
+  tc_fence_before();
+  cluster_sync_all();  // neither CTA frees tensor memory or leaves while its peer may still use it
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc_pair(tmem_base, 2 * kPairN);
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+// Makespan, in stages, of dealing the tiles of a schedule round-robin to `pairs` CTA pairs.
+static double pair_makespan(const PairSched& s, int pairs) {
+  const int P = s.total < pairs ? s.total : pairs;
+  if (P <= 0) return 0.0;
+  std::vector<double> load((size_t)P, 0.0);
+  for (int t = 0; t < s.total; ++t) {
+    const PairTile tl = pair_tile(s, t);
+    load[(size_t)(t % P)] += (double)tl.nt / kPairN * (double)(tl.kb1 - tl.kb0 + kTileOverheadStages);
+  }
+  double m = 0.0;
+  for (double v : load) m = v > m ? v : m;
+  return m;
+}
+
+static int choose_splits(int M, int N, int K, int batch, int pairs) {
+  const PairSched one = make_pair_sched(M, N, K, batch, 1);
+  if (one.total >= 2 * pairs || one.kb_total < 16) return 1;
+  int best = 1;
+  double best_cost = pair_makespan(one, pairs);
+  for (int s = 2; s <= 16 && one.kb_total / s >= 8; ++s) {
+    const PairSched cand = make_pair_sched(M, N, K, batch, s);
+    if ((s - 1) * cand.kb_per >= cand.kb_total) continue;  // an empty range
+    const double cost = pair_makespan(cand, pairs);
+    if (cost < 0.97 * best_cost) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+template <bool A_MN, bool B_MN, typename OutT, int EPI>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmParams& p, int pairs, cudaStream_t st) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OutT, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemTotal) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const PairSched s = make_pair_sched(p.M, p.N, p.K, p.batch, p.splits);
+  const int P = s.total < pairs ? s.total : pairs;
+  if (P <= 0) return 0;
+  kern<<<2 * P, kPairThreads, kPairSmemTotal, st>>>(ma, mb, md, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
+                   int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
+                   float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
+                   const uint32_t* wait_flags, uint32_t wait_seq, int region_rows, void* const* d_route, int n_route,
+                   int route_rows, int64_t route_batch_stride, int64_t route_base, long long wait_limit, int splits_hint) {
+  if (n_route > 0 && (C != nullptr || symmetric || n_extra > 0 || route_rows <= 0 || (int64_t)n_route * route_rows < M || n_route > 8))
+    return -5;  // routed output excludes the addend, the mirrored output and the extra destinations
+  const int pairs = sm_count / 2;
+  CUtensorMap ma, mb, md;
+  int r;
+  if (a_mn_major)  // memory [K, M]
+    r = make_tensor_map_3d(&ma, A, false, (uint64_t)M, (uint64_t)K, (uint64_t)batch, (uint64_t)lda, (uint64_t)bsa, 64, 64);
+  else  // memory [M, K]
+    r = make_tensor_map_3d(&ma, A, false, (uint64_t)K, (uint64_t)M, (uint64_t)batch, (uint64_t)lda, (uint64_t)bsa, 64, 128);
+  if (r != 0) return 100 + r;
+  if (b_mn_major)  // memory [K, N]
+    r = make_tensor_map_3d(&mb, B, false, (uint64_t)N, (uint64_t)K, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, 64, 64);
+  else  // memory [N, K]
+    r = make_tensor_map_3d(&mb, B, false, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, 64, 128);
+  if (r != 0) return 200 + r;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.alpha = alpha; p.beta = beta;
+  p.C = C; p.D = D; p.ldd = ldd; p.batch_stride_d = bsd;
+  p.status = status;
+  p.symmetric = symmetric ? 1 : 0;
+  p.n_extra = n_extra < 0 ? 0 : (n_extra > 7 ? 7 : n_extra);
+  for (int i = 0; i < 7; ++i) p.D_extra[i] = i < p.n_extra ? d_extra[i] : nullptr;
+  p.wait_flags = (wait_flags != nullptr && region_rows > 0 && !a_mn_major) ? wait_flags : nullptr;
+  p.wait_seq = wait_seq;
+  p.region_rows = region_rows > 0 ? region_rows : 1;
+  p.route_rows = n_route > 0 ? route_rows : 0;
+  p.route_batch_stride = route_batch_stride;
+  p.route_base = route_base;
+  for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;
+  p.wait_limit = wait_limit;
+  p.splits = 1;
+  p.reduce = 0;
+
+  // The TMA epilogue serves plain outputs: no routing, mirroring or extra destinations, and either no addend or an fp32
+  // output that accumulates into itself (D += alpha * A op(B)), which becomes a TMA reduction.
+  const size_t esz = out_f32 ? 4 : 2;
+  const bool accumulate = C != nullptr && C == D && beta == 1.0f && out_f32;
+  const bool aligned = (reinterpret_cast<uintptr_t>(D) % 16 == 0) && ((ldd * esz) % 16 == 0) && (batch == 1 || (bsd * esz) % 16 == 0);
+  const bool tma_epi = n_route == 0 && n_extra <= 0 && !symmetric && aligned && (C == nullptr || accumulate) && D != nullptr;
+  if (tma_epi) {
+    r = make_tensor_map_3d(&md, D, out_f32, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldd, (uint64_t)bsd, out_f32 ? 32 : 64, 32);
+    if (r != 0) return 300 + r;
+    p.reduce = accumulate ? 1 : 0;
+    if (out_f32 && p.wait_flags == nullptr) {
+      int splits = splits_hint > 0 ? splits_hint : choose_splits(M, N, K, batch, pairs);
+      const int kb_total = (K + kPairK - 1) / kPairK;
+      if (splits > kb_total) splits = kb_total;
+      while (splits > 1 && (splits - 1) * ((kb_total + splits - 1) / splits) >= kb_total) --splits;
+      if (splits > 1) {
+        if (!accumulate) {  // every range is added into a zeroed output
+          for (int b = 0; b < batch; ++b)
+            if (cudaMemset2DAsync(reinterpret_cast<char*>(D) + (size_t)b * bsd * 4, (size_t)ldd * 4, 0, (size_t)N * 4, (size_t)M, st) != cudaSuccess)
+              return -6;
+        }
+        p.splits = splits;
+        p.reduce = 1;
+      }
+    }
+  } else {
+    md = ma;  // unused
+  }
+#define SEG_PAIR(AM, BM_)                                                                                         \
+  (tma_epi ? (out_f32 ? launch_pair<AM, BM_, float, kEpiTma>(ma, mb, md, p, pairs, st)                            \
+                      : launch_pair<AM, BM_, __nv_bfloat16, kEpiTma>(ma, mb, md, p, pairs, st))                   \
+           : (out_f32 ? launch_pair<AM, BM_, float, kEpiGeneric>(ma, mb, md, p, pairs, st)                        \
+                      : launch_pair<AM, BM_, __nv_bfloat16, kEpiGeneric>(ma, mb, md, p, pairs, st)))
+  if (!a_mn_major && !b_mn_major) return SEG_PAIR(false, false);
+  if (!a_mn_major && b_mn_major) return SEG_PAIR(false, true);
+  if (a_mn_major && b_mn_major) return SEG_PAIR(true, true);
+  return SEG_PAIR(true, false);
+#undef SEG_PAIR
+}
+
+}  // namespace seg

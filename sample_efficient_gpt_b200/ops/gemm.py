@@ -8,6 +8,8 @@ batch strides multiples of 8 elements, 16-byte aligned base); callers fall back 
 
 from __future__ import annotations
 
+import os
+
 import torch
 from torch import Tensor
 
@@ -27,9 +29,18 @@ def usable(*tensors: Tensor) -> bool:
     return True
 
 
+# Which kernel runs: "pair" = one 256 x 256 tile per CTA pair (tcgen05 cta_group::2, TMA-store epilogue, split
+# contraction for small fp32 outputs), "single" = one CTA per 128-row tile.
+DEFAULT_IMPL = 0 if os.environ.get("SEGPT_GEMM_IMPL", "pair") == "single" else 1
+
+
 def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, symmetric=False,
-         extra_dst: list[int] | None = None, wait: tuple | None = None, route: tuple | None = None) -> Tensor:
-    """``extra_dst``: device addresses of up to 7 more buffers with the output's layout (peer memory of other ranks);
+         extra_dst: list[int] | None = None, wait: tuple | None = None, route: tuple | None = None, impl: int | None = None,
+         splits: int = 0, wait_limit: int = 0) -> Tensor:
+    """``impl``: 1 pair kernel, 0 single-CTA kernel, None = ``SEGPT_GEMM_IMPL``.  ``splits``: ranges of the contraction
+    (pair kernel, fp32 output stored or accumulated into itself; 0 = chosen from the shape).  ``wait_limit``: cycles a
+    wait inside the kernel may stand still before it gives up and sets the status word (0 = default).
+    ``extra_dst``: device addresses of up to 7 more buffers with the output's layout (peer memory of other ranks);
     every output tile is stored to all of them from the epilogue.
     ``wait`` = (flags int32 tensor, seq, region_rows): rows ``[r * region_rows, (r+1) * region_rows)`` of ``a`` are being
     written by rank r and are complete once ``flags[r] >= seq``; the kernel's producer waits per tile (bounded).
@@ -40,7 +51,8 @@ def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.
     flags, seq, rows = wait if wait is not None else (None, 0, 0)
     rp, rr, rbs, rbase, rld = route if route is not None else ([], 0, 0, 0, 0)
     return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric, extra_dst or [], flags, int(seq), int(rows),
-                          list(rp), int(rr), int(rbs), int(rbase), int(rld))
+                          list(rp), int(rr), int(rbs), int(rbase), int(rld), DEFAULT_IMPL if impl is None else int(impl), int(splits),
+                          int(wait_limit))
 
 
 def mm_nt(x: Tensor, w: Tensor, **kw) -> Tensor:

@@ -19,6 +19,16 @@ def _g():
     return G
 
 
+@pytest.fixture(autouse=True, params=[1, 0], ids=["pair", "single"])
+def gemm_impl(request):
+    """Every case runs on the CTA-pair kernel and on the one-CTA-per-tile kernel."""
+    G = _g()
+    prev = G.DEFAULT_IMPL
+    G.DEFAULT_IMPL = request.param
+    yield request.param
+    G.DEFAULT_IMPL = prev
+
+
 def _check(d, want, name, tol=2e-2):
     G = _g()
     torch.cuda.synchronize()
@@ -33,7 +43,8 @@ def _rand(*shape):
     return (torch.randn(*shape, device=DEV) * 0.5).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (128, 256, 128), (256, 512, 512), (200, 136, 72), (1000, 1152, 1152)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (128, 256, 128), (256, 512, 512), (200, 136, 72), (1000, 1152, 1152),
+                                   (24, 40, 64), (300, 1944, 200), (1300, 776, 1152)])
 def test_nt(M, N, K):
     G = _g()
     torch.manual_seed(0)
@@ -107,3 +118,25 @@ def test_large_shapes_and_speed():
     dy = _rand(8192, 3072)
     x = _rand(8192, 1152)
     _check(G.mm_tn(dy, x, out_f32=True), dy.float().t() @ x.float(), "wgrad 3072x1152x8192", tol=1e-2)
+
+
+def test_pair_store_reduce_and_split_contraction():
+    """The pair kernel's TMA epilogue: fp32 store, accumulation into the output (TMA reduce-add) and a contraction cut
+    into ranges that are all added into the output, on shapes with ragged last tiles."""
+    G = _g()
+    torch.manual_seed(6)
+    for (M, N, K) in [(1944, 1152, 4096), (200, 72, 1024), (1152, 1152, 2048)]:
+        dy, x = _rand(K, M), _rand(K, N)
+        want = dy.float().t() @ x.float()
+        _check(G.mm_tn(dy, x, out_f32=True, impl=1, splits=1), want, f"tn fp32 store {M}x{N}x{K}", tol=1e-2)
+        for splits in (0, 3, 8):
+            _check(G.mm_tn(dy, x, out_f32=True, impl=1, splits=splits), want, f"tn fp32 splits={splits} {M}x{N}x{K}", tol=1e-2)
+            base = torch.randn(M, N, device=DEV)
+            out = base.clone()
+            G.gemm(dy, x, a_mn=True, b_mn=True, c=out, out=out, out_f32=True, beta=1.0, impl=1, splits=splits)
+            _check(out, want + base, f"tn fp32 accumulate splits={splits} {M}x{N}x{K}", tol=1e-2)
+    a, w = _rand(520, 328), _rand(328, 1000)
+    o = torch.full((520, 1024), 7.0, device=DEV, dtype=torch.bfloat16)
+    G.gemm(a, w, b_mn=True, out=o[:, :1000], impl=1)  # strided output: columns past N stay untouched
+    _check(o[:, :1000], a.float() @ w.float(), "nn strided out")
+    assert (o[:, 1000:] == 7.0).all()
