@@ -416,11 +416,12 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
               int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
               const uint32_t* wait_flags, uint32_t wait_seq, int region_rows, void* const* d_route, int n_route, int route_rows,
-              int64_t route_batch_stride, int64_t route_base, long long wait_limit, int impl, int splits) {
+              int64_t route_batch_stride, int64_t route_base, long long wait_limit, int impl, void* workspace, uint32_t* ws_flags,
+              int split_k) {
   if (impl != 0)
     return gemm_bf16_pair(A, B, C, D, M, N, K, batch, lda, ldb, ldd, bsa, bsb, bsd, a_mn_major, b_mn_major, out_f32, alpha, beta, symmetric,
                           d_extra, n_extra, status, sm_count, st, wait_flags, wait_seq, region_rows, d_route, n_route, route_rows,
-                          route_batch_stride, route_base, wait_limit, splits);
+                          route_batch_stride, route_base, wait_limit, workspace, ws_flags, split_k);
   const int BN = (N <= 128) ? 128 : 256;
   if (n_route > 0 && (C != nullptr || symmetric || n_extra > 0 || route_rows <= 0 || (int64_t)n_route * route_rows < M || n_route > 8))
     return -5;  // routed output excludes the addend, the mirrored output and the extra destinations
@@ -451,8 +452,12 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.route_batch_stride = route_batch_stride;
   p.route_base = route_base;
   p.wait_limit = wait_limit;
-  p.splits = 1;
   p.reduce = 0;
+  p.n_static = 0;
+  p.splits = 1;
+  p.b_box_rows = 64;
+  p.ws = nullptr;
+  p.ws_flags = nullptr;
   for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;
 #define SEG_GEMM(BNv, AM, BM_)                                                                      \
   (out_f32 ? launch_gemm<BNv, AM, BM_, float>(ma, mb, p, sm_count, st)                              \

@@ -14,10 +14,26 @@ namespace {
 
 using torch::Tensor;
 
+struct PairWorkspace {
+  Tensor slots, flags;  // parts of tiles cut along the contraction and their ready flags; launches on one stream share them
+};
+
 struct DeviceState {
   Tensor status;  // int32[1], stays 0 unless a bounded wait gave up
   int sm_count = 0;
+  std::map<cudaStream_t, PairWorkspace> workspaces;
 };
+
+PairWorkspace& pair_workspace(DeviceState& st, const c10::Device& dev, cudaStream_t stream) {
+  auto it = st.workspaces.find(stream);
+  if (it == st.workspaces.end()) {
+    PairWorkspace w;
+    w.slots = torch::empty({(int64_t)seg::gemm_pair_workspace_bytes()}, torch::dtype(torch::kUInt8).device(dev));
+    w.flags = torch::zeros({(int64_t)seg::gemm_pair_flag_words()}, torch::dtype(torch::kInt32).device(dev));
+    it = st.workspaces.emplace(stream, std::move(w)).first;
+  }
+  return it->second;
+}
 
 DeviceState& device_state(const c10::Device& dev) {
   static std::map<int, DeviceState> states;
@@ -44,7 +60,7 @@ void check_operand(const Tensor& t, const char* name) {
 Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, std::optional<Tensor> out, bool out_f32, bool a_mn,
             bool b_mn, double alpha, double beta, bool symmetric, std::vector<int64_t> extra_dst,
             const std::optional<Tensor>& wait_flags, int64_t wait_seq, int64_t region_rows, std::vector<int64_t> route_ptrs,
-            int64_t route_rows, int64_t route_batch_stride, int64_t route_base, int64_t route_ld, int64_t impl, int64_t splits,
+            int64_t route_rows, int64_t route_batch_stride, int64_t route_base, int64_t route_ld, int64_t impl, bool split_k,
             int64_t wait_limit) {
   check_operand(a, "a");
   check_operand(b, "b");
@@ -92,12 +108,20 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
   }
   void* extras[7] = {nullptr};
   for (size_t i = 0; i < extra_dst.size(); ++i) extras[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(extra_dst[i]));
+  const cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+  void* ws = nullptr;
+  uint32_t* ws_flags = nullptr;
+  if (impl != 0 && split_k) {
+    auto& w = pair_workspace(st, a.device(), stream);
+    ws = w.slots.data_ptr();
+    ws_flags = reinterpret_cast<uint32_t*>(w.flags.data_ptr<int>());
+  }
   const int rc = seg::gemm_bf16(a.data_ptr(), b.data_ptr(), cptr, routed ? nullptr : d.data_ptr(), M, N, K, batch, a.stride(-2), b.stride(-2),
                                 routed ? route_ld : d.stride(-2), bsa, bsb, bsd, a_mn, b_mn, out_f32, (float)alpha, (float)beta, symmetric, extras,
-                                (int)extra_dst.size(), st.status.data_ptr<int>(), st.sm_count,
-                                at::cuda::getCurrentCUDAStream().stream(), wf, (uint32_t)wait_seq, (int)region_rows, routes,
-                                (int)route_ptrs.size(), (int)route_rows, route_batch_stride, route_base, (long long)wait_limit, (int)impl,
-                                (int)splits);
+                                (int)extra_dst.size(), st.status.data_ptr<int>(), st.sm_count, stream, wf, (uint32_t)wait_seq,
+                                (int)region_rows, routes,
+                                (int)route_ptrs.size(), (int)route_rows, route_batch_stride, route_base, (long long)wait_limit, (int)impl, ws,
+                                ws_flags, split_k ? 1 : 0);
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
   return d;
 }
@@ -111,6 +135,7 @@ int64_t gemm_status(int64_t device_index) {
 void gemm_reset_status(int64_t device_index) {
   auto& st = device_state(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
   st.status.zero_();
+  for (auto& kv : st.workspaces) kv.second.flags.zero_();  // a kernel that gave up may have left parts announced
 }
 
 // Causal GQA flash attention forward on the tcgen05 kernel: returns (o, lse).
@@ -172,7 +197,7 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("extra_dst") = std::vector<int64_t>(), pybind11::arg("wait_flags") = std::nullopt, pybind11::arg("wait_seq") = 0,
         pybind11::arg("region_rows") = 0, pybind11::arg("route_ptrs") = std::vector<int64_t>(), pybind11::arg("route_rows") = 0,
         pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0,
-        pybind11::arg("impl") = 1, pybind11::arg("splits") = 0, pybind11::arg("wait_limit") = 0);
+        pybind11::arg("impl") = 1, pybind11::arg("split_k") = true, pybind11::arg("wait_limit") = 0);
   m.def("fa_fwd", &fa_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
   m.def("fa_bwd", &fa_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("lse"),
         pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);

@@ -4,7 +4,8 @@
 //
 // A cluster of two CTAs (the two SMs of a TPC) owns a tile.  CTA r of the pair holds rows [128 r, 128 r + 128) of the
 // tile's A operand and columns [r nt/2, (r+1) nt/2) of its B operand (nt = the tile's width: 256, or the rounded-up
-// remainder for the last column tile) in its own shared memory - each CTA loads its own halves with plain, non-multicast
+// remainder for the last column tile, whose B halves are loaded in 64-column boxes so that a narrow tile moves fewer
+// bytes) in its own shared memory - each CTA loads its own halves with plain, non-multicast
 // TMA loads whose completion bytes are counted on the leader's barrier - and one tcgen05.mma.cta_group::2 instruction of
 // the leader (M 256, N nt, K 16) reads both halves and accumulates 128 rows into each CTA's tensor memory.  Against one
 // CTA per 128-row tile this halves the B bytes a CTA has to stage and read per FLOP, and the ring gets six stages.
@@ -13,19 +14,22 @@
 // (both CTAs, each on its own 128 accumulator rows; two accumulators of 256 columns so that a tile's epilogue overlaps
 // the next tile's mainloop).  Two epilogues:
 //   EPI_TMA     : plain outputs.  tcgen05.ld -> registers -> 128-byte-swizzled staging tile -> TMA store, or TMA
-//                 reduce-add for fp32 outputs that accumulate into themselves (weight gradients) or are cut along K.
+//                 reduce-add for fp32 outputs that accumulate into themselves (weight gradients).
 //   EPI_GENERIC : addend C, symmetric (mirrored) outputs, extra destinations in peer memory, routed outputs.
-// Tiles are dealt round-robin to the pairs, all full-width tiles first, then the narrower last-column tiles, ranges of
-// a split contraction outermost.  Every wait on an mbarrier or a flag is bounded (sm100.cuh); the two cluster barriers
-// are reached by every thread after a bounded time.
+// Schedule (gemm_pair_sched.h): whole tiles dealt round-robin to the pairs; the tiles of the last, partly filled wave (or
+// all of them when there are fewer tiles than pairs) are cut into ranges of the contraction whose raw accumulators meet
+// in a workspace and are summed in a fixed order by the item of the last range, which also runs the epilogue.
+// Every wait on an mbarrier or a flag is bounded (sm100.cuh); the two cluster barriers are reached by every thread after
+// a bounded time.
 //
 // The reference runs these products through cuBLAS (transformer/core.py:9-29 nn.Linear, torch.addmm) and Triton
 // (training/optimizers/muon_triton.py:58-252).
 #include <cuda.h>
 
-#include <vector>
+#include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_pair_sched.h"
 #include "gemm_params.cuh"
 #include "kernels.h"
 #include "sm100.cuh"
@@ -34,9 +38,6 @@ namespace seg {
 
 using namespace sm100;
 
-constexpr int kPairM = 256;  // rows of a pair tile, 128 per CTA
-constexpr int kPairN = 256;  // widest tile
-constexpr int kPairK = 64;   // contraction elements per stage
 constexpr int kPairThreads = 320;
 constexpr int kPairStages = 6;
 constexpr int kPairABytes = 128 * kPairK * 2;
@@ -46,48 +47,36 @@ constexpr int kPairStagingBytes = 8 * 4096;  // one 4 KB transposition / store t
 constexpr int kPairBarrierBytes = 256;
 constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes + kPairBarrierBytes + 1024;
 constexpr int kEpiTma = 1, kEpiGeneric = 0;
-// cost (in stages) that the schedule model adds to every tile for pipeline fill, accumulator hand-over and the epilogue
-constexpr int kTileOverheadStages = 6;
 
-struct PairSched {
-  int m_tiles, n_full, tail_nt, batch, splits, kb_total, kb_per, full_count, total;
-};
-__host__ __device__ inline PairSched make_pair_sched(int M, int N, int K, int batch, int splits) {
-  PairSched s;
-  s.m_tiles = (M + kPairM - 1) / kPairM;
-  s.n_full = N / kPairN;
-  const int rem = N - s.n_full * kPairN;
-  s.tail_nt = rem > 0 ? ((rem + 31) / 32) * 32 : 0;
-  s.batch = batch;
-  s.splits = splits;
-  s.kb_total = (K + kPairK - 1) / kPairK;
-  s.kb_per = (s.kb_total + splits - 1) / splits;
-  s.full_count = batch * s.m_tiles * s.n_full * splits;
-  s.total = s.full_count + (rem > 0 ? batch * s.m_tiles * splits : 0);
-  return s;
+// A contributor's raw accumulator chunk goes to its slot; consecutive lanes write consecutive 16-byte pieces.
+__device__ __forceinline__ void slot_store(uint4* slot_chunk, int lane, const uint32_t* v) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) __stcg(slot_chunk + j * 32 + lane, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
 }
-struct PairTile {
-  int b, m, n, nt, kb0, kb1;
-};
-__host__ __device__ inline PairTile pair_tile(const PairSched& s, int t) {
-  PairTile c;
-  int r;
-  if (t < s.full_count) {
-    c.n = t % s.n_full;
-    r = t / s.n_full;
-    c.nt = kPairN;
-  } else {
-    r = t - s.full_count;
-    c.n = s.n_full;
-    c.nt = s.tail_nt;
+__device__ __forceinline__ void slot_add(const uint4* slot_chunk, int lane, uint32_t* v) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint4 u = __ldcg(slot_chunk + j * 32 + lane);
+    v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + __uint_as_float(u.x));
+    v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + __uint_as_float(u.y));
+    v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + __uint_as_float(u.z));
+    v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + __uint_as_float(u.w));
   }
-  c.m = r % s.m_tiles;
-  r /= s.m_tiles;
-  c.b = r % s.batch;
-  const int ks = r / s.batch;
-  c.kb0 = ks * s.kb_per;
-  c.kb1 = c.kb0 + s.kb_per < s.kb_total ? c.kb0 + s.kb_per : s.kb_total;
-  return c;
+}
+__device__ __forceinline__ bool wait_slot_flag(uint32_t* flag, const AbortState& ab) {
+  uint32_t v;
+  const long long t0 = clock64();
+  while (true) {
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v != 0) return true;
+    if (*ab.cta_abort != 0) return false;
+    if (clock64() - t0 > ab.limit) {
+      *ab.cta_abort = 1;
+      atomicCAS(ab.global_status, 0, 7);
+      return false;
+    }
+    __nanosleep(40);
+  }
 }
 
 template <bool A_MN, bool B_MN, typename OutT, int EPI>
@@ -108,8 +97,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0: leader
-  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const PairSched sch = make_pair_sched(p.M, p.N, p.K, p.batch, p.splits);
+  const int n_pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
+  const PairSched sch = make_pair_sched(p.M, p.N, p.K, p.batch, p.symmetric, p.n_static, p.splits);
   const AbortState ab{cta_abort, p.status, p.wait_limit > 0 ? p.wait_limit : (p.wait_flags != nullptr ? kPeerWaitCycles : kWaitCycles)};
 
   if (threadIdx.x == 0) {
@@ -145,11 +134,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int it = 0;
       bool ok = true;
       uint32_t regions_ready = 0;
-      for (int t = pair; t < sch.total && ok; t += n_pairs) {
-        const PairTile tl = pair_tile(sch, t);
-        if (p.symmetric && tl.n < tl.m) continue;  // wholly below the diagonal: mirrored from its twin
+      for (int item = pair; item < sch.n_items && ok; item += n_pairs) {
+        const PairItem tl = pair_item(sch, item);
         const int a_row0 = tl.m * kPairM + (int)rank * 128;
         const int b_row0 = tl.n * kPairN + (int)rank * (tl.nt >> 1);
+        const int b_boxes = p.b_box_rows == 64 ? ((tl.nt >> 1) + 63) >> 6 : 128 / p.b_box_rows;  // boxes of this CTA's B half
         if (!A_MN && p.wait_flags != nullptr && a_row0 < p.M) {
           const int r0 = a_row0 / p.region_rows;
           const int last_row = min(a_row0 + 128, p.M) - 1;
@@ -165,7 +154,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, ab, 1)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * kPairStageBytes);
+          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * (kPairABytes + b_boxes * (B_MN ? 64 : p.b_box_rows) * kPairK * 2));
           const uint32_t fb = full_leader + s * 8;
           const uint32_t sa = smem_u32(smem + s * kPairStageBytes);
           const uint32_t sb = sa + kPairABytes;
@@ -175,11 +164,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           } else {
             tma_load_3d_pair(sa, &map_a, fb, kb * kPairK, a_row0, tl.b);
           }
-          if (B_MN) {
-            tma_load_3d_pair(sb, &map_b, fb, b_row0, kb * kPairK, tl.b);
-            tma_load_3d_pair(sb + 64 * kPairK * 2, &map_b, fb, b_row0 + 64, kb * kPairK, tl.b);
-          } else {
-            tma_load_3d_pair(sb, &map_b, fb, kb * kPairK, b_row0, tl.b);
+          for (int j = 0; j < b_boxes; ++j) {
+            if (B_MN)
+              tma_load_3d_pair(sb + j * (64 * kPairK * 2), &map_b, fb, b_row0 + j * 64, kb * kPairK, tl.b);
+            else
+              tma_load_3d_pair(sb + j * (p.b_box_rows * kPairK * 2), &map_b, fb, kb * kPairK, b_row0 + j * p.b_box_rows, tl.b);
           }
         }
       }
@@ -195,9 +184,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t accfull_peer = mapa_shared(smem_u32(&acc_full[0]), 1);
       int it = 0, local_tile = 0;
       bool ok = true;
-      for (int t = pair; t < sch.total && ok; t += n_pairs) {
-        const PairTile tl = pair_tile(sch, t);
-        if (p.symmetric && tl.n < tl.m) continue;
+      for (int item = pair; item < sch.n_items && ok; item += n_pairs) {
+        const PairItem tl = pair_item(sch, item);
         const int acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_ph ^ 1, ab, 2)) { ok = false; break; }
@@ -240,123 +228,140 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint8_t* stage_raw = stage_area + ep * 4096;
     int local_tile = 0;
     bool ok = true;
-
-    if (EPI == kEpiTma) {
-      // One 4 KB staging tile per warp in the 128-byte-swizzle layout of the output's tensor map: 32 rows x 128 bytes
-      // (64 bf16 = two chunks, or 32 fp32 = one chunk); the 16-byte piece j of row r sits at slot j ^ (r & 7).
-      constexpr bool kBf16 = sizeof(OutT) == 2;
-      const uint32_t stage_u32 = smem_u32(stage_raw);
-      uint4* row_slots = reinterpret_cast<uint4*>(stage_raw + lane * 128);
-      for (int t = pair; t < sch.total && ok; t += n_pairs) {
-        const PairTile tl = pair_tile(sch, t);
-        const int acc = local_tile & 1;
-        const uint32_t acc_ph = (local_tile >> 1) & 1;
-        if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6)) { ok = false; break; }
-        tc_fence_after();
-        const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;
-        if (row0 < p.M) {
-#pragma unroll 1
-          for (int ci = 0; ci < 4; ++ci) {
-            const int c0 = half * 128 + ci * 32;
-            const int col = tl.n * kPairN + c0;
-            if (c0 >= tl.nt || col >= p.N) break;  // warp-uniform
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN + c0, v);
-            if (!kBf16 || (ci & 1) == 0) {  // a new staging tile: the previous store has finished reading it
-              if (lane == 0) bulk_wait_group_read0();
-              __syncwarp();
-            }
-            tmem_ld_wait_regs(v);
-            if (kBf16) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 u;
-                __nv_bfloat162 h;
-                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j]), p.alpha * __uint_as_float(v[8 * j + 1]));
-                u.x = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 2]), p.alpha * __uint_as_float(v[8 * j + 3]));
-                u.y = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 4]), p.alpha * __uint_as_float(v[8 * j + 5]));
-                u.z = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 6]), p.alpha * __uint_as_float(v[8 * j + 7]));
-                u.w = *reinterpret_cast<uint32_t*>(&h);
-                row_slots[((ci & 1) * 4 + j) ^ (lane & 7)] = u;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                uint4 u;
-                u.x = __float_as_uint(p.alpha * __uint_as_float(v[4 * j]));
-                u.y = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 1]));
-                u.z = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 2]));
-                u.w = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 3]));
-                row_slots[j ^ (lane & 7)] = u;
-              }
-            }
-            const bool last_chunk = (ci == 3) || (c0 + 32 >= tl.nt) || (col + 32 >= p.N);
-            if (!kBf16 || (ci & 1) == 1 || last_chunk) {
-              fence_proxy_async();
-              __syncwarp();
-              if (lane == 0) {
-                const int col_store = kBf16 ? tl.n * kPairN + half * 128 + (ci & ~1) * 32 : col;
-                if (p.reduce)
-                  tma_reduce_add_3d(&map_d, stage_u32, col_store, row0, tl.b);
-                else
-                  tma_store_3d(&map_d, stage_u32, col_store, row0, tl.b);
-                bulk_commit_group();
-              }
-            }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(accempty_leader + acc * 8);
-        ++local_tile;
-      }
-      if (lane == 0) bulk_wait_group0();  // this warp's stores have left its staging tile and are complete
-    } else {
-      // Generic path: the chunk is transposed through the XOR-swizzled staging tile so that global accesses are coalesced
-      // (8 consecutive lanes cover one row, 4 values each); the addend C is read in that layout one chunk ahead.
-      float* stage = reinterpret_cast<float*>(stage_raw);
-      const int q = lane & 7, rsub = lane >> 3;
-      OutT* D = reinterpret_cast<OutT*>(p.D);
-      const OutT* C = reinterpret_cast<const OutT*>(p.C);
-      bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
-                    (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
+    // EPI_TMA: one 4 KB staging tile per warp in the 128-byte-swizzle layout of the output's tensor map: 32 rows x 128
+    // bytes (64 bf16 = two chunks, or 32 fp32 = one chunk); the 16-byte piece j of row r sits at slot j ^ (r & 7).
+    constexpr bool kBf16 = sizeof(OutT) == 2;
+    const uint32_t stage_u32 = smem_u32(stage_raw);
+    uint4* row_slots = reinterpret_cast<uint4*>(stage_raw + lane * 128);
+    // EPI_GENERIC: the chunk is transposed through the XOR-swizzled staging tile so that global accesses are coalesced
+    // (8 consecutive lanes cover one row, 4 values each); the addend C is read in that layout one chunk ahead.
+    float* stage = reinterpret_cast<float*>(stage_raw);
+    const int q = lane & 7, rsub = lane >> 3;
+    OutT* D = reinterpret_cast<OutT*>(p.D);
+    const OutT* C = reinterpret_cast<const OutT*>(p.C);
+    bool vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+                  (p.C == nullptr || (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.batch_stride_d % 8 == 0);
+    if (EPI == kEpiGeneric) {
       for (int d = 0; d < p.n_extra; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_extra[d]) & 15) == 0);
       if (p.route_rows > 0) {
         vec_ok = (p.ldd % 8 == 0) && ((p.route_base * sizeof(OutT)) % 16 == 0) && ((p.route_batch_stride * sizeof(OutT)) % 16 == 0);
         for (int d = 0; d < 8; ++d) vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(p.D_route[d]) & 15) == 0);
       }
-      for (int t = pair; t < sch.total && ok; t += n_pairs) {
-        const PairTile tl = pair_tile(sch, t);
-        if (p.symmetric && tl.n < tl.m) continue;
-        const int acc = local_tile & 1;
-        const uint32_t acc_ph = (local_tile >> 1) & 1;
-        if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6)) { ok = false; break; }
-        tc_fence_after();
-        const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;  // first row of this warp's 32-row band
-        const int64_t boff = (int64_t)tl.b * p.batch_stride_d;
-        OutT* rbase[8];
-        if (p.route_rows > 0) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = row0 + rsub + 4 * i;
-            const int reg = r / p.route_rows;
-            rbase[i] = reinterpret_cast<OutT*>(p.D_route[reg < 8 ? reg : 7]) + p.route_base + (int64_t)tl.b * p.route_batch_stride +
-                       (int64_t)(r - reg * p.route_rows) * p.ldd;
-          }
+    }
+    for (int item = pair; item < sch.n_items && ok; item += n_pairs) {
+      const PairItem tl = pair_item(sch, item);
+      const int acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      const bool owner = pair_item_owns(sch, tl);
+      const int n_parts = (owner && tl.ks > 0) ? tl.ks : 0;  // parts that earlier ranges of this tile left in the workspace
+      if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN;
+      if (!owner) {
+        // -------- part of a tile: the raw accumulator goes to the item's slot, then the flag of this warp is raised
+        const int slot = pair_slot(sch, tl.ks, tl.t);
+        uint4* const my_slot = p.ws + ((size_t)(slot * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32);
+#pragma unroll 1
+        for (int ci = 0; ci < 4; ++ci) {
+          const int c0 = half * 128 + ci * 32;
+          if (c0 >= tl.nt) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_acc + c0, v);
+          tmem_ld_wait_regs(v);
+          slot_store(my_slot + ci * (8 * 32), lane, v);
         }
-        float4 cnext[8];
-        bool have_next = false;
-        auto fetch_c = [&](int col, float4* dst) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = row0 + rsub + 4 * i;
-            dst[i] = (r < p.M) ? load4<OutT>(C + boff + (int64_t)r * p.ldd + col + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ws_flags + (slot * 2 + (int)rank) * 8 + ep), "r"(1u) : "memory");
+        }
+      } else {
+        if (n_parts != 0) {
+          if (lane == 0) {
+            for (int i = 0; i < n_parts && ok; ++i) ok = wait_slot_flag(p.ws_flags + (pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep, ab);
           }
-        };
-        if (row0 < p.M) {
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          if (!ok) break;
+        }
+        const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;  // first row of this warp's 32-row band
+        if (EPI == kEpiTma) {
+          if (row0 < p.M) {
+#pragma unroll 1
+            for (int ci = 0; ci < 4; ++ci) {
+              const int c0 = half * 128 + ci * 32;
+              const int col = tl.n * kPairN + c0;
+              if (c0 >= tl.nt || col >= p.N) break;  // warp-uniform
+              uint32_t v[32];
+              tmem_ld_32x32(tmem_acc + c0, v);
+              if (!kBf16 || (ci & 1) == 0) {  // a new staging tile: the previous store has finished reading it
+                if (lane == 0) bulk_wait_group_read0();
+                __syncwarp();
+              }
+              tmem_ld_wait_regs(v);
+              for (int i = 0; i < n_parts; ++i)
+                slot_add(p.ws + ((size_t)(pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32) + ci * (8 * 32), lane, v);
+              if (kBf16) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint4 u;
+                  __nv_bfloat162 h;
+                  h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j]), p.alpha * __uint_as_float(v[8 * j + 1]));
+                  u.x = *reinterpret_cast<uint32_t*>(&h);
+                  h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 2]), p.alpha * __uint_as_float(v[8 * j + 3]));
+                  u.y = *reinterpret_cast<uint32_t*>(&h);
+                  h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 4]), p.alpha * __uint_as_float(v[8 * j + 5]));
+                  u.z = *reinterpret_cast<uint32_t*>(&h);
+                  h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 6]), p.alpha * __uint_as_float(v[8 * j + 7]));
+                  u.w = *reinterpret_cast<uint32_t*>(&h);
+                  row_slots[((ci & 1) * 4 + j) ^ (lane & 7)] = u;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  uint4 u;
+                  u.x = __float_as_uint(p.alpha * __uint_as_float(v[4 * j]));
+                  u.y = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 1]));
+                  u.z = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 2]));
+                  u.w = __float_as_uint(p.alpha * __uint_as_float(v[4 * j + 3]));
+                  row_slots[j ^ (lane & 7)] = u;
+                }
+              }
+              const bool last_chunk = (ci == 3) || (c0 + 32 >= tl.nt) || (col + 32 >= p.N);
+              if (!kBf16 || (ci & 1) == 1 || last_chunk) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  const int col_store = kBf16 ? tl.n * kPairN + half * 128 + (ci & ~1) * 32 : col;
+                  if (p.reduce)
+                    tma_reduce_add_3d(&map_d, stage_u32, col_store, row0, tl.b);
+                  else
+                    tma_store_3d(&map_d, stage_u32, col_store, row0, tl.b);
+                  bulk_commit_group();
+                }
+              }
+            }
+          }
+        } else if (row0 < p.M) {
+          const int64_t boff = (int64_t)tl.b * p.batch_stride_d;
+          OutT* rbase[8];
+          if (p.route_rows > 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = row0 + rsub + 4 * i;
+              const int reg = r / p.route_rows;
+              rbase[i] = reinterpret_cast<OutT*>(p.D_route[reg < 8 ? reg : 7]) + p.route_base + (int64_t)tl.b * p.route_batch_stride +
+                         (int64_t)(r - reg * p.route_rows) * p.ldd;
+            }
+          }
+          float4 cnext[8];
+          bool have_next = false;
+          auto fetch_c = [&](int col, float4* dst) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = row0 + rsub + 4 * i;
+              dst[i] = (r < p.M) ? load4<OutT>(C + boff + (int64_t)r * p.ldd + col + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          };
           {
             const int col = tl.n * kPairN + half * 128;
             if (C != nullptr && vec_ok && half * 128 < tl.nt && col + 32 <= p.N) {
@@ -370,7 +375,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int col = tl.n * kPairN + c0;
             if (c0 >= tl.nt || col >= p.N) break;  // warp-uniform
             uint32_t v[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN + c0, v);
+            tmem_ld_32x32(tmem_acc + c0, v);
             float4 ccur[8];
             const bool have_cur = have_next;
             if (have_cur) {
@@ -383,6 +388,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               have_next = true;
             }
             tmem_ld_wait_regs(v);
+            for (int i = 0; i < n_parts; ++i)
+              slot_add(p.ws + ((size_t)(pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32) + ci * (8 * 32), lane, v);
             const int ncols = (p.N - col) < 32 ? (p.N - col) : 32;
             const bool fast = vec_ok && ncols == 32 && (C == nullptr || have_cur);
 #pragma unroll
@@ -427,7 +434,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               }
               if (p.symmetric) reinterpret_cast<float4*>(stage + rl * 32)[q ^ (rl & 7)] = f;  // final values for the mirror pass
             }
-            // symmetric outputs: the twin tile (this chunk's columns as rows) is skipped by the schedule when it lies wholly
+            // symmetric outputs: the twin tile (this chunk's columns as rows) is not in the schedule when it lies wholly
             // below the diagonal, so its elements are written from here, consecutive lanes on consecutive addresses
             const int row = row0 + lane;
             const bool mirror = p.symmetric && (row0 / kPairN) < (col / kPairM);
@@ -452,12 +459,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();  // the staging tile is rewritten by the next chunk
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(accempty_leader + acc * 8);
-        ++local_tile;
+        if (n_parts != 0 && lane == 0) {  // the slots are free for the next launch
+          for (int i = 0; i < n_parts; ++i) p.ws_flags[(pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep] = 0;
+        }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(accempty_leader + acc * 8);
+      ++local_tile;
     }
+    if (EPI == kEpiTma && lane == 0) bulk_wait_group0();  // this warp's stores have left its staging tile and are complete
   }
 
   // ------------------------------------------------------------------ teardown (also reached after an abort)
@@ -471,36 +482,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-// Makespan, in stages, of dealing the tiles of a schedule round-robin to `pairs` CTA pairs.
-static double pair_makespan(const PairSched& s, int pairs) {
-  const int P = s.total < pairs ? s.total : pairs;
-  if (P <= 0) return 0.0;
-  std::vector<double> load((size_t)P, 0.0);
-  for (int t = 0; t < s.total; ++t) {
-    const PairTile tl = pair_tile(s, t);
-    load[(size_t)(t % P)] += (double)tl.nt / kPairN * (double)(tl.kb1 - tl.kb0 + kTileOverheadStages);
-  }
-  double m = 0.0;
-  for (double v : load) m = v > m ? v : m;
-  return m;
-}
-
-static int choose_splits(int M, int N, int K, int batch, int pairs) {
-  const PairSched one = make_pair_sched(M, N, K, batch, 1);
-  if (one.total >= 2 * pairs || one.kb_total < 16) return 1;
-  int best = 1;
-  double best_cost = pair_makespan(one, pairs);
-  for (int s = 2; s <= 16 && one.kb_total / s >= 8; ++s) {
-    const PairSched cand = make_pair_sched(M, N, K, batch, s);
-    if ((s - 1) * cand.kb_per >= cand.kb_total) continue;  // an empty range
-    const double cost = pair_makespan(cand, pairs);
-    if (cost < 0.97 * best_cost) {
-      best = s;
-      best_cost = cost;
-    }
-  }
-  return best;
-}
+size_t gemm_pair_workspace_bytes() { return (size_t)kPairMaxSlots * kPairSlotPieces * sizeof(uint4); }
+size_t gemm_pair_flag_words() { return (size_t)kPairMaxSlots * 16; }
 
 template <bool A_MN, bool B_MN, typename OutT, int EPI>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmParams& p, int pairs, cudaStream_t st) {
@@ -510,10 +493,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemTotal) != cudaSuccess) return -2;
     configured = true;
   }
-  const PairSched s = make_pair_sched(p.M, p.N, p.K, p.batch, p.splits);
-  const int P = s.total < pairs ? s.total : pairs;
-  if (P <= 0) return 0;
-  kern<<<2 * P, kPairThreads, kPairSmemTotal, st>>>(ma, mb, md, p);
+  kern<<<2 * pairs, kPairThreads, kPairSmemTotal, st>>>(ma, mb, md, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -521,10 +501,15 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
                    int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
                    float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
                    const uint32_t* wait_flags, uint32_t wait_seq, int region_rows, void* const* d_route, int n_route,
-                   int route_rows, int64_t route_batch_stride, int64_t route_base, long long wait_limit, int splits_hint) {
+                   int route_rows, int64_t route_batch_stride, int64_t route_base, long long wait_limit, void* workspace,
+                   uint32_t* ws_flags, int split_k) {
   if (n_route > 0 && (C != nullptr || symmetric || n_extra > 0 || route_rows <= 0 || (int64_t)n_route * route_rows < M || n_route > 8))
     return -5;  // routed output excludes the addend, the mirrored output and the extra destinations
-  const int pairs = sm_count / 2;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  static const int b_box_env = [] {
+    const char* e = std::getenv("SEGPT_GEMM_BBOX");
+    return (e != nullptr && std::atoi(e) == 128) ? 128 : 64;
+  }();
   CUtensorMap ma, mb, md;
   int r;
   if (a_mn_major)  // memory [K, M]
@@ -535,7 +520,7 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   if (b_mn_major)  // memory [K, N]
     r = make_tensor_map_3d(&mb, B, false, (uint64_t)N, (uint64_t)K, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, 64, 64);
   else  // memory [N, K]
-    r = make_tensor_map_3d(&mb, B, false, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, 64, 128);
+    r = make_tensor_map_3d(&mb, B, false, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint64_t)ldb, (uint64_t)bsb, 64, (uint32_t)b_box_env);
   if (r != 0) return 200 + r;
 
   GemmParams p;
@@ -554,8 +539,14 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   p.route_base = route_base;
   for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;
   p.wait_limit = wait_limit;
-  p.splits = 1;
   p.reduce = 0;
+  p.ws = reinterpret_cast<uint4*>(workspace);
+  p.ws_flags = ws_flags;
+  p.b_box_rows = b_box_env;
+  pair_choose_split(M, N, K, batch, p.symmetric, sm_count / 2, split_k != 0 && workspace != nullptr && ws_flags != nullptr && p.wait_flags == nullptr,
+                    p.n_static, p.splits);
+  const PairSched sched = make_pair_sched(M, N, K, batch, p.symmetric, p.n_static, p.splits);
+  const int pairs = sched.n_items < sm_count / 2 ? sched.n_items : sm_count / 2;
 
   // The TMA epilogue serves plain outputs: no routing, mirroring or extra destinations, and either no addend or an fp32
   // output that accumulates into itself (D += alpha * A op(B)), which becomes a TMA reduction.
@@ -567,21 +558,6 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
     r = make_tensor_map_3d(&md, D, out_f32, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldd, (uint64_t)bsd, out_f32 ? 32 : 64, 32);
     if (r != 0) return 300 + r;
     p.reduce = accumulate ? 1 : 0;
-    if (out_f32 && p.wait_flags == nullptr) {
-      int splits = splits_hint > 0 ? splits_hint : choose_splits(M, N, K, batch, pairs);
-      const int kb_total = (K + kPairK - 1) / kPairK;
-      if (splits > kb_total) splits = kb_total;
-      while (splits > 1 && (splits - 1) * ((kb_total + splits - 1) / splits) >= kb_total) --splits;
-      if (splits > 1) {
-        if (!accumulate) {  // every range is added into a zeroed output
-          for (int b = 0; b < batch; ++b)
-            if (cudaMemset2DAsync(reinterpret_cast<char*>(D) + (size_t)b * bsd * 4, (size_t)ldd * 4, 0, (size_t)N * 4, (size_t)M, st) != cudaSuccess)
-              return -6;
-        }
-        p.splits = splits;
-        p.reduce = 1;
-      }
-    }
   } else {
     md = ma;  // unused
   }

@@ -34,8 +34,11 @@ struct GemmParams {
   int64_t route_batch_stride, route_base;
   long long wait_limit;  // cycles a wait may stand still before it gives up; 0: the defaults of sm100.cuh
   // pair kernel only
-  int splits;  // > 1: the contraction is cut into this many ranges, one tile each, all added into D (fp32) by TMA reductions
-  int reduce;  // TMA epilogue: 1 = add the tile into D (cp.reduce.async.bulk ... add), 0 = store it
+  int reduce;          // TMA epilogue: 1 = add the tile into D (cp.reduce.async.bulk ... add), 0 = store it
+  int n_static, splits;  // schedule (gemm_pair_sched.h): tiles computed whole; ranges of the contraction for the others
+  int b_box_rows;        // rows of the K-major B operand's TMA box (64 or 128)
+  uint4* ws;             // workspace slots for the parts of tiles that are cut along the contraction
+  uint32_t* ws_flags;    // one word per (slot, rank, epilogue warp), zero between launches
 };
 
 __device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t seq, const sm100::AbortState& ab, int code) {
@@ -59,12 +62,15 @@ __device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t 
 int make_tensor_map_3d(CUtensorMap* map, const void* base, bool f32, uint64_t inner, uint64_t outer, uint64_t batch,
                        uint64_t outer_stride_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_outer);
 
-// The pair kernel's launcher (gemm_pair.cu); same contract as gemm_bf16.  `splits_hint`: 0 = choose, n = use n ranges of the
-// contraction where the output allows it (fp32, plain store or accumulation into itself).
+// The pair kernel's launcher (gemm_pair.cu); same contract as gemm_bf16.  `workspace` / `ws_flags`: device buffers of
+// gemm_pair_workspace_bytes() bytes and gemm_pair_flag_words() zeroed 32-bit words that launches on one stream share;
+// without them (or with split_k == 0) every tile is computed by one pair from start to end.
+// (gemm_pair_workspace_bytes / gemm_pair_flag_words are declared in kernels.h.)
 int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, int N, int K, int batch, int64_t lda, int64_t ldb,
                    int64_t ldd, int64_t bsa, int64_t bsb, int64_t bsd, bool a_mn_major, bool b_mn_major, bool out_f32, float alpha,
                    float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
                    const uint32_t* wait_flags, uint32_t wait_seq, int region_rows, void* const* d_route, int n_route,
-                   int route_rows, int64_t route_batch_stride, int64_t route_base, long long wait_limit, int splits_hint);
+                   int route_rows, int64_t route_batch_stride, int64_t route_base, long long wait_limit, void* workspace,
+                   uint32_t* ws_flags, int split_k);
 
 }  // namespace seg

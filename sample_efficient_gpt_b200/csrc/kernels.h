@@ -127,10 +127,13 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
               float beta, bool symmetric, void* const* d_extra, int n_extra, int* status, int sm_count, cudaStream_t st,
               const uint32_t* wait_flags = nullptr, uint32_t wait_seq = 0, int region_rows = 0, void* const* d_route = nullptr,
               int n_route = 0, int route_rows = 0, int64_t route_batch_stride = 0, int64_t route_base = 0, long long wait_limit = 0,
-              int impl = 1, int splits = 0);
+              int impl = 1, void* workspace = nullptr, uint32_t* ws_flags = nullptr, int split_k = 1);
 // wait_limit: cycles a wait inside the kernel may stand still before it gives up (0: about one second, ten with wait_flags).
-// impl: 1 = CTA-pair kernel (cta_group::2, 256-row tiles), 0 = one CTA per 128-row tile.  splits: ranges of the contraction
-// (pair kernel, fp32 output that is stored or accumulated into itself; 0 = chosen from the shape).
+// impl: 1 = CTA-pair kernel (cta_group::2, 256-row tiles), 0 = one CTA per 128-row tile.  workspace / ws_flags / split_k:
+// the pair kernel's buffers for tiles cut along the contraction (sizes: gemm_pair_workspace_bytes / gemm_pair_flag_words) and
+// the switch for cutting.
+size_t gemm_pair_workspace_bytes();
+size_t gemm_pair_flag_words();
 // d_route (optional): routed output - rows [r * route_rows, (r+1) * route_rows) of every batch entry go to d_route[r] (a buffer of
 // rank r, peer-mapped) at element offset route_base + batch * route_batch_stride + (row - r * route_rows) * ldd + column; D is
 // not written.  Not combinable with C, symmetric or d_extra.

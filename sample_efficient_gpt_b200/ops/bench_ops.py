@@ -50,39 +50,40 @@ def rnd(*shape, scale=0.5):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
 
-def _bench_gemm_one(kind, M, N, K, batch, iters, splits, label=""):
+def _bench_gemm_one(kind, M, N, K, batch, iters, split_k, label=""):
     from sample_efficient_gpt_b200.ops import gemm as G
 
     bs = (batch,) if batch > 1 else ()
     f32 = kind == "tn"  # weight gradients are produced in fp32
     if kind == "nt":
         x, w = rnd(*bs, M, K), rnd(*bs, N, K)
-        ours, lib = (lambda impl: G.mm_nt(x, w, impl=impl)), (lambda: x @ w.mT)
+        ours, lib = (lambda impl: G.mm_nt(x, w, impl=impl, split_k=split_k)), (lambda: x @ w.mT)
     elif kind == "nn":
         x, w = rnd(*bs, M, K), rnd(*bs, K, N)
-        ours, lib = (lambda impl: G.mm_nn(x, w, impl=impl)), (lambda: x @ w)
+        ours, lib = (lambda impl: G.mm_nn(x, w, impl=impl, split_k=split_k)), (lambda: x @ w)
     else:
         x, w = rnd(*bs, K, M), rnd(*bs, K, N)
         out = torch.empty(*bs, M, N, device="cuda", dtype=torch.float32)
-        ours = lambda impl: G.mm_tn(x, w, out=out, out_f32=True, impl=impl, splits=splits)  # noqa: E731
+        ours = lambda impl: G.mm_tn(x, w, out=out, out_f32=True, impl=impl, split_k=split_k)  # noqa: E731
         lib = (lambda: torch.bmm(x.mT, w, out_dtype=torch.float32, out=out)) if bs else (lambda: torch.mm(x.mT, w, out_dtype=torch.float32, out=out))
     fl = 2.0 * M * N * K * max(batch, 1) / 1e9
     t_p, t_s, t_l = timeit(lambda: ours(1), iters), timeit(lambda: ours(0), iters), timeit(lib, iters)
     print(json.dumps({"op": f"gemm_{kind}", "label": label, "shape": [batch, M, N, K], "out": "fp32" if f32 else "bf16",
                       "pair_ms": round(t_p, 4), "pair_tflops": round(fl / t_p, 1), "single_ms": round(t_s, 4),
                       "single_tflops": round(fl / t_s, 1), "cublas_ms": round(t_l, 4), "cublas_tflops": round(fl / t_l, 1),
-                      "status": G.status()}), flush=True)
+                      "split_k": split_k, "status": G.status()}), flush=True)
 
 
 def bench_gemm(a):
+    sk = not a.no_split_k
     if a.shapes == "block":  # IMU-1 430M projections at T tokens: y = x W^T, dx = dy W, dW = dy^T x
         T = a.m
         for name, n_out, n_in in [("qkv+gate", 1944, 1152), ("out", 1152, 1152), ("up", 6144, 1152), ("down", 1152, 3072)]:
-            _bench_gemm_one("nt", T, n_out, n_in, 1, a.iters, 0, name + " fwd")
-            _bench_gemm_one("nn", T, n_in, n_out, 1, a.iters, 0, name + " dgrad")
-            _bench_gemm_one("tn", n_out, n_in, T, 1, a.iters, a.splits, name + " wgrad")
+            _bench_gemm_one("nt", T, n_out, n_in, 1, a.iters, sk, name + " fwd")
+            _bench_gemm_one("nn", T, n_in, n_out, 1, a.iters, sk, name + " dgrad")
+            _bench_gemm_one("tn", n_out, n_in, T, 1, a.iters, sk, name + " wgrad")
         return
-    _bench_gemm_one(a.kind, a.m, a.n, a.k, a.batch, a.iters, a.splits)
+    _bench_gemm_one(a.kind, a.m, a.n, a.k, a.batch, a.iters, sk)
 
 
 def bench_ns(a):
@@ -315,7 +316,7 @@ def main():
     p.add_argument("--cols", type=int, default=3072)
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--iters", type=int, default=10)
-    p.add_argument("--splits", type=int, default=0, help="gemm --kind tn: ranges of the contraction (0 = chosen from the shape)")
+    p.add_argument("--no-split-k", action="store_true", help="gemm: whole tiles only, no tile is cut along the contraction")
     p.add_argument("--shapes", default="", help="gemm: 'block' runs the IMU-1 block shapes (forward, data gradient, weight gradient)")
     a = p.parse_args()
     {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe, "decode": bench_decode}[a.op](a)

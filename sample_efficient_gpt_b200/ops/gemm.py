@@ -29,16 +29,18 @@ def usable(*tensors: Tensor) -> bool:
     return True
 
 
-# Which kernel runs: "pair" = one 256 x 256 tile per CTA pair (tcgen05 cta_group::2, TMA-store epilogue, split
-# contraction for small fp32 outputs), "single" = one CTA per 128-row tile.
+# Which kernel runs: "pair" = one 256 x 256 tile per CTA pair (tcgen05 cta_group::2, TMA-store epilogue, tiles of
+# the last wave cut along the contraction), "single" = one CTA per 128-row tile.
 DEFAULT_IMPL = 0 if os.environ.get("SEGPT_GEMM_IMPL", "pair") == "single" else 1
 
 
 def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, symmetric=False,
          extra_dst: list[int] | None = None, wait: tuple | None = None, route: tuple | None = None, impl: int | None = None,
-         splits: int = 0, wait_limit: int = 0) -> Tensor:
-    """``impl``: 1 pair kernel, 0 single-CTA kernel, None = ``SEGPT_GEMM_IMPL``.  ``splits``: ranges of the contraction
-    (pair kernel, fp32 output stored or accumulated into itself; 0 = chosen from the shape).  ``wait_limit``: cycles a
+         split_k: bool = True, wait_limit: int = 0) -> Tensor:
+    """``impl``: 1 pair kernel, 0 single-CTA kernel, None = ``SEGPT_GEMM_IMPL``.  ``split_k`` (pair kernel): tiles of the last, partly filled
+    wave may be cut into ranges of the contraction that several pairs compute and one of them sums in a fixed order (a
+    per-stream workspace of the extension holds the parts, allocated at the first call on a stream - make that call
+    before capturing the stream into a CUDA graph); False: whole tiles only.  ``wait_limit``: cycles a
     wait inside the kernel may stand still before it gives up and sets the status word (0 = default).
     ``extra_dst``: device addresses of up to 7 more buffers with the output's layout (peer memory of other ranks);
     every output tile is stored to all of them from the epilogue.
@@ -51,7 +53,7 @@ def gemm(a, b, c=None, out=None, out_f32=False, a_mn=False, b_mn=False, alpha=1.
     flags, seq, rows = wait if wait is not None else (None, 0, 0)
     rp, rr, rbs, rbase, rld = route if route is not None else ([], 0, 0, 0, 0)
     return ops.ext().gemm(a, b, c, out, out_f32, a_mn, b_mn, float(alpha), float(beta), symmetric, extra_dst or [], flags, int(seq), int(rows),
-                          list(rp), int(rr), int(rbs), int(rbase), int(rld), DEFAULT_IMPL if impl is None else int(impl), int(splits),
+                          list(rp), int(rr), int(rbs), int(rbase), int(rld), DEFAULT_IMPL if impl is None else int(impl), bool(split_k),
                           int(wait_limit))
 
 

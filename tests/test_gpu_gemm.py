@@ -121,22 +121,27 @@ def test_large_shapes_and_speed():
 
 
 def test_pair_store_reduce_and_split_contraction():
-    """The pair kernel's TMA epilogue: fp32 store, accumulation into the output (TMA reduce-add) and a contraction cut
-    into ranges that are all added into the output, on shapes with ragged last tiles."""
+    """The pair kernel's TMA epilogue (bf16 / fp32 store, accumulation into the output as a TMA reduce-add) with tiles that
+    several pairs compute together (long contractions, few tiles) and with whole tiles per pair, on ragged shapes."""
     G = _g()
     torch.manual_seed(6)
-    for (M, N, K) in [(1944, 1152, 4096), (200, 72, 1024), (1152, 1152, 2048)]:
+    for (M, N, K) in [(1944, 1152, 4096), (200, 72, 1024), (1152, 1152, 8192), (256, 256, 16384)]:
         dy, x = _rand(K, M), _rand(K, N)
         want = dy.float().t() @ x.float()
-        _check(G.mm_tn(dy, x, out_f32=True, impl=1, splits=1), want, f"tn fp32 store {M}x{N}x{K}", tol=1e-2)
-        for splits in (0, 3, 8):
-            _check(G.mm_tn(dy, x, out_f32=True, impl=1, splits=splits), want, f"tn fp32 splits={splits} {M}x{N}x{K}", tol=1e-2)
+        for sk in (True, False):
+            _check(G.mm_tn(dy, x, out_f32=True, impl=1, split_k=sk), want, f"tn fp32 store split_k={sk} {M}x{N}x{K}", tol=1e-2)
             base = torch.randn(M, N, device=DEV)
             out = base.clone()
-            G.gemm(dy, x, a_mn=True, b_mn=True, c=out, out=out, out_f32=True, beta=1.0, impl=1, splits=splits)
-            _check(out, want + base, f"tn fp32 accumulate splits={splits} {M}x{N}x{K}", tol=1e-2)
+            G.gemm(dy, x, a_mn=True, b_mn=True, c=out, out=out, out_f32=True, beta=1.0, impl=1, split_k=sk)
+            _check(out, want + base, f"tn fp32 accumulate split_k={sk} {M}x{N}x{K}", tol=1e-2)
+        first = G.mm_tn(dy, x, out_f32=True, impl=1)
+        again = G.mm_tn(dy, x, out_f32=True, impl=1)
+        assert torch.equal(first, again), "the parts are summed in a fixed order: two runs must agree bit for bit"
     a, w = _rand(520, 328), _rand(328, 1000)
     o = torch.full((520, 1024), 7.0, device=DEV, dtype=torch.bfloat16)
     G.gemm(a, w, b_mn=True, out=o[:, :1000], impl=1)  # strided output: columns past N stay untouched
     _check(o[:, :1000], a.float() @ w.float(), "nn strided out")
     assert (o[:, 1000:] == 7.0).all()
+    # generic epilogue (addend, bf16) on a long contraction that is cut between pairs
+    a, b, c = _rand(256, 8192), _rand(300, 8192), _rand(256, 300)
+    _check(G.gemm(a, b, c=c, alpha=0.5, beta=2.0, impl=1), 0.5 * (a.float() @ b.float().t()) + 2.0 * c.float(), "nt addend, cut contraction")
