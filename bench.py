@@ -159,14 +159,19 @@ def max_over_ranks(ms: float, world: int) -> float:
     return float(t.item())
 
 
+HOST_ENQUEUE_MS: list[float] = []
+
+
 def timed_loop(step_fn, n_steps: int, world: int) -> float:
     """Milliseconds for n_steps calls of step_fn(i), device-timed, max over ranks."""
     barrier_sync(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t0 = time.perf_counter()
     for i in range(n_steps):
         step_fn(i)
     e1.record()
+    HOST_ENQUEUE_MS.append((time.perf_counter() - t0) * 1e3 / max(n_steps, 1))  # host time to enqueue one step
     barrier_sync(world)
     return max_over_ranks(e0.elapsed_time(e1), world)
 
@@ -206,6 +211,7 @@ def emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, impl, extra_cfg, h
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": (ms_e2e / args.steps) if ms_e2e else None},
         "gpu_launches": launches,
+        "host_enqueue_ms_per_step": round(HOST_ENQUEUE_MS[0], 2) if HOST_ENQUEUE_MS else None,
     }
     print(json.dumps(line), flush=True)
 
@@ -287,7 +293,8 @@ def run_ours(args):
     if trainer.ddp is not None and trainer.ddp.comm is not None:
         trainer.ddp.comm.check()  # raises if a bounded wait on a peer gave up during the run
     emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, "ours",
-         {"comm": comm, "sharded_muon": bool(cfg.optim.shard_muon), "ema_every": cfg.trainer.ema_every, **extra}, h2d, d2h)
+         {"comm": comm, "sharded_muon": bool(cfg.optim.shard_muon), "ema_every": cfg.trainer.ema_every,
+          "block_gemm": os.environ.get("SEGPT_BLOCK_GEMM", "native"), "attention": os.environ.get("SEGPT_ATTN_IMPL", "native"), **extra}, h2d, d2h)
     if world > 1:
         dist.destroy_process_group()
 

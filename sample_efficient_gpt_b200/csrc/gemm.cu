@@ -456,6 +456,7 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.n_static = 0;
   p.splits = 1;
   p.b_box_rows = 64;
+  p.epi_backoff_ns = 0;
   p.ws = nullptr;
   p.ws_flags = nullptr;
   for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;

@@ -15,7 +15,9 @@
 // the next tile's mainloop).  Two epilogues:
 //   EPI_TMA     : plain outputs.  tcgen05.ld -> registers -> 128-byte-swizzled staging tile -> TMA store, or TMA
 //                 reduce-add for fp32 outputs that accumulate into themselves (weight gradients).
-//   EPI_GENERIC : addend C, symmetric (mirrored) outputs, extra destinations in peer memory, routed outputs.
+//   EPI_TMA_C   : bf16 outputs with an addend: boxes of C are fetched by TMA into the warp's staging tiles ahead of the
+//                 accumulator, the result overwrites them in place and is stored by TMA.
+//   EPI_GENERIC : symmetric (mirrored) outputs, extra destinations in peer memory, routed outputs, fp32 addends.
 // Schedule (gemm_pair_sched.h): whole tiles dealt round-robin to the pairs; the tiles of the last, partly filled wave (or
 // all of them when there are fewer tiles than pairs) are cut into ranges of the contraction whose raw accumulators meet
 // in a workspace and are summed in a fixed order by the item of the last range, which also runs the epilogue.
@@ -39,14 +41,18 @@ namespace seg {
 using namespace sm100;
 
 constexpr int kPairThreads = 320;
-constexpr int kPairStages = 6;
+constexpr int kEpiGeneric = 0, kEpiTma = 1, kEpiTmaC = 2;
+// The addend variant keeps two 4 KB tiles per epilogue warp (each receives a box of C, is overwritten with the result and
+// stored), paid for with one stage of the ring.
+__host__ __device__ constexpr int pair_stages(int epi) { return epi == kEpiTmaC ? 5 : 6; }
+__host__ __device__ constexpr int pair_staging_bytes(int epi) { return epi == kEpiTmaC ? 8 * 8192 : 8 * 4096; }
 constexpr int kPairABytes = 128 * kPairK * 2;
 constexpr int kPairBBytes = 128 * kPairK * 2;
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
-constexpr int kPairStagingBytes = 8 * 4096;  // one 4 KB transposition / store tile per epilogue warp
-constexpr int kPairBarrierBytes = 256;
-constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + kPairStagingBytes + kPairBarrierBytes + 1024;
-constexpr int kEpiTma = 1, kEpiGeneric = 0;
+constexpr int kPairBarrierBytes = 512;
+__host__ __device__ constexpr int pair_smem_total(int epi) {
+  return pair_stages(epi) * kPairStageBytes + pair_staging_bytes(epi) + kPairBarrierBytes + 1024;  // + alignment slack
+}
 
 // A contributor's raw accumulator chunk goes to its slot; consecutive lanes write consecutive 16-byte pieces.
 __device__ __forceinline__ void slot_store(uint4* slot_chunk, int lane, const uint32_t* v) {
@@ -82,17 +88,18 @@ __device__ __forceinline__ bool wait_slot_flag(uint32_t* flag, const AbortState&
 template <bool A_MN, bool B_MN, typename OutT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_d, GemmParams p) {
-  constexpr int kStages = kPairStages;
+                 const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_c, GemmParams p) {
+  constexpr int kStages = pair_stages(EPI);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_area = smem + kStages * kPairStageBytes;
-  uint8_t* bar_area = stage_area + kPairStagingBytes;
+  uint8_t* bar_area = stage_area + pair_staging_bytes(EPI);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);  // leader's: bytes of both CTAs' loads
   uint64_t* empty_bar = full_bar + kStages;                     // each CTA's: its stage has been read by the MMAs
   uint64_t* acc_full = empty_bar + kStages;                     // each CTA's: the accumulator is complete
   uint64_t* acc_empty = acc_full + 2;                           // leader's: 16 epilogue warps have drained it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* c_bar = acc_empty + 2;                              // EPI_TMA_C: per epilogue warp and staging tile, the box of C has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(c_bar + 16);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,10 +118,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       mbar_init(smem_u32(&acc_full[a]), 1);
       mbar_init(smem_u32(&acc_empty[a]), 16);  // one arrival per epilogue warp of either CTA
     }
+    for (int a = 0; a < 16; ++a) mbar_init(smem_u32(&c_bar[a]), 1);
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
-    if (EPI == kEpiTma) prefetch_tensormap(&map_d);
+    if (EPI != kEpiGeneric) prefetch_tensormap(&map_d);
+    if (EPI == kEpiTmaC) prefetch_tensormap(&map_c);
   }
   if (warp == 0) {
     __syncwarp();
@@ -225,9 +234,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int ep = warp - 2;
     const int half = ep >> 2;
     const uint32_t accempty_leader = mapa_shared(smem_u32(&acc_empty[0]), 0);
-    uint8_t* stage_raw = stage_area + ep * 4096;
+    uint8_t* stage_raw = stage_area + ep * (pair_staging_bytes(EPI) / 8);
     int local_tile = 0;
     bool ok = true;
+    uint32_t c_phase = 0;  // EPI_TMA_C: phase bits of this warp's two addend barriers
     // EPI_TMA: one 4 KB staging tile per warp in the 128-byte-swizzle layout of the output's tensor map: 32 rows x 128
     // bytes (64 bf16 = two chunks, or 32 fp32 = one chunk); the 16-byte piece j of row r sits at slot j ^ (r & 7).
     constexpr bool kBf16 = sizeof(OutT) == 2;
@@ -253,10 +263,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       const bool owner = pair_item_owns(sch, tl);
-      const int n_parts = (owner && tl.ks > 0) ? tl.ks : 0;  // parts that earlier ranges of this tile left in the workspace
-      if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6)) { ok = false; break; }
+      // the sum of the ranges before this one sits in the slot of range ks - 1: every item adds it to its own accumulator,
+      // so the parts are summed in range order and nobody reads more than one
+      const int prev_slot = tl.ks > 0 ? pair_slot(sch, tl.ks - 1, tl.t) : -1;
+      const uint4* const prev = prev_slot >= 0 ? p.ws + ((size_t)(prev_slot * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32) : nullptr;
+      const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;  // first row of this warp's 32-row band
+      if (EPI == kEpiTmaC && owner && row0 < p.M) {
+        // the two boxes of C that this warp needs (64 columns each) are on their way before the accumulator is complete
+        if (lane == 0) {
+          bulk_wait_group_read0();  // the previous item's stores have left the staging tiles
+          for (int k = 0; k < 2; ++k) {
+            const int c0 = half * 128 + k * 64;
+            if (c0 < tl.nt && tl.n * kPairN + c0 < p.N) {
+              const uint32_t cb = smem_u32(&c_bar[ep * 2 + k]);
+              mbar_expect_tx(cb, 4096);
+              tma_load_3d(stage_u32 + k * 4096, &map_c, cb, tl.n * kPairN + c0, row0, tl.b);
+            }
+          }
+        }
+        __syncwarp();
+      }
+      if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6, p.epi_backoff_ns)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN;
+      if (prev != nullptr) {
+        if (lane == 0) ok = wait_slot_flag(p.ws_flags + (prev_slot * 2 + (int)rank) * 8 + ep, ab);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+      }
       if (!owner) {
         // -------- part of a tile: the raw accumulator goes to the item's slot, then the flag of this warp is raised
         const int slot = pair_slot(sch, tl.ks, tl.t);
@@ -268,6 +302,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint32_t v[32];
           tmem_ld_32x32(tmem_acc + c0, v);
           tmem_ld_wait_regs(v);
+          if (prev != nullptr) slot_add(prev + ci * (8 * 32), lane, v);
           slot_store(my_slot + ci * (8 * 32), lane, v);
         }
         __syncwarp();
@@ -276,15 +311,51 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ws_flags + (slot * 2 + (int)rank) * 8 + ep), "r"(1u) : "memory");
         }
       } else {
-        if (n_parts != 0) {
-          if (lane == 0) {
-            for (int i = 0; i < n_parts && ok; ++i) ok = wait_slot_flag(p.ws_flags + (pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep, ab);
+        if (EPI == kEpiTmaC) {
+          if (row0 < p.M) {
+#pragma unroll 1
+            for (int ci = 0; ci < 4; ++ci) {
+              const int c0 = half * 128 + ci * 32;
+              const int col = tl.n * kPairN + c0;
+              if (c0 >= tl.nt || col >= p.N) break;  // warp-uniform
+              const int k = ci >> 1;
+              uint32_t v[32];
+              tmem_ld_32x32(tmem_acc + c0, v);
+              if ((ci & 1) == 0) {  // first chunk of a box: its addend has landed
+                if (!mbar_wait(smem_u32(&c_bar[ep * 2 + k]), (c_phase >> k) & 1u, ab, 8)) { ok = false; break; }
+                c_phase ^= 1u << k;
+              }
+              tmem_ld_wait_regs(v);
+              if (prev != nullptr) slot_add(prev + ci * (8 * 32), lane, v);
+              uint4* slots = reinterpret_cast<uint4*>(stage_raw + k * 4096 + lane * 128);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4& u = slots[((ci & 1) * 4 + j) ^ (lane & 7)];
+                const uint4 cin = u;
+                const uint32_t cw[4] = {cin.x, cin.y, cin.z, cin.w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 cf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cw[e]));
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(p.alpha * __uint_as_float(v[8 * j + 2 * e]) + p.beta * cf.x,
+                                                                 p.alpha * __uint_as_float(v[8 * j + 2 * e + 1]) + p.beta * cf.y);
+                  ow[e] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                u = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+              }
+              const bool last_chunk = (ci == 3) || (c0 + 32 >= tl.nt) || (col + 32 >= p.N);
+              if ((ci & 1) == 1 || last_chunk) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_3d(&map_d, stage_u32 + k * 4096, tl.n * kPairN + half * 128 + k * 64, row0, tl.b);
+                  bulk_commit_group();
+                }
+              }
+            }
+            if (!ok) break;
           }
-          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-          if (!ok) break;
-        }
-        const int row0 = tl.m * kPairM + (int)rank * 128 + sub * 32;  // first row of this warp's 32-row band
-        if (EPI == kEpiTma) {
+        } else if (EPI == kEpiTma) {
           if (row0 < p.M) {
 #pragma unroll 1
             for (int ci = 0; ci < 4; ++ci) {
@@ -298,8 +369,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 __syncwarp();
               }
               tmem_ld_wait_regs(v);
-              for (int i = 0; i < n_parts; ++i)
-                slot_add(p.ws + ((size_t)(pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32) + ci * (8 * 32), lane, v);
+              if (prev != nullptr) slot_add(prev + ci * (8 * 32), lane, v);
               if (kBf16) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -388,8 +458,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               have_next = true;
             }
             tmem_ld_wait_regs(v);
-            for (int i = 0; i < n_parts; ++i)
-              slot_add(p.ws + ((size_t)(pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32) + ci * (8 * 32), lane, v);
+            if (prev != nullptr) slot_add(prev + ci * (8 * 32), lane, v);
             const int ncols = (p.N - col) < 32 ? (p.N - col) : 32;
             const bool fast = vec_ok && ncols == 32 && (C == nullptr || have_cur);
 #pragma unroll
@@ -459,16 +528,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();  // the staging tile is rewritten by the next chunk
           }
         }
-        if (n_parts != 0 && lane == 0) {  // the slots are free for the next launch
-          for (int i = 0; i < n_parts; ++i) p.ws_flags[(pair_slot(sch, i, tl.t) * 2 + (int)rank) * 8 + ep] = 0;
-        }
       }
+      if (prev != nullptr && lane == 0) p.ws_flags[(prev_slot * 2 + (int)rank) * 8 + ep] = 0;  // free for the next launch
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(accempty_leader + acc * 8);
       ++local_tile;
     }
-    if (EPI == kEpiTma && lane == 0) bulk_wait_group0();  // this warp's stores have left its staging tile and are complete
+    if (EPI != kEpiGeneric && lane == 0) bulk_wait_group0();  // this warp's stores have left its staging tile and are complete
   }
 
   // ------------------------------------------------------------------ teardown (also reached after an abort)
@@ -486,14 +553,15 @@ size_t gemm_pair_workspace_bytes() { return (size_t)kPairMaxSlots * kPairSlotPie
 size_t gemm_pair_flag_words() { return (size_t)kPairMaxSlots * 16; }
 
 template <bool A_MN, bool B_MN, typename OutT, int EPI>
-static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmParams& p, int pairs, cudaStream_t st) {
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const CUtensorMap& mc, const GemmParams& p, int pairs,
+                       cudaStream_t st) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, OutT, EPI>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemTotal) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_total(EPI)) != cudaSuccess) return -2;
     configured = true;
   }
-  kern<<<2 * pairs, kPairThreads, kPairSmemTotal, st>>>(ma, mb, md, p);
+  kern<<<2 * pairs, kPairThreads, pair_smem_total(EPI), st>>>(ma, mb, md, mc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -510,7 +578,7 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
     const char* e = std::getenv("SEGPT_GEMM_BBOX");
     return (e != nullptr && std::atoi(e) == 128) ? 128 : 64;
   }();
-  CUtensorMap ma, mb, md;
+  CUtensorMap ma, mb, md, mc;
   int r;
   if (a_mn_major)  // memory [K, M]
     r = make_tensor_map_3d(&ma, A, false, (uint64_t)M, (uint64_t)K, (uint64_t)batch, (uint64_t)lda, (uint64_t)bsa, 64, 64);
@@ -543,6 +611,11 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   p.ws = reinterpret_cast<uint4*>(workspace);
   p.ws_flags = ws_flags;
   p.b_box_rows = b_box_env;
+  static const int backoff_env = [] {
+    const char* e = std::getenv("SEGPT_GEMM_EPI_BACKOFF_NS");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  p.epi_backoff_ns = backoff_env;
   pair_choose_split(M, N, K, batch, p.symmetric, sm_count / 2, split_k != 0 && workspace != nullptr && ws_flags != nullptr && p.wait_flags == nullptr,
                     p.n_static, p.splits);
   const PairSched sched = make_pair_sched(M, N, K, batch, p.symmetric, p.n_static, p.splits);
@@ -553,19 +626,26 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   const size_t esz = out_f32 ? 4 : 2;
   const bool accumulate = C != nullptr && C == D && beta == 1.0f && out_f32;
   const bool aligned = (reinterpret_cast<uintptr_t>(D) % 16 == 0) && ((ldd * esz) % 16 == 0) && (batch == 1 || (bsd * esz) % 16 == 0);
-  const bool tma_epi = n_route == 0 && n_extra <= 0 && !symmetric && aligned && (C == nullptr || accumulate) && D != nullptr;
-  if (tma_epi) {
+  const bool plain = n_route == 0 && n_extra <= 0 && !symmetric && aligned && D != nullptr;
+  const bool tma_epi = plain && (C == nullptr || accumulate);
+  const bool tma_c_epi = plain && !tma_epi && !out_f32 && (reinterpret_cast<uintptr_t>(C) % 16 == 0);
+  md = ma;  // placeholders when unused
+  mc = ma;
+  if (tma_epi || tma_c_epi) {
     r = make_tensor_map_3d(&md, D, out_f32, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldd, (uint64_t)bsd, out_f32 ? 32 : 64, 32);
     if (r != 0) return 300 + r;
-    p.reduce = accumulate ? 1 : 0;
-  } else {
-    md = ma;  // unused
+    p.reduce = (tma_epi && accumulate) ? 1 : 0;
   }
-#define SEG_PAIR(AM, BM_)                                                                                         \
-  (tma_epi ? (out_f32 ? launch_pair<AM, BM_, float, kEpiTma>(ma, mb, md, p, pairs, st)                            \
-                      : launch_pair<AM, BM_, __nv_bfloat16, kEpiTma>(ma, mb, md, p, pairs, st))                   \
-           : (out_f32 ? launch_pair<AM, BM_, float, kEpiGeneric>(ma, mb, md, p, pairs, st)                        \
-                      : launch_pair<AM, BM_, __nv_bfloat16, kEpiGeneric>(ma, mb, md, p, pairs, st)))
+  if (tma_c_epi) {
+    r = make_tensor_map_3d(&mc, C, false, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldd, (uint64_t)bsd, 64, 32);
+    if (r != 0) return 400 + r;
+  }
+#define SEG_PAIR(AM, BM_)                                                                                             \
+  (tma_c_epi ? launch_pair<AM, BM_, __nv_bfloat16, kEpiTmaC>(ma, mb, md, mc, p, pairs, st)                            \
+   : tma_epi ? (out_f32 ? launch_pair<AM, BM_, float, kEpiTma>(ma, mb, md, mc, p, pairs, st)                          \
+                        : launch_pair<AM, BM_, __nv_bfloat16, kEpiTma>(ma, mb, md, mc, p, pairs, st))                 \
+             : (out_f32 ? launch_pair<AM, BM_, float, kEpiGeneric>(ma, mb, md, mc, p, pairs, st)                      \
+                        : launch_pair<AM, BM_, __nv_bfloat16, kEpiGeneric>(ma, mb, md, mc, p, pairs, st)))
   if (!a_mn_major && !b_mn_major) return SEG_PAIR(false, false);
   if (!a_mn_major && b_mn_major) return SEG_PAIR(false, true);
   if (a_mn_major && b_mn_major) return SEG_PAIR(true, true);

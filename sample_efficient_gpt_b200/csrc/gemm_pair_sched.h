@@ -1,15 +1,17 @@
 // Schedule of the CTA-pair GEMM (gemm_pair.cu): plain C++ that compiles for the host and the device, so the same
 // functions place the work in the kernel, size the grid on the host and can be checked exhaustively on a CPU.
 //
-// Tiles are 256 rows x (256 | last-column remainder) columns.  Order: all full-width tiles (column index fastest, then row
-// tile, then batch), then the narrower last-column tiles; a symmetric output lists only tiles on or above the diagonal.
+// Tiles are 256 rows x (256 | last-column remainder) columns.  Order: column index fastest (the narrower last-column tile
+// closes its row of tiles, so that the pairs that run narrow tiles - which move more operand bytes per FLOP - are always
+// a minority), then row tile, then batch; a symmetric output lists only tiles on or above the diagonal.
 // Work items are dealt round-robin to the pairs, so that the pairs running at the same time work on neighbouring tiles
 // and walk the contraction in step - operand panels shared between tiles are then fetched from HBM once and served from
 // L2 to the others.  The first n_static tiles are whole-tile items.  The remaining R tiles (the last, partly filled wave,
 // or everything when there are fewer tiles than pairs) are cut into `splits` ranges of the contraction, range index
-// outermost: items of ranges 0 .. splits-2 leave their raw fp32 accumulator in a workspace slot, the item of the last
-// range owns the tile, adds the parts in range order (deterministic) and runs the epilogue.  An owner's parts always
-// belong to items with a lower index, which their pairs reach no later than the owner reaches its own.
+// outermost: the item of range ks adds the running sum that range ks-1 left in its workspace slot to its own raw fp32
+// accumulator and leaves the new sum in its own slot; the item of the last range owns the tile and runs the epilogue on
+// the total.  The order of the additions is fixed, so results are reproducible, and the slot an item reads always
+// belongs to an item with a lower index, which its pair reaches no later than this one is reached.
 #pragma once
 #if !defined(__CUDACC__)
 #define __host__
@@ -27,7 +29,7 @@ constexpr int kPairMaxSplits = 12;
 
 struct PairSched {
   int m_tiles, n_full, tail_nt, batch, kb_total, symmetric;
-  int full_per_batch, tail_per_batch, full_count, total;
+  int per_batch, total;  // tiles per batch entry, tiles in all
   int n_static, splits, kb_per, rem_tiles, n_items;
 };
 
@@ -40,10 +42,10 @@ __host__ __device__ inline PairSched make_pair_sched(int M, int N, int K, int ba
   s.batch = batch;
   s.kb_total = (K + kPairK - 1) / kPairK;
   s.symmetric = symmetric;
-  s.full_per_batch = symmetric ? s.n_full * (s.n_full + 1) / 2 : s.m_tiles * s.n_full;
-  s.tail_per_batch = rem > 0 ? s.m_tiles : 0;
-  s.full_count = batch * s.full_per_batch;
-  s.total = s.full_count + batch * s.tail_per_batch;
+  const int n_cols = s.n_full + (rem > 0 ? 1 : 0);
+  // symmetric: row m holds column tiles m .. n_cols - 1
+  s.per_batch = symmetric ? n_cols * (n_cols + 1) / 2 - (n_cols - s.m_tiles) * (n_cols - s.m_tiles + 1) / 2 : s.m_tiles * n_cols;
+  s.total = batch * s.per_batch;
   s.splits = splits < 1 ? 1 : splits;
   s.n_static = (s.splits == 1 || n_static > s.total) ? s.total : (n_static < 0 ? 0 : n_static);
   s.rem_tiles = s.total - s.n_static;
@@ -58,30 +60,23 @@ struct PairItem {
 };
 
 __host__ __device__ inline void pair_tile_coords(const PairSched& s, int t, PairItem& c) {
-  if (t < s.full_count) {
-    c.b = t / s.full_per_batch;
-    int idx = t - c.b * s.full_per_batch;
-    if (s.symmetric) {  // rows of the upper triangle: row m holds tiles n = m .. n_full - 1
-      int m = 0, row = s.n_full;
-      while (idx >= row) {
-        idx -= row;
-        --row;
-        ++m;
-      }
-      c.m = m;
-      c.n = m + idx;
-    } else {
-      c.m = idx / s.n_full;
-      c.n = idx - c.m * s.n_full;
+  const int n_cols = s.n_full + (s.tail_nt > 0 ? 1 : 0);
+  c.b = t / s.per_batch;
+  int idx = t - c.b * s.per_batch;
+  if (s.symmetric) {
+    int m = 0, row = n_cols;
+    while (idx >= row) {
+      idx -= row;
+      --row;
+      ++m;
     }
-    c.nt = kPairN;
+    c.m = m;
+    c.n = m + idx;
   } else {
-    const int idx = t - s.full_count;
-    c.b = idx / s.tail_per_batch;
-    c.m = idx - c.b * s.tail_per_batch;
-    c.n = s.n_full;
-    c.nt = s.tail_nt;
+    c.m = idx / n_cols;
+    c.n = idx - c.m * n_cols;
   }
+  c.nt = c.n < s.n_full ? kPairN : s.tail_nt;
 }
 
 __host__ __device__ inline PairItem pair_item(const PairSched& s, int i) {
@@ -107,55 +102,24 @@ __host__ __device__ inline int pair_slot(const PairSched& s, int ks, int t) { re
 
 // ---------------------------------------------------------------------------------------------------------- host model
 // Makespan, in k-blocks of a full-width tile, of dealing a schedule round-robin to `pairs` pairs.  Each item costs its
-// k-blocks scaled by its width plus a fixed overhead (pipeline fill, accumulator hand-over, epilogue); an owner pays for
-// reading the parts.  Items come in at most four runs of equal cost (static full, static narrow, then per range: split
-// full, split narrow), which round-robin spreads evenly, so the load of a pair follows from counting.
-struct PairRun {
-  long long count;
-  double cost;
-};
+// k-blocks scaled by its width plus a fixed overhead (pipeline fill, accumulator hand-over, epilogue); an item of a cut tile also
+// pays for reading and writing the running sum.  Only evaluated for problems of a few waves (pair_choose_split).
 inline double pair_makespan(const PairSched& s, int pairs) {
-  const double kItemOverhead = 5.0, kPartRead = 3.0;
-  const double wt = s.tail_nt / 256.0;
-  PairRun runs[2 + 2 * kPairMaxSplits];
-  int n = 0;
-  const long long sf = s.n_static < s.full_count ? s.n_static : s.full_count;  // static full-width tiles
-  const long long st = s.n_static - sf;                                         // static narrow tiles
-  if (sf > 0) runs[n++] = {sf, s.kb_total + kItemOverhead};
-  if (st > 0) runs[n++] = {st, wt * s.kb_total + kItemOverhead};
-  const long long rf = s.full_count - sf, rt = s.rem_tiles - rf;  // split tiles of either width
-  for (int ks = 0; ks < s.splits && s.rem_tiles > 0; ++ks) {
-    const int kb0 = ks * s.kb_per, kb1 = kb0 + s.kb_per < s.kb_total ? kb0 + s.kb_per : s.kb_total;
-    const double extra = kItemOverhead + (ks == s.splits - 1 ? kPartRead * (s.splits - 1) : 1.0);
-    if (rf > 0) runs[n++] = {rf, (double)(kb1 - kb0) + extra};
-    if (rt > 0) runs[n++] = {rt, wt * (kb1 - kb0) + extra};
-  }
+  const double kItemOverhead = 5.0, kPartRead = 2.0, kPartWrite = 1.0;
   const int P = s.n_items < pairs ? s.n_items : pairs;
   if (P <= 0) return 0.0;
-  // load of pair p = sum over runs of (items of the run that land on p) * cost; evaluate at the breakpoints only
-  double best = 0.0;
-  long long start = 0;
-  long long marks[2 * (2 + 2 * kPairMaxSplits) + 1];
-  int nm = 0;
-  marks[nm++] = 0;
-  for (int r = 0; r < n; ++r) {
-    marks[nm++] = start % P;
-    start += runs[r].count;
-    marks[nm++] = start % P;
+  double load[256];
+  if (P > 256) return 0.0;
+  for (int i = 0; i < P; ++i) load[i] = 0.0;
+  for (int i = 0; i < s.n_items; ++i) {
+    const PairItem it = pair_item(s, i);
+    double c = (it.nt / 256.0) * (it.kb1 - it.kb0) + kItemOverhead;
+    if (it.ks >= 0) c += (it.ks > 0 ? kPartRead : 0.0) + (it.ks < s.splits - 1 ? kPartWrite : 0.0);
+    load[i % P] += c;
   }
-  for (int mi = 0; mi < nm; ++mi) {
-    const long long p = marks[mi];
-    double load = 0.0;
-    long long s0 = 0;
-    for (int r = 0; r < n; ++r) {
-      // items s0 .. s0 + count - 1 go to pairs (index % P): how many land on p
-      const long long first = s0 + ((p - s0 % P) + P) % P;
-      if (first < s0 + runs[r].count) load += (double)((s0 + runs[r].count - 1 - first) / P + 1) * runs[r].cost;
-      s0 += runs[r].count;
-    }
-    best = load > best ? load : best;
-  }
-  return best;
+  double m = 0.0;
+  for (int i = 0; i < P; ++i) m = load[i] > m ? load[i] : m;
+  return m;
 }
 
 // Chooses how many trailing tiles to cut along the contraction, and into how many ranges.

@@ -37,6 +37,7 @@ struct GemmParams {
   int reduce;          // TMA epilogue: 1 = add the tile into D (cp.reduce.async.bulk ... add), 0 = store it
   int n_static, splits;  // schedule (gemm_pair_sched.h): tiles computed whole; ranges of the contraction for the others
   int b_box_rows;        // rows of the K-major B operand's TMA box (64 or 128)
+  int epi_backoff_ns;    // sleep between the epilogue warps' polls of the accumulator barrier (0: none)
   uint4* ws;             // workspace slots for the parts of tiles that are cut along the contraction
   uint32_t* ws_flags;    // one word per (slot, rank, epilogue warp), zero between launches
 };

@@ -79,7 +79,9 @@ struct AbortState {
   long long limit = kWaitCycles;
 };
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortState& ab, int code) {
+// `backoff_ns` > 0: sleep that long between polls - for roles whose wake-up latency is hidden (an epilogue that waits for a
+// whole mainloop), so that their polling does not take issue slots and power from the roles that feed the tensor cores.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortState& ab, int code, unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -90,6 +92,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
       atomicCAS(ab.global_status, 0, code);
       return false;
     }
+    if (backoff_ns != 0) __nanosleep(backoff_ns);
   }
 }
 

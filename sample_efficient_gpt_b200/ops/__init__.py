@@ -156,9 +156,9 @@ def swiglu_bwd(df, u):
 
 # ----------------------------------------------------------------------------- GEMMs
 def _native_gemm(*tensors) -> bool:
-    """``SEGPT_BLOCK_GEMM=native`` runs the block projections (and their gradients) on this package's tcgen05 GEMM instead
-    of the library GEMM; the default is the library, which is 15-25 % faster on these plain shapes."""
-    if os.environ.get("SEGPT_BLOCK_GEMM", "library") != "native":
+    """The block projections (and their gradients) run on this package's tcgen05 GEMM (CTA pairs, csrc/gemm_pair.cu);
+    ``SEGPT_BLOCK_GEMM=library`` sends them to the library GEMM instead (comparison runs)."""
+    if os.environ.get("SEGPT_BLOCK_GEMM", "native") != "native":
         return False
     from sample_efficient_gpt_b200.ops import gemm as G
 
@@ -166,7 +166,8 @@ def _native_gemm(*tensors) -> bool:
 
 
 def matmul_nt(x: Tensor, w: Tensor, out_dtype=None) -> Tensor:
-    """x [M,K] @ w[N,K]^T -> [M,N].  Library GEMM (cuBLAS on a GPU) unless the tcgen05 GEMM is selected."""
+    """x [M,K] @ w[N,K]^T -> [M,N] on the tcgen05 GEMM; the library GEMM for CPU tensors, fp32 runs and shapes that do
+    not meet the TMA alignment rules."""
     if out_dtype in (None, x.dtype) and _native_gemm(x, w):
         from sample_efficient_gpt_b200.ops import gemm as G
 

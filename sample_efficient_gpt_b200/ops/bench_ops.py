@@ -46,11 +46,33 @@ def timeit(fn, iters: int = 10, warmup: int = 3, flush: bool = True) -> float:
     return total / iters
 
 
+def time_sustained(fn, seconds: float = 1.0) -> float:
+    """Milliseconds per call when the call runs back to back for about ``seconds`` (the power cap, not the burst clock,
+    then sets the rate - the state a kernel meets inside a training step)."""
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    n = max(20, int(seconds * 1e3 / max(e0.elapsed_time(e1) / 20, 1e-3)))
+    for _ in range(n // 4):  # bring the chip to its steady power state first
+        fn()
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
 def rnd(*shape, scale=0.5):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
 
-def _bench_gemm_one(kind, M, N, K, batch, iters, split_k, label=""):
+def _bench_gemm_one(kind, M, N, K, batch, iters, split_k, label="", sustained=False):
     from sample_efficient_gpt_b200.ops import gemm as G
 
     bs = (batch,) if batch > 1 else ()
@@ -67,6 +89,12 @@ def _bench_gemm_one(kind, M, N, K, batch, iters, split_k, label=""):
         ours = lambda impl: G.mm_tn(x, w, out=out, out_f32=True, impl=impl, split_k=split_k)  # noqa: E731
         lib = (lambda: torch.bmm(x.mT, w, out_dtype=torch.float32, out=out)) if bs else (lambda: torch.mm(x.mT, w, out_dtype=torch.float32, out=out))
     fl = 2.0 * M * N * K * max(batch, 1) / 1e9
+    if sustained:
+        t_p, t_l = time_sustained(lambda: ours(1)), time_sustained(lib)
+        print(json.dumps({"op": f"gemm_{kind}", "label": label, "mode": "sustained", "shape": [batch, M, N, K], "pair_ms": round(t_p, 4),
+                          "pair_tflops": round(fl / t_p, 1), "cublas_ms": round(t_l, 4), "cublas_tflops": round(fl / t_l, 1),
+                          "status": G.status()}), flush=True)
+        return
     t_p, t_s, t_l = timeit(lambda: ours(1), iters), timeit(lambda: ours(0), iters), timeit(lib, iters)
     print(json.dumps({"op": f"gemm_{kind}", "label": label, "shape": [batch, M, N, K], "out": "fp32" if f32 else "bf16",
                       "pair_ms": round(t_p, 4), "pair_tflops": round(fl / t_p, 1), "single_ms": round(t_s, 4),
@@ -79,11 +107,11 @@ def bench_gemm(a):
     if a.shapes == "block":  # IMU-1 430M projections at T tokens: y = x W^T, dx = dy W, dW = dy^T x
         T = a.m
         for name, n_out, n_in in [("qkv+gate", 1944, 1152), ("out", 1152, 1152), ("up", 6144, 1152), ("down", 1152, 3072)]:
-            _bench_gemm_one("nt", T, n_out, n_in, 1, a.iters, sk, name + " fwd")
-            _bench_gemm_one("nn", T, n_in, n_out, 1, a.iters, sk, name + " dgrad")
-            _bench_gemm_one("tn", n_out, n_in, T, 1, a.iters, sk, name + " wgrad")
+            _bench_gemm_one("nt", T, n_out, n_in, 1, a.iters, sk, name + " fwd", a.sustained)
+            _bench_gemm_one("nn", T, n_in, n_out, 1, a.iters, sk, name + " dgrad", a.sustained)
+            _bench_gemm_one("tn", n_out, n_in, T, 1, a.iters, sk, name + " wgrad", a.sustained)
         return
-    _bench_gemm_one(a.kind, a.m, a.n, a.k, a.batch, a.iters, sk)
+    _bench_gemm_one(a.kind, a.m, a.n, a.k, a.batch, a.iters, sk, "", a.sustained)
 
 
 def bench_ns(a):
@@ -316,6 +344,7 @@ def main():
     p.add_argument("--cols", type=int, default=3072)
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--sustained", action="store_true", help="gemm: time about a second of back-to-back calls (power-capped rate) instead of flushed single calls")
     p.add_argument("--no-split-k", action="store_true", help="gemm: whole tiles only, no tile is cut along the contraction")
     p.add_argument("--shapes", default="", help="gemm: 'block' runs the IMU-1 block shapes (forward, data gradient, weight gradient)")
     a = p.parse_args()

@@ -1,7 +1,8 @@
 """Newton-Schulz chain on the tcgen05 GEMM.
 
-Per iteration and for a whole batch of same-shape matrices: the Gram matrix ``A`` and ``B = b A + c A A`` compute only
-the tiles on or above the diagonal and mirror them (both are symmetric); the update ``a X + B X`` (wide X) or
+Per iteration and for a whole batch of same-shape matrices: the Gram matrix ``A`` computes only the tiles on or above
+the diagonal and mirrors them; ``B = b A + c A A`` is computed in full, because with the addend fetched by TMA the
+plain epilogue is faster than the mirrored one on this short contraction; the update ``a X + B X`` (wide X) or
 ``a X + X B`` (tall X) reads its operands in place (K-major and MN-major tiles), so tall matrices are never
 transposed: for ``R > C`` the chain runs on ``X^T`` implicitly with ``A = X^T X``.  Every product accumulates in fp32
 and is rounded to bf16, as in the reference (training/optimizers/muon_triton.py:327-377).  Shapes the TMA path
@@ -13,7 +14,11 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
+import os
+
 from sample_efficient_gpt_b200.ops import gemm as G
+
+_SYM_B = os.environ.get("SEGPT_NS_SYMMETRIC_B", "0") == "1"  # mirrored instead of full computation of b A + c A A
 
 
 def ns_iterations(X: Tensor, Y: Tensor, coeffs, final_extra_dst=None) -> Tensor:
@@ -36,7 +41,7 @@ def ns_iterations(X: Tensor, Y: Tensor, coeffs, final_extra_dst=None) -> Tensor:
                 G.gemm(X, X, out=A, a_mn=True, b_mn=True, symmetric=True)  # X^T X
             else:
                 G.gemm(X, X, out=A, symmetric=True)  # X X^T
-            G.gemm(A, A, c=A, out=B, alpha=c, beta=b, symmetric=True)
+            G.gemm(A, A, c=A, out=B, alpha=c, beta=b, symmetric=_SYM_B)
             extra = final_extra_dst(Y) if (it == last and final_extra_dst is not None) else None
             pushed = pushed or bool(extra)
             if tall:

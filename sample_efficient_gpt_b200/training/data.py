@@ -129,11 +129,15 @@ class MemoryMappedDataset:
     def _prefetch_loop(self):
         pin = torch.cuda.is_available()
         while True:
-            inputs, targets = self._get_batch_internal(self._prefetch_batch_size)
-            # contiguous pinned copies so that .to(device, non_blocking=True) is a true async DMA
-            inputs, targets = inputs.contiguous(), targets.contiguous()
-            if pin:
-                inputs, targets = inputs.pin_memory(), targets.pin_memory()
+            try:
+                inputs, targets = self._get_batch_internal(self._prefetch_batch_size)
+                # contiguous pinned copies so that .to(device, non_blocking=True) is a true async DMA
+                inputs, targets = inputs.contiguous(), targets.contiguous()
+                if pin:
+                    inputs, targets = inputs.pin_memory(), targets.pin_memory()
+            except BaseException as e:  # handed to the consumer: get_batch() raises it instead of waiting forever
+                self._queue.put(e)
+                return
             self._queue.put((inputs, targets))
 
     def get_batch(self, batch_size: int) -> tuple[Tensor, Tensor]:
@@ -145,7 +149,11 @@ class MemoryMappedDataset:
             self._thread.start()
         elif batch_size != self._prefetch_batch_size:
             raise ValueError(f"get_batch() batch_size changed: {batch_size} != {self._prefetch_batch_size}")
-        return self._queue.get()
+        item = self._queue.get()
+        if isinstance(item, BaseException):
+            self._queue.put(item)  # later calls fail the same way
+            raise RuntimeError("the data prefetch thread failed") from item
+        return item
 
     def get_iterator(self, batch_size: int) -> Iterator[tuple[Tensor, Tensor]]:
         """Sequential, non-overlapping windows of a single-file dataset; the last partial batch is dropped."""

@@ -86,23 +86,22 @@ class FusedEngine:
 
     # ------------------------------------------------------------------ helpers
     def refresh_shadows(self):
-        """Re-cast every GEMM weight from its fp32 master (after a load or an external update)."""
-        if self.lp == torch.float32:
-            return
-        ps = list(self.shadows.keys())
-        torch._foreach_copy_([self.shadows[p] for p in ps], [p.detach() for p in ps])
+        """Re-cast every GEMM weight from its fp32 master (after a load or an external update).  In fp32 runs most shadows
+        are the masters themselves; the stacked expert weights are copies in every precision."""
+        ps = [p for p in self.shadows if self.shadows[p].data_ptr() != p.data_ptr()]
+        if ps:
+            torch._foreach_copy_([self.shadows[p] for p in ps], [p.detach() for p in ps])
         if self.moe is not None:
             self.moe.refresh()
 
     def register_with(self, optimizers):
-        """Let the optimizers write the bf16 shadows in the same kernel that updates the masters."""
-        if self.lp == torch.float32:
-            return
+        """Let the optimizers write the shadows (bf16 copies; in fp32 runs only the stacked expert weights are copies) in the
+        same kernel that updates the masters."""
         for opt in optimizers:
             if hasattr(opt, "lowp_shadows"):
                 for g in opt.param_groups:
                     for p in g["params"]:
-                        if p in self.shadows:
+                        if p in self.shadows and self.shadows[p].data_ptr() != p.data_ptr():
                             opt.lowp_shadows[p] = self.shadows[p]
 
     def ensure_grads(self):

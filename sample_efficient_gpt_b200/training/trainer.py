@@ -210,6 +210,12 @@ class Trainer:
         self._nan_guard = NonFiniteGuard(tc.nan_abort_after)
         self._micro_in_window = 0
         self.last_step_ms = 0.0
+        self.status_probes: list[tuple[str, Any]] = []
+        if self.device.type == "cuda":
+            from sample_efficient_gpt_b200 import ops
+
+            if ops.has_kernel("gemm_status"):
+                self.status_probes.append(("a GEMM / attention kernel", lambda: ops.ext().gemm_status(self.device.index)))
         logger.info(
             f"Init [rank={self.rank}]: max_steps={tc.max_steps}, start_iter={self.iteration}, "
             f"val_every={tc.val_every}, save_every={tc.save_every}, world_size={self.world_size}, "
@@ -290,6 +296,8 @@ class Trainer:
     def load_state(self, path, model_only=True, optimizers_only=False):
         logger.info(f"Loading {model_only=} state from {str(path)}")
         if optimizers_only:
+            if self.ep_group is not None and len(self.optimizers) == 3:
+                return self._load_optimizers_expert_parallel(path)
             return load_optimizer(path, self.cfg, self.model, self.optimizers)
         self.iteration, self.run_id = load_model(path, self.cfg, self.model)
         if self.engine is not None:
@@ -297,18 +305,68 @@ class Trainer:
         logger.info(f"Restored {self.iteration} iteration")
         return self.iteration
 
+    def _load_optimizers_expert_parallel(self, path):
+        """Files hold the state of a run with all experts in one process (two optimizers); this rank takes the state of the
+        replicated matrices and of its own experts out of it."""
+        from sample_efficient_gpt_b200.training.ep_checkpoint import split_muon_state
+
+        ckpt = torch.load(path, map_location="cpu", weights_only=False)
+        saved = ckpt.get("optimizer")
+        if not saved or saved[0] is None or len(saved) < 2:
+            logger.info("no optimizers detected in the checkpoint, skipping...")
+            return
+        shared_sd, local_sd = split_muon_state(saved[1], self.model, self.optimizers[1], self.optimizers[2], self.ep_group)
+        for opt, sd in zip(self.optimizers, (saved[0], shared_sd, local_sd)):
+            opt.load_state_dict(sd)
+            for p_, st in opt.state.items():
+                for k, v in list(st.items()):
+                    if torch.is_tensor(v):
+                        st[k] = v.to(p_.device)
+            if hasattr(opt, "_batches"):
+                opt.load_state_dict(opt.state_dict())  # rebind the stacked storage on the right device
+
+    def check_kernel_status(self):
+        """Raise ``CommTimeout`` if a bounded wait inside one of this package's kernels gave up since the last check (the kernel
+        then returned early and what it produced is incomplete).  Reads the status words on the device, which synchronises;
+        the training loop calls it where it synchronises anyway (logging steps) and before every checkpoint, so that no file
+        is written after a failed step.  ``status_probes`` holds the readers (name, callable returning a code, 0 = fine)."""
+        from sample_efficient_gpt_b200.parallel.symm import CommTimeout
+
+        if self.ddp is not None and self.ddp.comm is not None:
+            self.ddp.comm.check()
+        for name, probe in self.status_probes:
+            code = int(probe())
+            if code != 0:
+                raise CommTimeout(f"a bounded wait inside {name} gave up (status {code}) at iteration {self.iteration}")
+
     def save_state(self):
-        """Collective when the Muon step is sharded (owner-resident momentum is gathered first)."""
+        """Collective when the Muon step is sharded (owner-resident momentum is gathered first) or experts are split over
+        ranks (every rank's experts and their optimizer state are gathered into the single-process layout)."""
+        self.check_kernel_status()
         for opt in self.optimizers or []:
             if hasattr(opt, "consolidate_state"):
                 opt.consolidate_state()
+        model_sd, opt_sds, ema_sd = None, None, None
+        if self.ep_group is not None and len(self.optimizers or []) == 3:
+            from sample_efficient_gpt_b200.training.ep_checkpoint import gather_experts, gather_full_state
+
+            full = gather_full_state(self.model, self.optimizers, self.ep_group)
+            if self.ema is not None:
+                ema_sd = gather_experts(self.ema.state_dict(), self.model, self.ep_group)
+            if full is not None:
+                model_sd, opt_sds = full
         if not self.rank_zero_only:
             return
         logger.info(f"Saving training state at iter={self.iteration}")
         run_id = getattr(self.wandb, "id", None) if self.wandb is not None else self.run_id
-        save_checkpoint(self.save_dir / f"{self.iteration}.pt", self.cfg, self.model, self.optimizers, self.iteration, run_id)
+        fpath = self.save_dir / f"{self.iteration}.pt"
+        if model_sd is not None:
+            save_checkpoint(fpath, self.cfg, model_sd, None, self.iteration, run_id, extra={"optimizer": opt_sds})
+        else:
+            save_checkpoint(fpath, self.cfg, self.model, self.optimizers, self.iteration, run_id)
         if self.ema is not None:
-            save_checkpoint(self.save_dir / f"{self.iteration}_ema.pt", self.cfg, self.ema.state_dict(), None, self.iteration, run_id)
+            save_checkpoint(self.save_dir / f"{self.iteration}_ema.pt", self.cfg, ema_sd if ema_sd is not None else self.ema.state_dict(),
+                            None, self.iteration, run_id)
 
     def log(self, data, rank_zero=True):
         if (not rank_zero) or self.rank_zero_only:
@@ -401,6 +459,29 @@ class Trainer:
             coef /= self.world_size
         return coef
 
+    def _expert_parallel_grad_norm(self, params, max_norm: float | None, ga: int) -> Tensor:
+        """Global gradient norm when experts are split over ranks: the replicated parameters' (already reduced) gradients
+        count once, every rank's own experts are added through one scalar all-reduce, so that all ranks see the same norm
+        and - with clipping on - scale by the same factor (replicated weights then stay identical)."""
+        named = list(self.model.named_parameters())
+        expert_grads = [p.grad for n, p in named if p.grad is not None and ".experts." in n]
+        shared_grads = [p.grad for n, p in named if p.grad is not None and ".experts." not in n]
+        sq_local = torch.stack([n.float() ** 2 for n in torch._foreach_norm(expert_grads)]).sum() if expert_grads else torch.zeros((), device=self.device)
+        dist.all_reduce(sq_local, group=self.ep_group)
+        sq_shared = None
+        if self.ddp is not None and self.ddp.comm is not None and ga == 1:
+            in_buckets = [p.grad for n, p in named if p.grad is not None and ".experts." not in n and p not in self.ddp.param_bucket]
+            sq_shared = self.ddp.reduced_grad_norm(in_buckets)
+            sq_shared = None if sq_shared is None else sq_shared.float() ** 2
+        if sq_shared is None:
+            sq_shared = torch.stack([n.float() ** 2 for n in torch._foreach_norm(shared_grads)]).sum()
+        norm = (sq_shared + sq_local).sqrt()
+        if max_norm is not None:
+            factor = (max_norm / (norm + 1e-8)).clamp(max=1.0)
+            factor = torch.where(norm >= max_norm, factor, torch.ones_like(factor))
+            torch._foreach_mul_([p.grad for p in params], factor)
+        return norm
+
     def _zero_grads(self):
         if self.ddp is not None:
             self.ddp.zero_grad()
@@ -451,7 +532,9 @@ class Trainer:
             if self.ddp is not None:
                 time_comm = self.ddp.finish_gradient_synchronization()
             params = [p for p in self.model.parameters() if p.grad is not None]
-            if tc.clip_fix:
+            if self.ep_group is not None:
+                gnorm = self._expert_parallel_grad_norm(params, tc.max_grad_norm if tc.clip_fix else None, ga)
+            elif tc.clip_fix:
                 gnorm = clip_grad_norm_(params, tc.max_grad_norm)
             else:  # norm only: the reference's clipping never scales
                 gnorm = None
@@ -506,6 +589,13 @@ class Trainer:
                 out[k] = v.item() if torch.is_tensor(v) else v
         return out
 
+    def _check_finite(self, loss: Tensor):
+        bad = (~torch.isfinite(loss.detach().float())).float().reshape(1)
+        if self.is_distributed:
+            bad = bad.to(self.device)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        self._nan_guard.check(float("nan") if float(bad.item()) > 0 else 0.0)
+
     def fetch_batch(self) -> tuple[Tensor, Tensor]:
         inputs, targets = self.train_dataset.get_batch(self.cfg.data.batch_size)
         return inputs.to(self.device, non_blocking=True), targets.to(self.device, non_blocking=True)
@@ -530,6 +620,11 @@ class Trainer:
             need_log = self.rank_zero_only and (self.iteration % tc.log_every == 0)
             if cuda:
                 ev1.record()
+            if self.iteration % tc.log_every == 0:
+                # every rank takes the same decision at the same iteration: a failed bounded wait or a run of non-finite losses
+                # stops all of them here instead of leaving the others to wait for a rank that has raised
+                self.check_kernel_status()
+                self._check_finite(stats["train_loss"])
             if need_log:
                 if cuda:
                     ev1.synchronize()
@@ -538,7 +633,6 @@ class Trainer:
                     stats["step_time"] = time.monotonic() - t0
                 self.last_step_ms = stats["step_time"] * 1e3
                 s = self.postprocess_step_stats(stats)
-                self._nan_guard.check(float(s["train_loss"]))
                 logger.info(f"Train iteration {self.iteration}")
                 self.log(
                     {

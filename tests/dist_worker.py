@@ -283,6 +283,89 @@ def moe_gpu(rank, world):
         assert torch.allclose(a, b, atol=3e-2, rtol=0.1), (n, float((a - b).abs().max()))
 
 
+def moe_ckpt_cpu(rank, world):
+    """Expert-parallel trainer on gloo ranks: a checkpoint holds every rank's experts and their optimizer state in the layout
+    of a single process; it reloads under expert parallelism (each rank finds its own experts and state) and in one
+    process; with clipping on, replicated parameters stay bit-identical across ranks."""
+    import tempfile
+
+    from sample_efficient_gpt_b200.training.trainer import Trainer
+    from sample_efficient_gpt_b200.utils.config_tools import apply_overrides, load_cfg
+
+    tmp = [tempfile.mkdtemp(prefix="segpt_epckpt_") if rank == 0 else None]
+    dist.broadcast_object_list(tmp, src=0)
+    over = {"trainer.device": "cpu", "trainer.dtype": "float32", "trainer.dist_mode": "ddp_ep", "model.vocab_size": 512,
+            "data.batch_size": 2 * world, "data.context_length": 32, "model.n_experts": 2 * world, "model.moe_top_k": 2,
+            "model.moe_d_ff": 64, "model.moe_capacity_factor": 2.0, "model.moe_aux_loss_weight": 0.01, "trainer.save_dir": tmp[0],
+            "trainer.clip_fix": True, "trainer.max_grad_norm": 0.05, "trainer.ema_every": 1, "data.train_path": "", "data.validation_path": ""}
+    cfg = apply_overrides(load_cfg("tiny_cpu.yaml"), over)
+    tr = Trainer(cfg)
+    assert len(tr.optimizers) == 3 and tr.ep_group is not None
+    g = torch.Generator().manual_seed(5 + rank)
+    for _ in range(3):
+        w = torch.randint(0, 512, (2, 33), generator=g)
+        log = tr.train_step(w[:, :-1], w[:, 1:])
+        tr.iteration += 1
+    assert float(log["grad_norm"]) > 0.05, "the test wants clipping to be active"
+    norms = [torch.zeros(1) for _ in range(world)]
+    dist.all_gather(norms, log["grad_norm"].reshape(1).float())
+    assert all(torch.equal(n, norms[0]) for n in norms), "every rank must see the same global gradient norm"
+    shared = torch.cat([p.detach().flatten() for n, p in tr.model.named_parameters() if ".experts." not in n])
+    other = [torch.empty_like(shared) for _ in range(world)]
+    dist.all_gather(other, shared)
+    assert all(torch.equal(o, shared) for o in other), "replicated parameters diverged under clipping"
+    tr.save_state()
+    dist.barrier()
+    path = Path(tmp[0]) / f"{tr.iteration}.pt"
+    ck = torch.load(path, map_location="cpu", weights_only=False)
+    E = 2 * world
+    for kind in ("up", "down"):
+        keys = sorted(int(k.rsplit(".", 1)[1]) for k in ck["model"] if k.startswith(f"blocks.0.ffn.experts.{kind}."))
+        assert keys == list(range(E)), f"file holds experts {keys}"
+    ema = torch.load(Path(tmp[0]) / f"{tr.iteration}_ema.pt", map_location="cpu", weights_only=False)["model"]
+    assert sum(k.startswith("blocks.0.ffn.experts.up.") for k in ema) == E
+    assert len(ck["optimizer"]) == 2
+    # this rank's experts and their momentum are in the file under their global ids
+    mine = {n: p for n, p in tr.model.named_parameters() if ".experts." in n}
+    for n, p in mine.items():
+        head, e = n.rsplit(".", 1)
+        assert torch.equal(ck["model"][f"{head}.{int(e) + rank * 2}"], p.detach()), n
+    # reload under expert parallelism: parameters and optimizer state come back exactly
+    tr2 = Trainer(cfg, load_from=str(path))
+    assert tr2.iteration == tr.iteration
+    for (n, a), (_, b) in zip(tr.model.named_parameters(), tr2.model.named_parameters()):
+        assert torch.equal(a, b), f"parameter {n} after reload"
+    for oa, ob in zip(tr.optimizers, tr2.optimizers):
+        for ga, gb in zip(oa.param_groups, ob.param_groups):
+            for pa, pb in zip(ga["params"], gb["params"]):
+                for k, v in oa.state[pa].items():
+                    if torch.is_tensor(v):
+                        assert torch.equal(v, ob.state[pb][k]), f"optimizer state {k} after reload"
+    # one more step from both: identical results
+    w = torch.randint(0, 512, (2, 33), generator=torch.Generator().manual_seed(77 + rank))
+    la, lb = tr.train_step(w[:, :-1], w[:, 1:]), tr2.train_step(w[:, :-1], w[:, 1:])
+    assert torch.allclose(la["train_loss"], lb["train_loss"]), (float(la["train_loss"]), float(lb["train_loss"]))
+    for (n, a), (_, b) in zip(tr.model.named_parameters(), tr2.model.named_parameters()):
+        assert torch.allclose(a, b, atol=1e-6), f"{n} differs by {float((a - b).abs().max())} one step after the reload"
+    dist.barrier()
+    if rank == 0:  # the same file in a process that holds all experts (what a single-GPU user or a converter sees)
+        from sample_efficient_gpt_b200.models import build_model
+        from sample_efficient_gpt_b200.utils.config_tools import load_config
+
+        full = build_model(load_config(ck["config"]).model, device="cpu", dtype=torch.float32)
+        missing = full.load_state_dict(ck["model"], strict=True)
+        assert not missing.missing_keys and not missing.unexpected_keys
+        n_mats = sum(1 for n, p in full.named_parameters() if p.ndim >= 2 and not any(k in n for k in ("embedding", "lm_head", ".router.")))
+        assert sum(len(g["params"]) for g in ck["optimizer"][1]["param_groups"]) == n_mats
+        from sample_efficient_gpt_b200.optim import NorMuonCWD
+
+        opt = NorMuonCWD([p for n, p in full.named_parameters() if p.ndim >= 2 and not any(k in n for k in ("embedding", "lm_head", ".router."))])
+        opt.load_state_dict(ck["optimizer"][1])  # group structure and shapes match a freshly built optimizer
+        for grp in opt.param_groups:
+            for p in grp["params"]:
+                assert opt.state[p]["momentum_buffer"].shape == p.shape
+
+
 def main():
     mode = sys.argv[1]
     cuda = mode.endswith("_gpu")
@@ -291,7 +374,8 @@ def main():
     dist.init_process_group("nccl" if cuda else "gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     try:
-        {"ddp_cpu": ddp_cpu, "moe_ep_cpu": moe_ep_cpu, "comm_gpu": comm_gpu, "train_gpu": train_gpu, "moe_gpu": moe_gpu}[mode](rank, world)
+        {"ddp_cpu": ddp_cpu, "moe_ep_cpu": moe_ep_cpu, "comm_gpu": comm_gpu, "train_gpu": train_gpu, "moe_gpu": moe_gpu,
+         "moe_ckpt_cpu": moe_ckpt_cpu}[mode](rank, world)
         dist.barrier()
         if rank == 0:
             print(f"WORKER-OK {mode}", flush=True)

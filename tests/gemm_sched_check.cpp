@@ -1,7 +1,6 @@
 // Host check of the CTA-pair GEMM's schedule: for a list of shapes, every k-block of every tile is covered exactly once,
-// every tile has exactly one owning item, the parts an owner reads are written by items with a lower index (so the pair
-// that holds them reaches them no later than the owner reaches its item), slots are unique and inside the workspace, and
-// the makespan model agrees with a direct simulation of the round-robin deal.  Prints "ok <cases>" or the first violation.
+// every tile has exactly one owning item, the running sum an item reads was written by the item of the range before it, which has a lower index (so the
+// pair that holds it reaches it no later than the reader reaches its own item), and slots are unique and inside the workspace.  Prints "ok <cases>" or the first violation.
 #include <cstdio>
 #include <cstdlib>
 #include <cmath>
@@ -11,20 +10,6 @@
 #include "gemm_pair_sched.h"
 
 using namespace seg;
-
-static double simulate(const PairSched& s, int pairs) {
-  const int P = s.n_items < pairs ? s.n_items : pairs;
-  std::vector<double> load(P > 0 ? P : 1, 0.0);
-  for (int i = 0; i < s.n_items; ++i) {
-    const PairItem it = pair_item(s, i);
-    double c = (it.nt / 256.0) * (it.kb1 - it.kb0) + 5.0;
-    if (it.ks >= 0) c += (it.ks == s.splits - 1) ? 3.0 * (s.splits - 1) : 1.0;
-    load[i % P] += c;
-  }
-  double m = 0;
-  for (double v : load) m = v > m ? v : m;
-  return m;
-}
 
 static int check(int M, int N, int K, int batch, int symmetric, int sm_pairs, bool allow) {
   int n_static, splits;
@@ -42,14 +27,14 @@ static int check(int M, int N, int K, int batch, int symmetric, int sm_pairs, bo
     if (symmetric && it.n < it.m) { std::printf("tile below the diagonal scheduled\n"); return 1; }
     if (it.nt % 32 != 0 || it.nt < 32 || it.nt > 256) { std::printf("bad width %d\n", it.nt); return 1; }
     for (int k = it.kb0; k < it.kb1; ++k) cover[it.t][k]++;
+    if (it.ks > 0) {  // the running sum this item reads was written by the item of the range before it
+      const int writer = s.n_static + (it.ks - 1) * s.rem_tiles + (it.t - s.n_static);
+      if (writer >= i) { std::printf("running sum written by a later item\n"); return 1; }
+      const PairItem w = pair_item(s, writer);
+      if (w.t != it.t || w.ks != it.ks - 1 || pair_item_owns(s, w) || w.kb1 != it.kb0) { std::printf("running-sum chain broken\n"); return 1; }
+    }
     if (pair_item_owns(s, it)) {
       owners[it.t]++;
-      for (int ks = 0; ks < (it.ks > 0 ? it.ks : 0); ++ks) {
-        const int writer = s.n_static + ks * s.rem_tiles + (it.t - s.n_static);  // item that writes this part
-        if (writer >= i) { std::printf("part written by a later item\n"); return 1; }
-        const PairItem w = pair_item(s, writer);
-        if (w.t != it.t || w.ks != ks || pair_item_owns(s, w)) { std::printf("part/owner mismatch\n"); return 1; }
-      }
     } else {
       const int slot = pair_slot(s, it.ks, it.t);
       if (slot < 0 || slot >= kPairMaxSlots || !slots.insert(slot).second) { std::printf("slot %d reused or out of range\n", slot); return 1; }
@@ -60,12 +45,20 @@ static int check(int M, int N, int K, int batch, int symmetric, int sm_pairs, bo
     for (int k = 0; k < s.kb_total; ++k)
       if (cover[t][k] != 1) { std::printf("M %d N %d K %d b %d sym %d: tile %d k-block %d covered %d times\n", M, N, K, batch, symmetric, t, k, cover[t][k]); return 1; }
   }
-  if (symmetric) {
-    const int nf = N / 256, tail = N % 256 ? 1 : 0, mt = (M + 255) / 256;
-    if (s.total != batch * (nf * (nf + 1) / 2 + tail * mt)) { std::printf("symmetric tile count\n"); return 1; }
+  if (symmetric) {  // exactly the tiles with n >= m
+    const int nc = (N + 255) / 256, mt = (M + 255) / 256;
+    int want = 0;
+    for (int m = 0; m < mt; ++m) want += nc - m;
+    if (s.total != batch * want) { std::printf("symmetric tile count %d, expected %d\n", s.total, batch * want); return 1; }
   }
-  const double a = pair_makespan(s, sm_pairs), b = simulate(s, sm_pairs);
-  if (std::fabs(a - b) > 1e-6 * (1.0 + b)) { std::printf("M %d N %d K %d b %d: makespan model %.3f, simulation %.3f\n", M, N, K, batch, a, b); return 1; }
+  // every tile position appears once
+  std::set<long long> seen;
+  for (int t = 0; t < s.total; ++t) {
+    PairItem c;
+    pair_tile_coords(s, t, c);
+    if (!seen.insert(((long long)c.b << 40) | ((long long)c.m << 20) | c.n).second) { std::printf("tile listed twice\n"); return 1; }
+    if ((c.n < s.n_full) != (c.nt == 256) && s.tail_nt != 256) { std::printf("width of tile\n"); return 1; }
+  }
   return 0;
 }
 

@@ -75,3 +75,42 @@ def test_ema_recurrence():
         m.weight.add_(1.0)
     assert not ema.maybe_update() and ema.maybe_update()
     assert torch.allclose(ema.state_dict()["weight"], 0.8 * w0 + 0.2 * (w0 + 1.0))
+
+
+def test_failed_kernel_wait_stops_training_before_the_next_checkpoint(tmp_path):
+    """A status word that reports an expired wait (here through an injected probe - on a GPU the probes read the kernels'
+    device words) makes train() raise at the next logging step, and no checkpoint is written after that."""
+    import pytest
+
+    from sample_efficient_gpt_b200.parallel.symm import CommTimeout
+
+    cfg = _cfg(tmp_path, **{"trainer.max_steps": 6, "trainer.save_every": 3, "trainer.log_every": 1})
+    tr = Trainer(cfg)
+    state = {"calls": 0}
+
+    def probe():
+        state["calls"] += 1
+        return 4 if tr.iteration >= 4 else 0
+
+    tr.status_probes.append(("a test probe", probe))
+    with pytest.raises(CommTimeout):
+        tr.train()
+    assert tr.iteration == 4 and state["calls"] >= 4
+    names = sorted(p.name for p in (tmp_path / "ck").iterdir() if p.name.endswith(".pt") and "ema" not in p.name)
+    assert names == ["0.pt", "3.pt"], names  # nothing from iteration 4 on
+    with pytest.raises(CommTimeout):
+        tr.save_state()  # a save attempt after the failure is refused as well
+
+
+def test_prefetch_thread_failure_reaches_the_consumer(tmp_path):
+    import pytest
+
+    from sample_efficient_gpt_b200.training.data import MemoryMappedDataset
+
+    cfg = _cfg(tmp_path)
+    ds = MemoryMappedDataset(cfg.data.train_path, 32, torch.device("cpu"), 0)
+    ds._get_batch_internal = lambda bs: (_ for _ in ()).throw(OSError("disk went away"))
+    with pytest.raises(RuntimeError, match="prefetch thread failed"):
+        ds.get_batch(4)
+    with pytest.raises(RuntimeError, match="prefetch thread failed"):
+        ds.get_batch(4)

@@ -26,6 +26,10 @@ def test_two_rank_expert_parallel_engine():
     run_workers("moe_ep_cpu", 2, 29633)
 
 
+def test_two_rank_expert_parallel_checkpoint_and_clipping():
+    run_workers("moe_ckpt_cpu", 2, 29635)
+
+
 def test_bucket_assignment_rule():
     import torch
 
