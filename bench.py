@@ -314,7 +314,7 @@ def make_tokenizer(path: Path):
 def run_reference(args):
     ref_root = ROOT / "baseline" / "_ref"
     if not (ref_root / "sample_efficient_gpt").exists():
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip install of /root/reference)"}))
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip install of the reference package into baseline/_ref)"}))
         return
     sys.path.insert(0, str(ref_root))
     os.environ.setdefault("WANDB_MODE", "disabled")

@@ -1,8 +1,8 @@
 """Loss-curve parity: the same IMU-1 430M training run on this package and on the unmodified reference.
 
-    python loss_parity.py --impl ours --steps 600 --out gpurun_out/parity_ours.json
-    python loss_parity.py --impl reference --steps 600 --out gpurun_out/parity_ref.json
-    python loss_parity.py --compare gpurun_out/parity_ours.json gpurun_out/parity_ref.json
+    python loss_parity.py --impl ours --steps 600 --out parity_ours.json
+    python loss_parity.py --impl reference --steps 600 --out parity_ref.json
+    python loss_parity.py --compare parity_ours.json parity_ref.json
 
 Both arms: stage ``stable`` of ``configs/imu1_base.yaml`` (their own copy), random init from the same seed, the same
 synthetic Zipf(s=1.1) token shards read by their own loaders from the same data seed, 16 sequences of 2048 tokens per

@@ -13,8 +13,8 @@
 //   C  unpack  : G[s, b] = fp32(W_me[s, b]) for the slices owned by other ranks          (all-gather landing + cast)
 // Block b only ever touches sub-slice b, on every rank, so per-block barriers suffice and no grid-wide sync is needed.
 // Flags are monotonically increasing sequence numbers (never reset), one word per (block, source rank).
-// Every wait is bounded: after kCommWaitCycles without the peer's flag the block records the failure in a status
-// word and stops touching remote memory; the host raises an error after the step.
+// Every wait is bounded: after the wait limit (a kernel argument, kCommWaitCycles by default) without the peer's flag the
+// block records the failure in a status word and stops touching remote memory; the host raises an error after the step.
 //
 // The reference reduces each bucket with an NCCL all-reduce of a bf16 copy and casts back on the host side
 // (training/distributed/ddp_bucket.py:91-104,118-134).
@@ -40,7 +40,7 @@ struct CommPeers {
 };
 
 // All threads of the block call this.  Returns false when a peer did not show up in time.
-__device__ __forceinline__ bool block_barrier(const CommPeers& pe, int rank, int world, uint32_t seq, int* status) {
+__device__ __forceinline__ bool block_barrier(const CommPeers& pe, int rank, int world, uint32_t seq, int* status, long long limit) {
   __threadfence_system();
   __syncthreads();
   __shared__ int ok_s;
@@ -52,7 +52,7 @@ __device__ __forceinline__ bool block_barrier(const CommPeers& pe, int rank, int
     const uint32_t* mine = pe.flags[rank] + (size_t)blockIdx.x * kMaxRanks + peer;
     const long long t0 = clock64();
     while ((int32_t)(ld_acquire_sys(mine) - seq) < 0) {
-      if (clock64() - t0 > kCommWaitCycles) {
+      if (clock64() - t0 > limit) {
         atomicCAS(status, 0, 1000 + peer);
         ok_s = 0;
         break;
@@ -81,7 +81,7 @@ __device__ __forceinline__ void multimem_st_bf16x8(void* mc_ptr, const uint32_t*
 // sum of one scalar per rank instead of a pass over every gradient tensor).
 __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict__ grads, CommPeers pe, void* mc_base,
                                                              int64_t wire_off, int64_t n, int rank, int world, uint32_t seq,
-                                                             int* status, float* __restrict__ sq_out) {
+                                                             int* status, float* __restrict__ sq_out, long long limit) {
   const int64_t slice = n / world;
   const int nb = gridDim.x;
   // sub-slice b of a slice, in units of 8 elements
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
         if (v + (int64_t)u * blockDim.x < v1) store8<__nv_bfloat16>(w_me + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
     }
   }
-  if (!block_barrier(pe, rank, world, seq, status)) return;
+  if (!block_barrier(pe, rank, world, seq, status, limit)) return;
 
   // B: reduce my slice, push the result to everyone
   float sq = 0.f;
@@ -130,35 +130,49 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
           }
       }
     } else {
-      for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-        bf16x8 in[kMaxRanks];
-        float own[8];
+      // kPeerUnroll vectors per thread and trip: (world - 1) * kPeerUnroll independent 16-byte peer loads are in flight before
+      // the first is used, which is what hides the NVLink round trip at small world sizes
+      constexpr int kPeerUnroll = 2;
+      for (int64_t v = v0 + threadIdx.x; v < v1; v += (int64_t)blockDim.x * kPeerUnroll) {
+        bf16x8 in[kPeerUnroll][kMaxRanks];
+        float own[kPeerUnroll][8];
 #pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
-          if (p < world && p != rank)
-            in[p] = *reinterpret_cast<const bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(pe.buf[p]) + wire_off + base + v * 8);
-        load8<float>(grads + base + v * 8, own);
-        float acc[8];
+        for (int u = 0; u < kPeerUnroll; ++u) {
+          const int64_t vv = v + (int64_t)u * blockDim.x;
+          if (vv < v1) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)  // fixed order of summation on every rank; each term is bf16-rounded
-          if (p < world) {
-            float f[8];
-            unpack8(p == rank ? pack8(own) : in[p], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            for (int p = 0; p < kMaxRanks; ++p)
+              if (p < world && p != rank)
+                in[u][p] = *reinterpret_cast<const bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(pe.buf[p]) + wire_off + base + vv * 8);
+            load8<float>(grads + base + vv * 8, own[u]);
           }
-        const bf16x8 out = pack8(acc);
-        float fin[8];
-        unpack8(out, fin);  // every rank ends with the same bf16-rounded value
-        store8<float>(grads + base + v * 8, fin);
+        }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sq = fmaf(fin[j], fin[j], sq);
+        for (int u = 0; u < kPeerUnroll; ++u) {
+          const int64_t vv = v + (int64_t)u * blockDim.x;
+          if (vv >= v1) continue;
+          float acc[8];
 #pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p)
-          if (p < world && p != rank)
-            *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(pe.buf[p]) + wire_off + base + v * 8) = out;
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p)  // fixed order of summation on every rank; each term is bf16-rounded
+            if (p < world) {
+              float f[8];
+              unpack8(p == rank ? pack8(own[u]) : in[u][p], f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            }
+          const bf16x8 out = pack8(acc);
+          float fin[8];
+          unpack8(out, fin);  // every rank ends with the same bf16-rounded value
+          store8<float>(grads + base + vv * 8, fin);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sq = fmaf(fin[j], fin[j], sq);
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p)
+            if (p < world && p != rank)
+              *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(pe.buf[p]) + wire_off + base + vv * 8) = out;
+        }
       }
     }
   }
@@ -167,7 +181,7 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
     const float total = block_sum(sq, red_s);
     if (threadIdx.x == 0) atomicAdd(sq_out, total);
   }
-  if (!block_barrier(pe, rank, world, seq + 1, status)) return;
+  if (!block_barrier(pe, rank, world, seq + 1, status, limit)) return;
 
   // C: unpack the other owners' slices
   for (int s = 0; s < world; ++s) {
@@ -188,8 +202,8 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
 // All-gather in place: `buf` (symmetric, 16-byte elements view) holds world chunks of chunk_bytes; rank r's chunk r is
 // valid on entry, all chunks are valid on exit.  Pull model: every rank copies the peers' chunks from their memory.
 __global__ void __launch_bounds__(512) allgather_kernel(CommPeers pe, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,
-                                                      uint32_t seq, int* status) {
-  if (!block_barrier(pe, rank, world, seq, status)) return;
+                                                      uint32_t seq, int* status, long long limit) {
+  if (!block_barrier(pe, rank, world, seq, status, limit)) return;
   const int nb = gridDim.x;
   const int64_t vecs = chunk_bytes / 16;
   const int64_t v0 = vecs * blockIdx.x / nb, v1 = vecs * (blockIdx.x + 1) / nb;
@@ -201,7 +215,7 @@ __global__ void __launch_bounds__(512) allgather_kernel(CommPeers pe, int64_t of
     for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) dst[v] = theirs[v];
   }
   // nobody may overwrite its chunk (next step) before every peer has read it
-  block_barrier(pe, rank, world, seq + 1, status);
+  block_barrier(pe, rank, world, seq + 1, status, limit);
 }
 
 static CommPeers make_peers(void* const* bufs, uint32_t* const* flags, int world) {
@@ -214,14 +228,16 @@ static CommPeers make_peers(void* const* bufs, uint32_t* const* flags, int world
 }
 
 void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
-                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st, float* sq_out) {
+                           int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st, float* sq_out,
+                           long long wait_cycles) {
   allreduce_bucket_kernel<<<blocks, 512, 0, st>>>(grads, make_peers(wire_bufs, flags, world), mc_base, wire_off, n, rank, world, seq,
-                                                  status, sq_out);
+                                                  status, sq_out, wait_cycles > 0 ? wait_cycles : kCommWaitCycles);
 }
 
 void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,
-                    uint32_t seq, int blocks, int* status, cudaStream_t st) {
-  allgather_kernel<<<blocks, 512, 0, st>>>(make_peers(bufs, flags, world), off_bytes, chunk_bytes, rank, world, seq, status);
+                    uint32_t seq, int blocks, int* status, cudaStream_t st, long long wait_cycles) {
+  allgather_kernel<<<blocks, 512, 0, st>>>(make_peers(bufs, flags, world), off_bytes, chunk_bytes, rank, world, seq, status,
+                                           wait_cycles > 0 ? wait_cycles : kCommWaitCycles);
 }
 
 }  // namespace seg

@@ -79,10 +79,12 @@ constexpr int kCommMaxBlocks = 128;  // flag words per rank = kCommMaxBlocks * k
 // sq_out (optional, fp32 scalar): += sum of squares of the reduced slice this rank owns.
 void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
                            int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st,
-                           float* sq_out = nullptr);
+                           float* sq_out = nullptr, long long wait_cycles = 0);
+// wait_cycles (both collectives): how long a block waits for a peer's flag before it gives up and sets *status to
+// 1000 + peer (0: about ten seconds).
 // bufs[p] + off_bytes holds `world` chunks of chunk_bytes (multiple of 16); chunk `rank` is valid on entry, all on exit.
 void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,
-                    uint32_t seq, int blocks, int* status, cudaStream_t st);
+                    uint32_t seq, int blocks, int* status, cudaStream_t st, long long wait_cycles = 0);
 
 // ---- moe.cu (router, slot assignment, expert-parallel push / pull over peer memory)
 constexpr int kMoeMaxExperts = 32;

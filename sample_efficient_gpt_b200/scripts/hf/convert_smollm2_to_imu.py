@@ -39,16 +39,18 @@ def repeat_map(src_units: int, dst_units: int) -> tuple[torch.Tensor, torch.Tens
     return torch.arange(src_units).repeat_interleave(counts), counts
 
 
-def zero_sum_noise(block: torch.Tensor, counts: torch.Tensor, std: float, gen: torch.Generator) -> torch.Tensor:
-    """Noise on the columns of repeated units that sums to zero over each unit's copies (keeps the function)."""
+def zero_sum_noise(block: torch.Tensor, counts: torch.Tensor, std: float, gen: torch.Generator, width: int = 1) -> torch.Tensor:
+    """Noise on the columns of repeated units that sums to zero over each unit's copies (keeps the function).  A unit is
+    ``width`` adjacent columns (1 for FFN channels, head_dim for attention heads); its copies follow one another."""
     if std <= 0:
         return block
     pos = 0
     for c in counts.tolist():
         if c > 1:
-            n = torch.randn(block.size(0), c, generator=gen) * std * block[:, pos : pos + c].std() / c
-            block[:, pos : pos + c] += n - n.mean(dim=1, keepdim=True)
-        pos += c
+            span = block[:, pos : pos + c * width]
+            n = torch.randn(block.size(0), c, width, generator=gen) * std * span.std() / c
+            span += (n - n.mean(dim=1, keepdim=True)).reshape(block.size(0), c * width)
+        pos += c * width
     return block
 
 
@@ -68,7 +70,7 @@ def net2wider_heads(q, k, v, o, src_heads, src_kv, dst_heads, dst_kv, hd, noise_
     cols = rows(oldq)
     denom = cq[oldq].repeat_interleave(hd).to(o.dtype)
     on = o[:, cols] / denom[None, :]
-    on = zero_sum_noise(on, cq.repeat_interleave(1) * 1, 0.0, gen) if noise_std <= 0 else on
+    on = zero_sum_noise(on, cq, noise_std, gen, width=hd)  # copies of a head see the same attention output: their noise cancels
     return qn, kn, vn, on
 
 

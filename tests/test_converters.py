@@ -118,6 +118,31 @@ def test_smollm2_init_packing_and_function_preserving_ffn_widening(tmp_path):
     assert wider["embedding.weight"].shape == (100, 64) and float(wider["embedding.weight"][:, 32:].abs().sum()) == 0
 
 
+def test_head_widening_noise_breaks_symmetry_and_keeps_the_function():
+    from sample_efficient_gpt_b200.scripts.hf.convert_smollm2_to_imu import net2wider_heads
+
+    torch.manual_seed(0)
+    d, H, KV, hd = 32, 4, 2, 8
+    q, k, v, o = torch.randn(H * hd, d), torch.randn(KV * hd, d), torch.randn(KV * hd, d), torch.randn(d, H * hd)
+    x = torch.randn(6, d)
+
+    def attn_out(q, k, v, o, heads, kv):
+        qh = (x @ q.t()).view(6, heads, hd)
+        kh = (x @ k.t()).view(6, kv, hd).repeat_interleave(heads // kv, dim=1)
+        vh = (x @ v.t()).view(6, kv, hd).repeat_interleave(heads // kv, dim=1)
+        att = torch.einsum("thd,shd->hts", qh, kh).div(hd**0.5).softmax(-1)
+        return torch.einsum("hts,shd->thd", att, vh).reshape(6, heads * hd) @ o.t()
+
+    want = attn_out(q, k, v, o, H, KV)
+    gen = torch.Generator().manual_seed(1)
+    q0, k0, v0, o0 = net2wider_heads(q, k, v, o.clone(), H, KV, 8, 4, hd, 0.0, gen)
+    q1, k1, v1, o1 = net2wider_heads(q, k, v, o.clone(), H, KV, 8, 4, hd, 0.5, gen)
+    assert torch.allclose(attn_out(q0, k0, v0, o0, 8, 4), want, atol=1e-5)
+    assert torch.allclose(attn_out(q1, k1, v1, o1, 8, 4), want, atol=1e-4), "zero-sum noise must keep the function"
+    assert torch.equal(o0[:, :hd], o0[:, hd : 2 * hd]), "without noise the copies of a head are exact duplicates"
+    assert not torch.allclose(o1[:, :hd], o1[:, hd : 2 * hd]), "--noise-std must perturb the copies"
+
+
 def test_posthoc_ema(tmp_path):
     from sample_efficient_gpt_b200.scripts.ema_posthoc import ema_of, list_checkpoints
 
