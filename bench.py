@@ -55,6 +55,7 @@ def parse():
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     p.add_argument("--config-key", type=str, default="bench")
     p.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
+    p.add_argument("--no-check", action="store_true", help="multi-GPU runs: skip the comparison of the NVLink kernels with torch.distributed collectives before timing")
     p.add_argument("--model", type=str, default="imu1", choices=sorted(MODELS), help="imu1 is the headline configuration")
     return p.parse_args()
 
@@ -268,6 +269,12 @@ def run_ours(args):
 
     for i in range(args.warmup):
         dev_step(i)
+    comm_check = None
+    if trainer.ddp is not None and trainer.ddp.comm is not None and not args.no_check:
+        from sample_efficient_gpt_b200.parallel.comm_check import run_all
+
+        torch.cuda.synchronize()
+        comm_check = run_all(trainer.ddp.comm, with_experts=args.model == "moe")  # raises on every rank when a comparison fails
     sampler = ClockSampler(local)
     sampler.start()
     l0 = ops.launch_count
@@ -294,7 +301,8 @@ def run_ours(args):
         trainer.ddp.comm.check()  # raises if a bounded wait on a peer gave up during the run
     emit(args, world, rank, ms_dev, ms_e2e, launches, clocks, "ours",
          {"comm": comm, "sharded_muon": bool(cfg.optim.shard_muon), "ema_every": cfg.trainer.ema_every,
-          "block_gemm": os.environ.get("SEGPT_BLOCK_GEMM", "native"), "attention": os.environ.get("SEGPT_ATTN_IMPL", "native"), **extra}, h2d, d2h)
+          "block_gemm": os.environ.get("SEGPT_BLOCK_GEMM", "native"), "attention": os.environ.get("SEGPT_ATTN_IMPL", "native"),
+          **({"comm_check": comm_check} if comm_check else {}), **extra}, h2d, d2h)
     if world > 1:
         dist.destroy_process_group()
 

@@ -3,6 +3,12 @@
     python loss_parity.py --impl ours --steps 600 --out parity_ours.json
     python loss_parity.py --impl reference --steps 600 --out parity_ref.json
     python loss_parity.py --compare parity_ours.json parity_ref.json
+    torchrun --nproc-per-node 2 ... loss_parity.py --impl ours --gpus 2 --steps 600 --out parity_ours_2gpu.json
+
+With ``--gpus N`` (N = 2 here: one micro-batch of 8 per GPU) the run goes through everything a multi-GPU job uses - bucketed
+gradient reduction over the NVLink kernels, sharded NorMuon with the all-gather in the GEMM epilogue - on the *same* 16
+sequences per optimizer step as the single-GPU run: every rank draws the single-GPU run's two micro-batches and keeps its
+own, and the schedule position advances by two per step as it does there.  Rank r's loss is micro-step r of the step.
 
 Both arms: stage ``stable`` of ``configs/imu1_base.yaml`` (their own copy), random init from the same seed, the same
 synthetic Zipf(s=1.1) token shards read by their own loaders from the same data seed, 16 sequences of 2048 tokens per
@@ -25,6 +31,45 @@ import bench
 
 OVERRIDES = {"optim.zero_lr_steps": 0, "optim.warmup_steps": 100, "trainer.gradient_accumulation_steps": 2, "trainer.log_every": 10**9,
              "trainer.load_from": None, "data.batch_size": 8, "data.context_length": bench.SEQ}
+
+
+def run_distributed(steps: int, n_gpus: int) -> list[float] | None:
+    import torch.distributed as dist
+
+    from sample_efficient_gpt_b200.training.data import MemoryMappedDataset
+    from sample_efficient_gpt_b200.training.trainer import Trainer
+    from sample_efficient_gpt_b200.utils.config_tools import apply_overrides, load_cfg
+
+    world, rank, local = bench.dist_setup(n_gpus)
+    assert world == 2, "two micro-batches of 8 per optimizer step: one per GPU"
+    tmp = [tempfile.mkdtemp(prefix="segpt_parity_dist_") if rank == 0 else None]
+    dist.broadcast_object_list(tmp, src=0)
+    tmp = Path(tmp[0])
+    if rank == 0:
+        bench.make_dataset(tmp)
+    dist.barrier()
+    paths = {"data.train_path": str(tmp / "train"), "data.validation_path": str(tmp / "val.npy"), "trainer.save_dir": str(tmp / "ckpt")}
+    cfg = load_cfg(str(bench.ROOT / "sample_efficient_gpt_b200/configs/imu1_base.yaml"), "stable")
+    cfg = apply_overrides(cfg, {**OVERRIDES, **paths, "data.tokenizer_path": "", "trainer.device": f"cuda:{local}", "trainer.dtype": "bfloat16",
+                                "trainer.ema_every": 0, "trainer.gradient_accumulation_steps": 1, "data.batch_size": 8 * world,
+                                "optim.shard_muon": True, "trainer.comm_backend": os.environ.get("SEGPT_COMM_BACKEND", "auto")})
+    cfg.optim.lr, cfg.optim.muon_lr = float(cfg.optim.lr), float(cfg.optim.muon_lr)
+    trainer = Trainer(cfg)
+    assert trainer.ddp is not None
+    source = MemoryMappedDataset(cfg.data.train_path, cfg.data.context_length, trainer.device, cfg.data.seed)  # the single-GPU stream
+    losses = []
+    for step in range(steps):
+        micro = [source._get_batch_internal(8) for _ in range(world)]
+        x, y = micro[rank]
+        trainer.iteration = 2 * step + 1  # where the single-GPU run stands when it takes this optimizer step
+        log = trainer.train_step(x.to(trainer.device), y.to(trainer.device))
+        both = [torch.zeros((), device=trainer.device) for _ in range(world)]
+        dist.all_gather(both, log["train_loss"].detach().float().reshape(()))
+        losses.extend(both)
+    trainer.check_kernel_status()
+    out = [float(v) for v in torch.stack(losses).cpu()]
+    dist.destroy_process_group()
+    return out if rank == 0 else None
 
 
 def run(impl: str, steps: int) -> list[float]:
@@ -90,11 +135,18 @@ def main():
     p.add_argument("--steps", type=int, default=600, help="optimizer steps (two micro-steps each)")
     p.add_argument("--out", default=None)
     p.add_argument("--compare", nargs=2, default=None)
+    p.add_argument("--gpus", type=int, default=1, help="2: the multi-GPU path on the single-GPU run's data (launch under torchrun)")
     a = p.parse_args()
     if a.compare:
         compare(*a.compare)
         return
-    losses = run(a.impl, a.steps)
+    if a.gpus > 1:
+        assert a.impl == "ours"
+        losses = run_distributed(a.steps, a.gpus)
+        if losses is None:
+            return
+    else:
+        losses = run(a.impl, a.steps)
     if a.out:
         Path(a.out).parent.mkdir(parents=True, exist_ok=True)
         json.dump({"impl": a.impl, "steps": a.steps, "losses": losses}, open(a.out, "w"))

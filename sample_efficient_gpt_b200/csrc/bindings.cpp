@@ -112,32 +112,45 @@ Tensor swiglu_bwd(const Tensor& df, const Tensor& u) {
 
 void check_hd(int hd) { TORCH_CHECK(hd == 32 || hd == 64 || hd == 128, "head_dim must be 32, 64 or 128"); }
 
+// z: [T, H] gate logits, possibly a column slice of a wider tensor (row stride >= H, unit column stride)
+void check_gate_logits(const Tensor& z, bool bf16, int64_t T, int H, const char* name) {
+  TORCH_CHECK(z.is_cuda() && z.scalar_type() == (bf16 ? at::kBFloat16 : at::kFloat), name, " has the wrong device or dtype");
+  TORCH_CHECK(z.dim() == 2 && z.size(0) == T && z.size(1) == H && z.stride(1) == 1 && z.stride(0) >= H, name, " must be [T, H] with unit column stride");
+}
+
 Tensor gate_fwd(const Tensor& o, const Tensor& z) {
   const bool bf16 = o.scalar_type() == at::kBFloat16;
   check_lp(o, bf16, "o");
-  check_lp(z, bf16, "z");
   TORCH_CHECK(o.dim() == 3, "o must be [T, H, hd]");
   const int64_t T = o.size(0);
   const int H = o.size(1), hd = o.size(2);
   check_hd(hd);
+  check_gate_logits(z, bf16, T, H, "z");
   c10::cuda::CUDAGuard guard(o.device());
   Tensor g = torch::empty({T, (int64_t)H * hd}, o.options());
-  seg::gate_fwd(o.data_ptr(), z.data_ptr(), g.data_ptr(), T, H, hd, bf16, cur_stream());
+  seg::gate_fwd(o.data_ptr(), z.data_ptr(), g.data_ptr(), T, H, hd, bf16, cur_stream(), z.stride(0));
   return g;
 }
 
-std::tuple<Tensor, Tensor> gate_bwd(const Tensor& dg, const Tensor& o, const Tensor& z) {
+// dz_out (optional): [T, H] destination of the gate-logit gradient, e.g. columns of the fused projection's gradient buffer
+std::tuple<Tensor, Tensor> gate_bwd(const Tensor& dg, const Tensor& o, const Tensor& z, const OptTensor& dz_out) {
   const bool bf16 = o.scalar_type() == at::kBFloat16;
   check_lp(o, bf16, "o");
-  check_lp(z, bf16, "z");
   check_lp(dg, bf16, "dg");
   const int64_t T = o.size(0);
   const int H = o.size(1), hd = o.size(2);
   check_hd(hd);
+  check_gate_logits(z, bf16, T, H, "z");
   c10::cuda::CUDAGuard guard(o.device());
   Tensor dout = torch::empty_like(o);
-  Tensor dz = torch::empty_like(z);
-  seg::gate_bwd(dg.data_ptr(), o.data_ptr(), z.data_ptr(), dout.data_ptr(), dz.data_ptr(), T, H, hd, bf16, cur_stream());
+  Tensor dz;
+  if (dz_out.has_value()) {
+    dz = *dz_out;
+    check_gate_logits(dz, bf16, T, H, "dz_out");
+  } else {
+    dz = torch::empty({T, (int64_t)H}, o.options());
+  }
+  seg::gate_bwd(dg.data_ptr(), o.data_ptr(), z.data_ptr(), dout.data_ptr(), dz.data_ptr(), T, H, hd, bf16, cur_stream(), z.stride(0), dz.stride(0));
   return {dout, dz};
 }
 
@@ -185,7 +198,7 @@ std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTens
 std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
     const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& qkv, const OptTensor& v1, const Tensor& cos,
     const Tensor& sin, const Tensor& qgain, const Tensor& a1, const Tensor& a2, const Tensor& vs, int B, int S, int H, int Hkv,
-    int hd, bool qknorm, const OptTensor& dqkv_out) {
+    int hd, bool qknorm, const OptTensor& dqkv_out, const OptTensor& dv1_acc) {
   const bool bf16 = qkv.scalar_type() == at::kBFloat16;
   check_rows(qkv, bf16, "qkv");
   check_lp(dq, bf16, "dq");
@@ -210,7 +223,16 @@ std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
   }
   p.qkv_stride = qkv.stride(0);
   OptTensor dv1;
-  if (v1.has_value()) dv1 = torch::empty({B, S, Hkv, hd}, f32);
+  if (v1.has_value()) {
+    if (dv1_acc.has_value()) {  // running sum over blocks, updated in place
+      check_f32(*dv1_acc, "dv1_acc");
+      TORCH_CHECK(dv1_acc->numel() == T * Hkv * hd, "dv1_acc must hold [B, S, Hkv, hd]");
+      dv1 = *dv1_acc;
+      p.dv1_accumulate = true;
+    } else {
+      dv1 = torch::empty({B, S, Hkv, hd}, f32);
+    }
+  }
   Tensor scalars = torch::empty({4}, f32);
   Tensor partial = torch::empty({seg::qkv_post_bwd_grid(T, H + 2 * Hkv, hd), 4}, f32);
   seg::qkv_post_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dv_f32, qkv.data_ptr(), opt_ptr(v1), dqkv.data_ptr(),
@@ -409,14 +431,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("gate_fwd", &gate_fwd);
-  m.def("gate_bwd", &gate_bwd);
+  m.def("gate_bwd", &gate_bwd, pybind11::arg("dg"), pybind11::arg("o"), pybind11::arg("z"), pybind11::arg("dz_out") = std::nullopt);
   m.def("qkv_post_fwd", &qkv_post_fwd, pybind11::arg("qkv"), pybind11::arg("v1"), pybind11::arg("cos"), pybind11::arg("sin"),
         pybind11::arg("qgain"), pybind11::arg("a1"), pybind11::arg("a2"), pybind11::arg("vs"), pybind11::arg("B"), pybind11::arg("S"),
         pybind11::arg("H"), pybind11::arg("Hkv"), pybind11::arg("hd"), pybind11::arg("qknorm"), pybind11::arg("pos") = std::nullopt);
   m.def("qkv_post_bwd", &qkv_post_bwd, pybind11::arg("dq"), pybind11::arg("dk"), pybind11::arg("dv"), pybind11::arg("qkv"),
         pybind11::arg("v1"), pybind11::arg("cos"), pybind11::arg("sin"), pybind11::arg("qgain"), pybind11::arg("a1"), pybind11::arg("a2"),
         pybind11::arg("vs"), pybind11::arg("B"), pybind11::arg("S"), pybind11::arg("H"), pybind11::arg("Hkv"), pybind11::arg("hd"),
-        pybind11::arg("qknorm"), pybind11::arg("dqkv_out") = std::nullopt);
+        pybind11::arg("qknorm"), pybind11::arg("dqkv_out") = std::nullopt, pybind11::arg("dv1_acc") = std::nullopt);
   m.def("ce_chunk_fwd_bwd", &ce_chunk_fwd_bwd);
   m.def("adamw", &adamw);
   m.def("ema", &ema);

@@ -96,24 +96,31 @@ void swiglu_bwd(const void* df, const void* u, void* du, int64_t T, int F, bool 
 #undef SEG_SWB
 }
 
-// One group of hd/4 threads per (token, head); hd/4 is 16 (hd 64) or 32 (hd 128), so a warp holds 2 or 1 heads.
+// One group of hd/8 threads per (token, head): 16-byte accesses, hd/8 is 8 (hd 64) or 16 (hd 128), so a warp holds 4 or 2
+// heads.  The gate logits z (and their gradient) are addressed as [token * stride + head], so they can be columns of a
+// wider projection output and no compact copy is needed.
 template <typename T, int HD>
 __global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ o, const T* __restrict__ z, T* __restrict__ g,
-                                                     int64_t n_heads_total) {
-  constexpr int TPH = HD / 4;
+                                                     int64_t n_heads_total, int H, int64_t z_stride) {
+  constexpr int TPH = HD / 8;
   const int64_t total = n_heads_total * TPH;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t head = i / TPH;
-    const float s = 2.f * sigmoidf_(to_f<T>(z[head]));
-    const float4 v = load4<T>(o + i * 4);
-    store4<T>(g + i * 4, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
+    const int64_t tok = head / H;
+    const float s = 2.f * sigmoidf_(to_f<T>(z[tok * z_stride + (head - tok * H)]));
+    float v[8];
+    load8<T>(o + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= s;
+    store8<T>(g + i * 8, v);
   }
 }
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dg, const T* __restrict__ o, const T* __restrict__ z,
-                                                     T* __restrict__ dout, T* __restrict__ dz, int64_t n_heads_total) {
-  constexpr int TPH = HD / 4;
+                                                     T* __restrict__ dout, T* __restrict__ dz, int64_t n_heads_total, int H,
+                                                     int64_t z_stride, int64_t dz_stride) {
+  constexpr int TPH = HD / 8;
   const int64_t total = n_heads_total * TPH;  // multiple of TPH; blockDim is a multiple of 32 >= TPH
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t rounds = (total + stride - 1) / stride;
@@ -121,33 +128,46 @@ __global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dg,
   for (int64_t it = 0; it < rounds; ++it, i += stride) {
     const bool live = i < total;
     const int64_t head = live ? i / TPH : 0;
+    const int64_t tok = head / H;
+    const int h = (int)(head - tok * H);
     float sg = 0.f, dot = 0.f;
     if (live) {
-      sg = sigmoidf_(to_f<T>(z[head]));
-      const float4 a = load4<T>(dg + i * 4), b = load4<T>(o + i * 4);
+      sg = sigmoidf_(to_f<T>(z[tok * z_stride + h]));
+      float a[8], b[8];
+      load8<T>(dg + i * 8, a);
+      load8<T>(o + i * 8, b);
       const float s2 = 2.f * sg;
-      store4<T>(dout + i * 4, make_float4(a.x * s2, a.y * s2, a.z * s2, a.w * s2));
-      dot = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dot += a[j] * b[j];
+        a[j] *= s2;
+      }
+      store8<T>(dout + i * 8, a);
     }
 #pragma unroll
     for (int off = TPH / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    if (live && (i % TPH) == 0) dz[head] = from_f<T>(2.f * sg * (1.f - sg) * dot);
+    if (live && (i % TPH) == 0) dz[tok * dz_stride + h] = from_f<T>(2.f * sg * (1.f - sg) * dot);
   }
 }
 
-void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, bool bf16, cudaStream_t st) {
+void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, bool bf16, cudaStream_t st, int64_t z_stride) {
   const int64_t nh = T * H;
-  const int grid = stream_grid(nh * (hd / 4), 256);
-#define SEG_GATE(TY, HD) gate_fwd_kernel<TY, HD><<<grid, 256, 0, st>>>((const TY*)o, (const TY*)z, (TY*)g, nh)
+  const int grid = stream_grid(nh * (hd / 8), 256);
+  if (z_stride <= 0) z_stride = H;
+#define SEG_GATE(TY, HD) gate_fwd_kernel<TY, HD><<<grid, 256, 0, st>>>((const TY*)o, (const TY*)z, (TY*)g, nh, H, z_stride)
   if (bf16) { if (hd == 64) SEG_GATE(__nv_bfloat16, 64); else if (hd == 128) SEG_GATE(__nv_bfloat16, 128); else SEG_GATE(__nv_bfloat16, 32); }
   else { if (hd == 64) SEG_GATE(float, 64); else if (hd == 128) SEG_GATE(float, 128); else SEG_GATE(float, 32); }
 #undef SEG_GATE
 }
 
-void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st) {
+void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st,
+              int64_t z_stride, int64_t dz_stride) {
   const int64_t nh = T * H;
-  const int grid = stream_grid(nh * (hd / 4), 256);
-#define SEG_GATE(TY, HD) gate_bwd_kernel<TY, HD><<<grid, 256, 0, st>>>((const TY*)dg, (const TY*)o, (const TY*)z, (TY*)dout, (TY*)dz, nh)
+  const int grid = stream_grid(nh * (hd / 8), 256);
+  if (z_stride <= 0) z_stride = H;
+  if (dz_stride <= 0) dz_stride = H;
+#define SEG_GATE(TY, HD) \
+  gate_bwd_kernel<TY, HD><<<grid, 256, 0, st>>>((const TY*)dg, (const TY*)o, (const TY*)z, (TY*)dout, (TY*)dz, nh, H, z_stride, dz_stride)
   if (bf16) { if (hd == 64) SEG_GATE(__nv_bfloat16, 64); else if (hd == 128) SEG_GATE(__nv_bfloat16, 128); else SEG_GATE(__nv_bfloat16, 32); }
   else { if (hd == 64) SEG_GATE(float, 64); else if (hd == 128) SEG_GATE(float, 128); else SEG_GATE(float, 32); }
 #undef SEG_GATE

@@ -42,6 +42,8 @@ struct GemmParams {
   uint32_t* ws_flags;    // one word per (slot, rank, epilogue warp), zero between launches
 };
 
+// Gives up after half the limit of the barrier waits: the roles that wait (through the ring) for what this producer loads
+// then still have time left, and the status word names the flag, not one of its consequences.
 __device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t seq, const sm100::AbortState& ab, int code) {
   uint32_t v;
   const long long t0 = clock64();
@@ -49,7 +51,7 @@ __device__ __forceinline__ bool wait_region_flag(const uint32_t* flag, uint32_t 
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if ((int32_t)(v - seq) >= 0) return true;
     if (*ab.cta_abort != 0) return false;
-    if (clock64() - t0 > ab.limit) {
+    if (clock64() - t0 > ab.limit / 2) {
       *ab.cta_abort = 1;
       atomicCAS(ab.global_status, 0, code);
       return false;

@@ -17,8 +17,10 @@ void add_rmsnorm_bwd(const void* dy, const float* dres_in, const float* x, const
 // ---- elementwise.cu
 void swiglu_fwd(const void* u, void* f, int64_t T, int F, bool bf16, cudaStream_t st);
 void swiglu_bwd(const void* df, const void* u, void* du, int64_t T, int F, bool bf16, cudaStream_t st);
-void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, bool bf16, cudaStream_t st);
-void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st);
+// z and dz are addressed as [token * stride + head] (stride in elements; 0 = H, i.e. compact [T, H]).
+void gate_fwd(const void* o, const void* z, void* g, int64_t T, int H, int hd, bool bf16, cudaStream_t st, int64_t z_stride = 0);
+void gate_bwd(const void* dg, const void* o, const void* z, void* dout, void* dz, int64_t T, int H, int hd, bool bf16, cudaStream_t st,
+              int64_t z_stride = 0, int64_t dz_stride = 0);
 
 // ---- qkv_post.cu
 constexpr int kQkvPostMaxGrid = 148 * 8;  // CTAs of the kernels == rows of the backward's scalar scratch
@@ -34,6 +36,7 @@ struct QkvPostParams {
   const float* vscale;  // [1]
   int64_t qkv_stride;   // row stride (elements) of qkv and dqkv: (H + 2 Hkv) * hd, or more when the projection is wider
   const int* pos;       // optional device scalar added to every token's position (decode: S == 1, position = cache length)
+  bool dv1_accumulate = false;  // backward: add the value-residual gradient to dv1_out instead of overwriting it
 };
 void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st);
 // dv_is_f32: dv is fp32 (first block, after the v1 gradients were added); dv1_out fp32 [T,Hkv,hd] or nullptr;

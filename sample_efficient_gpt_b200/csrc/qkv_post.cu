@@ -231,6 +231,16 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
         store8<T>(dqkv + row_off, o1);
         store8<T>(dqkv + row_off + HALF, o2);
         if (dv1_out != nullptr) {
+          if (p.dv1_accumulate) {  // the gradient of the first block's values gathers over all later blocks
+            float b1[8], b2[8];
+            load8<float>(dv1_out + off, b1);
+            load8<float>(dv1_out + off + HALF, b2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              e1[j] += b1[j];
+              e2[j] += b2[j];
+            }
+          }
           store8<float>(dv1_out + off, e1);
           store8<float>(dv1_out + off + HALF, e2);
         }

@@ -95,16 +95,19 @@ def qkv_post_fwd(qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qkn
     return ref.qkv_post_fwd(qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm)
 
 
-def qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm, dqkv_out=None):
+def qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm, dqkv_out=None, dv1_acc=None):
     """``qkv`` may be a column slice of a wider projection output; ``dqkv_out`` (same shape and row stride as ``qkv``)
-    receives the gradient in place of a fresh buffer."""
+    receives the gradient in place of a fresh buffer.  ``dv1_acc`` (fp32 [B,S,Hkv,hd]): the running sum of the
+    value-residual gradients of the later blocks; this block's contribution is added in place and the sum is returned."""
     if _use_cuda(qkv, "qkv_post_bwd"):
         _count(2)
-        return ext().qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm, dqkv_out)
+        return ext().qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm, dqkv_out, dv1_acc)
     out = ref.qkv_post_bwd(dq, dk, dv, qkv, v1, cos, sin, qgain, a1, a2, vscale, B, S, H, Hkv, hd, qknorm)
     if dqkv_out is not None:
         dqkv_out.copy_(out[0])
         out = (dqkv_out, *out[1:])
+    if dv1_acc is not None and out[1] is not None:
+        out = (out[0], dv1_acc.add_(out[1]), *out[2:])
     return out
 
 
@@ -133,11 +136,16 @@ def gate_fwd(o, z):
     return ref.gate_fwd(o, z)
 
 
-def gate_bwd(dg, o, z):
+def gate_bwd(dg, o, z, dz_out=None):
+    """``z`` may be a column slice of a wider tensor; ``dz_out`` ([T, H], likewise) receives the gate-logit gradient."""
     if _use_cuda(o, "gate_bwd"):
         _count()
-        return ext().gate_bwd(dg, o, z)
-    return ref.gate_bwd(dg, o, z)
+        return ext().gate_bwd(dg, o, z, dz_out)
+    do, dz = ref.gate_bwd(dg, o, z)
+    if dz_out is not None:
+        dz_out.copy_(dz)
+        dz = dz_out
+    return do, dz
 
 
 def swiglu_fwd(u):

@@ -5,8 +5,9 @@ the diagonal and mirrors them; ``B = b A + c A A`` is computed in full, because 
 plain epilogue is faster than the mirrored one on this short contraction; the update ``a X + B X`` (wide X) or
 ``a X + X B`` (tall X) reads its operands in place (K-major and MN-major tiles), so tall matrices are never
 transposed: for ``R > C`` the chain runs on ``X^T`` implicitly with ``A = X^T X``.  Every product accumulates in fp32
-and is rounded to bf16, as in the reference (training/optimizers/muon_triton.py:327-377).  Shapes the TMA path
-cannot take (a side that is not a multiple of 8, e.g. the 18 x d gate matrices) use the library batched GEMM.
+and is rounded to bf16, as in the reference (training/optimizers/muon_triton.py:327-377).  A short side that is not a
+multiple of 8 (the 18 x d gate matrices; TMA wants 16-byte rows) is padded with zero rows or columns, which the chain
+leaves zero, so the result is the one of the unpadded matrix.
 """
 
 from __future__ import annotations
@@ -31,6 +32,13 @@ def ns_iterations(X: Tensor, Y: Tensor, coeffs, final_extra_dst=None) -> Tensor:
     n, R, C = X.shape
     tall = R > C
     r = min(R, C)
+    if r % 8 != 0 and max(R, C) % 8 == 0 and X.is_cuda and X.dtype == torch.bfloat16 and G.usable(X.new_empty(8, 8)):
+        rp = (r + 7) // 8 * 8
+        Xp = X.new_zeros((n, R, rp) if tall else (n, rp, C))
+        (Xp[:, :, :r] if tall else Xp[:, :r]).copy_(X)
+        res = ns_iterations(Xp, torch.empty_like(Xp), coeffs)
+        Y.copy_(res[:, :, :r] if tall else res[:, :r])
+        return Y
     if r % 8 == 0 and max(R, C) % 8 == 0 and G.usable(X, Y):
         A = torch.empty((n, r, r), dtype=torch.bfloat16, device=X.device)
         B = torch.empty_like(A)

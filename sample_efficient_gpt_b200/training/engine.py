@@ -58,6 +58,10 @@ class FusedEngine:
         for p in self._matrix_params:
             self.shadows[p] = p.detach().to(act_dtype) if act_dtype != p.dtype else p.detach()
         self._first_accum = True
+        # the per-layer LayerNorm scaling factors live in device buffers of the model: read them once, not with a
+        # device-to-host copy (and a stalled launch queue) in every block of every pass
+        self._ln_scale = [float(b.ln1.position_scale) for b in model.blocks]
+        self._final_scale = float(model.final_norm.position_scale)
         at = model.blocks[0].attn
         self.H, self.Hkv, self.hd = at.n_heads, at.n_kv_heads, at.head_dim
         self._ones = torch.ones(1, dtype=torch.float32, device=model.embedding.weight.device)
@@ -109,6 +113,14 @@ class FusedEngine:
             if p.requires_grad and p.grad is None:
                 p.grad = torch.zeros_like(p, dtype=torch.float32)
 
+    def _dqkvz_buffer(self, T: int, n_ext: int, like: Tensor) -> Tensor:
+        """Gradient buffer of the fused qkv+gate projection, shared by all blocks (the kernels of a step run in stream order);
+        its padding columns are zeroed once, at allocation, and never written afterwards."""
+        buf = getattr(self, "_dqkvz", None)
+        if buf is None or buf.shape != (T, n_ext) or buf.dtype != like.dtype or buf.device != like.device:
+            buf = self._dqkvz = torch.zeros((T, n_ext), dtype=like.dtype, device=like.device)
+        return buf
+
     def _w(self, p: Tensor) -> Tensor:
         return self.shadows[p]
 
@@ -127,12 +139,12 @@ class FusedEngine:
         at = blk.attn
         H, Hkv, hd = self.H, self.Hkv, self.hd
         T = B * S
-        scale = float(blk.ln1.position_scale)
+        scale = self._ln_scale[i]
         x, n1, rstd1, kurt = ops.add_rmsnorm_fwd(res, delta, blk.ln1.gain, scale, blk.ln1.eps, self.lp, want_kurt)
         if i in self.qkvz_w:
             n_qkv = at.qkv.linear.weight.size(0)
             qkvz = ops.matmul_nt(n1, self.qkvz_w[i])
-            qkv, z = qkvz[:, :n_qkv], qkvz[:, n_qkv : n_qkv + H].contiguous()
+            qkv, z = qkvz[:, :n_qkv], qkvz[:, n_qkv : n_qkv + H]  # column views: the kernels take the row stride
         else:
             qkv = ops.matmul_nt(n1, self._w(at.qkv.linear.weight))
             z = ops.matmul_nt(n1, self._w(at.attn_gate.linear.weight)) if at.gating else None
@@ -160,7 +172,7 @@ class FusedEngine:
         H, Hkv, hd = self.H, self.Hkv, self.hd
         T = B * S
         x, n1, rstd1, qkv, z, q, k, v, o, lse, g, y, n2, rstd2, u, f = saved
-        scale = float(blk.ln1.position_scale)
+        scale = self._ln_scale[i]
         w_out, w_qkv = at.out.linear.weight, at.qkv.linear.weight
 
         if blk.is_moe:
@@ -177,28 +189,25 @@ class FusedEngine:
 
         dg = ops.matmul_nn(dy_lp, self._w(w_out))
         self._wgrad(w_out, dy_lp, g)
+        fused = i in self.qkvz_w
+        dqkvz = None
+        if fused:  # [dqkv | dz | zero padding], the layout of the fused projection's output; both kernels write into it
+            n_qkv, n_ext = w_qkv.size(0), self.qkvz_w[i].size(0)
+            dqkvz = self._dqkvz_buffer(T, n_ext, qkv)
         if at.gating:
-            do, dz = ops.gate_bwd(dg, o.view(T, H, hd), z)
+            do, dz = ops.gate_bwd(dg, o.view(T, H, hd), z, dz_out=dqkvz[:, n_qkv : n_qkv + H] if fused else None)
         else:
             do, dz = dg, None
         dq, dk, dv = ops.attention_bwd(do.view(B, S, H, hd), q, k, v, o, lse, True, 0)
         if i == 0 and dv1_acc is not None:
             dv = dv.float() + dv1_acc
         qgain = at.sdpa_qknorm.gain if at.qknorm else self._ones
-        fused = i in self.qkvz_w
-        dqkvz = None
-        if fused:  # [dqkv | dz | zero padding], the layout of the fused projection's output
-            n_qkv, n_ext = w_qkv.size(0), self.qkvz_w[i].size(0)
-            dqkvz = torch.empty((T, n_ext), dtype=qkv.dtype, device=qkv.device)
-            dqkvz[:, n_qkv : n_qkv + H] = dz
-            if n_ext > n_qkv + H:
-                dqkvz[:, n_qkv + H :] = 0
         dqkv, dv1, dqg, da1, da2, dvs = ops.qkv_post_bwd(
             dq, dk, dv, qkv, v1, at.rope.cos, at.rope.sin, qgain, at.alpha1, at.alpha2, at.scale, B, S, H, Hkv, hd, at.qknorm,
-            dqkv_out=dqkvz[:, :n_qkv] if fused else None,
+            dqkv_out=dqkvz[:, :n_qkv] if fused else None, dv1_acc=dv1_acc if v1 is not None else None,
         )
         if dv1 is not None:
-            dv1_acc = dv1 if dv1_acc is None else dv1_acc.add_(dv1)
+            dv1_acc = dv1  # the kernel added this block's part to the running sum (or started it)
         if at.qknorm:
             self._acc(at.sdpa_qknorm.gain, dqg)
         if at.value_residual:
@@ -262,7 +271,7 @@ class FusedEngine:
                 res, delta = y, m
                 kurts.append(kurt)
             fn = model.final_norm
-            xf, hf, rstdf, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, float(fn.position_scale), fn.eps, self.lp, False)
+            xf, hf, rstdf, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, self._final_scale, fn.eps, self.lp, False)
         head = model.lm_head.linear.weight
         with nvtx_range("cross entropy"):
             if first_micro_step:
@@ -271,7 +280,7 @@ class FusedEngine:
                 hf, self._w(head), targets.reshape(-1), LSE_SQUARE_SCALE, IGNORE_INDEX, loss_coef / T, model.output_mult, dw_out=head.grad
             )
         with nvtx_range("backward"):
-            dres, dres_lp, dgain_f = ops.add_rmsnorm_bwd(dh, None, xf, fn.gain, rstdf, float(fn.position_scale), self.lp)
+            dres, dres_lp, dgain_f = ops.add_rmsnorm_bwd(dh, None, xf, fn.gain, rstdf, self._final_scale, self.lp)
             self._acc(fn.gain, dgain_f)
             if self.grad_ready is not None:
                 self.grad_ready([head, fn.gain])
@@ -313,7 +322,7 @@ class FusedEngine:
                 v1 = v
             kurts.append(kurt)
         fn = model.final_norm
-        _, hf, _, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, float(fn.position_scale), fn.eps, self.lp, False)
+        _, hf, _, _ = ops.add_rmsnorm_fwd(res, delta, fn.gain, self._final_scale, fn.eps, self.lp, False)
         loss_tok, z_tok, _, _ = ops.linear_ce_fwd_bwd(
             hf, self._w(model.lm_head.linear.weight), targets.reshape(-1), LSE_SQUARE_SCALE, IGNORE_INDEX, 0.0,
             model.output_mult, need_grad=False,

@@ -93,7 +93,7 @@ def test_newton_schulz_on_gemm_matches_library_path():
     from sample_efficient_gpt_b200.ops.newton_schulz import newton_schulz
 
     torch.manual_seed(4)
-    for shape in [(4, 256, 512), (3, 512, 256), (1152, 1152)]:
+    for shape in [(4, 256, 512), (3, 512, 256), (1152, 1152), (5, 18, 256), (2, 256, 20)]:
         Gm = torch.randn(*shape, device=DEV)
         X = newton_schulz(Gm, 1e-7, POLAR_EXPRESS_COEFFS)
         Xb = Gm.to(torch.bfloat16)

@@ -67,6 +67,17 @@ def test_swiglu_and_gate(bf16):
         dor, dzr = ref.gate_bwd(dg.float(), o.float(), z.float())
         close(do, dor, tol, name="do")
         close(dz, dzr, 0.25 if bf16 else 1e-4, name="dz")
+        # gate logits and their gradient as columns of wider tensors (the fused qkv+gate projection's layout)
+        wide = torch.randn(257, H + 40, device=DEV).to(lp)
+        zs = wide[:, 8 : 8 + H]
+        dwide = torch.full((257, H + 40), 7.0, device=DEV).to(lp)
+        close(_ext().gate_fwd(o, zs), ref.gate_fwd(o.float(), zs.float()), tol, name="gate strided")
+        do2, dz2 = _ext().gate_bwd(dg, o, zs, dwide[:, 16 : 16 + H])
+        dor2, dzr2 = ref.gate_bwd(dg.float(), o.float(), zs.float())
+        close(do2, dor2, tol, name="do strided")
+        close(dwide[:, 16 : 16 + H], dzr2, 0.25 if bf16 else 1e-4, name="dz strided")
+        assert dz2.data_ptr() == dwide[:, 16 : 16 + H].data_ptr()
+        assert bool((dwide[:, :16] == 7.0).all()) and bool((dwide[:, 16 + H :] == 7.0).all()), "columns around dz must stay untouched"
 
 
 @pytest.mark.parametrize("hd,H,Hkv", [(64, 18, 6), (128, 4, 2), (32, 4, 4)])
@@ -99,6 +110,12 @@ def test_qkv_post(hd, H, Hkv, bf16, qknorm):
                 close(out[1], outr[1], tol, name="dv1")
             for i, nm in zip(range(2, 6), ("dqgain", "da1", "da2", "dvscale")):
                 close(out[i], outr[i], 0.5 if bf16 else 1e-2, 2e-3, name=nm)
+            if v1_ is not None:  # the running sum over blocks is updated in place
+                run = torch.randn(B, S, Hkv, hd, device=DEV)
+                before = run.clone()
+                out2 = _ext().qkv_post_bwd(dq, dk, dv, qkv, v1_, *args, None, run)
+                assert out2[1].data_ptr() == run.data_ptr()
+                close(run, before + outr[1], tol, name="dv1 accumulated")
 
 
 def test_ce_chunk():
