@@ -27,6 +27,7 @@
 // (transformer/ops/triton_flash_attn.py:104-201).  Every mbarrier wait is bounded.
 #include <cuda.h>
 
+#include "bounds.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "sm100.cuh"
@@ -442,8 +443,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         float f[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(a[e]) * mul;
+        if (SEG_IN_BOUNDS(p.status, 33, row + c * 32, 32, (size_t)p.B * p.S * p.Hkv * kBHD)) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(dst + c * 32)[q4] = pack8(f + q4 * 8);
+          for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(dst + c * 32)[q4] = pack8(f + q4 * 8);
+        }
       }
     }
   }

@@ -25,6 +25,7 @@
 
 #include <type_traits>
 
+#include "bounds.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "sm100.cuh"
@@ -367,12 +368,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         float f[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(o[e]) * inv;
-        if (in_range) {
+        if (in_range && SEG_IN_BOUNDS(p.status, 31, (orow - p.o) + c * 32, 32, (size_t)p.B * p.S * p.H * kAHD)) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) reinterpret_cast<bf16x8*>(orow + c * 32)[q4] = pack8(f + q4 * 8);
         }
       }
-      if (in_range) p.lse[((size_t)b * p.H + h) * p.S + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      if (in_range && SEG_IN_BOUNDS(p.status, 32, ((size_t)b * p.H + h) * p.S + row, 1, (size_t)p.B * p.H * p.S))
+        p.lse[((size_t)b * p.H + h) * p.S + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
       SEG_PROF_ADD(7, t)
     }
   }

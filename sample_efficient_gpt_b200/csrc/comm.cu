@@ -18,6 +18,7 @@
 //
 // The reference reduces each bucket with an NCCL all-reduce of a bf16 copy and casts back on the host side
 // (training/distributed/ddp_bucket.py:91-104,118-134).
+#include "bounds.cuh"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -81,7 +82,8 @@ __device__ __forceinline__ void multimem_st_bf16x8(void* mc_ptr, const uint32_t*
 // sum of one scalar per rank instead of a pass over every gradient tensor).
 __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict__ grads, CommPeers pe, void* mc_base,
                                                              int64_t wire_off, int64_t n, int rank, int world, uint32_t seq,
-                                                             int* status, float* __restrict__ sq_out, long long limit) {
+                                                             int* status, float* __restrict__ sq_out, long long limit,
+                                                             int64_t wire_elems) {
   const int64_t slice = n / world;
   const int nb = gridDim.x;
   // sub-slice b of a slice, in units of 8 elements
@@ -101,7 +103,8 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
         if (v + (int64_t)u * blockDim.x < v1) load8<float>(grads + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
-        if (v + (int64_t)u * blockDim.x < v1) store8<__nv_bfloat16>(w_me + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
+        if (v + (int64_t)u * blockDim.x < v1 && SEG_IN_BOUNDS(status, 11, wire_off + base + (v + (int64_t)u * blockDim.x) * 8, 8, wire_elems))
+          store8<__nv_bfloat16>(w_me + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
     }
   }
   if (!block_barrier(pe, rank, world, seq, status, limit)) return;
@@ -165,13 +168,15 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
           const bf16x8 out = pack8(acc);
           float fin[8];
           unpack8(out, fin);  // every rank ends with the same bf16-rounded value
-          store8<float>(grads + base + vv * 8, fin);
+          if (SEG_IN_BOUNDS(status, 13, base + vv * 8, 8, n)) store8<float>(grads + base + vv * 8, fin);
 #pragma unroll
           for (int j = 0; j < 8; ++j) sq = fmaf(fin[j], fin[j], sq);
+          if (SEG_IN_BOUNDS(status, 12, wire_off + base + vv * 8, 8, wire_elems)) {
 #pragma unroll
-          for (int p = 0; p < kMaxRanks; ++p)
-            if (p < world && p != rank)
-              *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(pe.buf[p]) + wire_off + base + vv * 8) = out;
+            for (int p = 0; p < kMaxRanks; ++p)
+              if (p < world && p != rank)
+                *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(pe.buf[p]) + wire_off + base + vv * 8) = out;
+          }
         }
       }
     }
@@ -194,7 +199,8 @@ __global__ void __launch_bounds__(512) allreduce_bucket_kernel(float* __restrict
         if (v + (int64_t)u * blockDim.x < v1) load8<__nv_bfloat16>(w_me + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
-        if (v + (int64_t)u * blockDim.x < v1) store8<float>(grads + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
+        if (v + (int64_t)u * blockDim.x < v1 && SEG_IN_BOUNDS(status, 13, base + (v + (int64_t)u * blockDim.x) * 8, 8, n))
+          store8<float>(grads + base + (v + (int64_t)u * blockDim.x) * 8, f[u]);
     }
   }
 }
@@ -229,9 +235,10 @@ static CommPeers make_peers(void* const* bufs, uint32_t* const* flags, int world
 
 void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
                            int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st, float* sq_out,
-                           long long wait_cycles) {
+                           long long wait_cycles, int64_t wire_elems) {
+  if (wire_elems <= 0) wire_elems = wire_off + n;  // callers that do not say how long the wire buffers are: this bucket's end
   allreduce_bucket_kernel<<<blocks, 512, 0, st>>>(grads, make_peers(wire_bufs, flags, world), mc_base, wire_off, n, rank, world, seq,
-                                                  status, sq_out, wait_cycles > 0 ? wait_cycles : kCommWaitCycles);
+                                                  status, sq_out, wait_cycles > 0 ? wait_cycles : kCommWaitCycles, wire_elems);
 }
 
 void comm_allgather(void* const* bufs, uint32_t* const* flags, int64_t off_bytes, int64_t chunk_bytes, int rank, int world,

@@ -19,7 +19,7 @@ void fill_ptrs(const std::vector<int64_t>& in, void** out, int world) {
 
 void comm_allreduce_bucket(Tensor grads, std::vector<int64_t> wire_ptrs, std::vector<int64_t> flag_ptrs, int64_t mc_ptr,
                            int64_t wire_off, int64_t rank, int64_t seq, int64_t blocks, Tensor status,
-                           const std::optional<Tensor>& sq_out, int64_t wait_cycles) {
+                           const std::optional<Tensor>& sq_out, int64_t wait_cycles, int64_t wire_elems) {
   TORCH_CHECK(grads.is_cuda() && grads.scalar_type() == at::kFloat && grads.is_contiguous(), "grads must be a contiguous CUDA fp32 tensor");
   TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt, "status must be a CUDA int32 tensor");
   const int world = (int)wire_ptrs.size();
@@ -35,7 +35,7 @@ void comm_allreduce_bucket(Tensor grads, std::vector<int64_t> wire_ptrs, std::ve
   seg::comm_allreduce_bucket(grads.data_ptr<float>(), wires, reinterpret_cast<uint32_t* const*>(flags),
                              reinterpret_cast<void*>(static_cast<uintptr_t>(mc_ptr)), wire_off, n, (int)rank, world, (uint32_t)seq,
                              (int)blocks, status.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream(),
-                             sq_out.has_value() ? sq_out->data_ptr<float>() : nullptr, (long long)wait_cycles);
+                             sq_out.has_value() ? sq_out->data_ptr<float>() : nullptr, (long long)wait_cycles, wire_elems);
 }
 
 void comm_allgather(std::vector<int64_t> buf_ptrs, std::vector<int64_t> flag_ptrs, int64_t off_bytes, int64_t chunk_bytes,
@@ -58,7 +58,8 @@ void comm_allgather(std::vector<int64_t> buf_ptrs, std::vector<int64_t> flag_ptr
 void register_comm(pybind11::module_& m) {
   m.def("comm_allreduce_bucket", &comm_allreduce_bucket, pybind11::arg("grads"), pybind11::arg("wire_ptrs"), pybind11::arg("flag_ptrs"),
         pybind11::arg("mc_ptr"), pybind11::arg("wire_off"), pybind11::arg("rank"), pybind11::arg("seq"), pybind11::arg("blocks"),
-        pybind11::arg("status"), pybind11::arg("sq_out") = std::nullopt, pybind11::arg("wait_cycles") = 0);
+        pybind11::arg("status"), pybind11::arg("sq_out") = std::nullopt, pybind11::arg("wait_cycles") = 0,
+        pybind11::arg("wire_elems") = 0);
   m.def("comm_allgather", &comm_allgather, pybind11::arg("buf_ptrs"), pybind11::arg("flag_ptrs"), pybind11::arg("off_bytes"),
         pybind11::arg("chunk_bytes"), pybind11::arg("rank"), pybind11::arg("seq"), pybind11::arg("blocks"), pybind11::arg("status"),
         pybind11::arg("wait_cycles") = 0);

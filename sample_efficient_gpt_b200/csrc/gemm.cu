@@ -25,6 +25,7 @@
 // (training/optimizers/muon_triton.py:58-252, ns_line_1 / ns_line_2).
 #include <cuda.h>
 
+#include "bounds.cuh"
 #include "common.cuh"
 #include "gemm_params.cuh"
 #include "kernels.h"
@@ -289,8 +290,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                   f.x += p.beta * ccur[i].x; f.y += p.beta * ccur[i].y; f.z += p.beta * ccur[i].z; f.w += p.beta * ccur[i].w;
                 }
                 if (p.route_rows > 0) {
-                  store4<OutT>(rbase[i] + col + 4 * q, f);
-                } else {
+                  const int reg = r / p.route_rows;
+                  const int64_t roff = p.route_base + (int64_t)tc.b * p.route_batch_stride + (int64_t)(r - reg * p.route_rows) * p.ldd + col + 4 * q;
+                  if (SEG_IN_BOUNDS(p.status, 3, reg < 8 ? roff : -1, 4, p.route_extent)) store4<OutT>(rbase[i] + col + 4 * q, f);
+                } else if (SEG_IN_BOUNDS(p.status, 1, off, 4, p.d_extent)) {
                   store4<OutT>(D + off, f);
                   for (int d = 0; d < p.n_extra; ++d) store4<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + off, f);
                 }
@@ -302,8 +305,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     float val = fv[e];
                     if (C != nullptr) val += p.beta * to_f<OutT>(C[off + e]);
                     if (p.route_rows > 0) {
-                      rbase[i][col + 4 * q + e] = from_f<OutT>(val);
-                    } else {
+                      const int reg = r / p.route_rows;
+                      const int64_t roff = p.route_base + (int64_t)tc.b * p.route_batch_stride + (int64_t)(r - reg * p.route_rows) * p.ldd + col + 4 * q + e;
+                      if (SEG_IN_BOUNDS(p.status, 3, reg < 8 ? roff : -1, 1, p.route_extent)) rbase[i][col + 4 * q + e] = from_f<OutT>(val);
+                    } else if (SEG_IN_BOUNDS(p.status, 1, off + e, 1, p.d_extent)) {
                       D[off + e] = from_f<OutT>(val);
                       for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[off + e] = from_f<OutT>(val);
                     }
@@ -331,8 +336,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (row < p.M && cc < ncols) {
                   const OutT val = from_f<OutT>(fv[e]);
                   const int64_t moff = boff + (int64_t)(col + cc) * p.ldd + row;
-                  D[moff] = val;
-                  for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+                  if (SEG_IN_BOUNDS(p.status, 4, moff, 1, p.d_extent)) {
+                    D[moff] = val;
+                    for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+                  }
                 }
               }
             }
@@ -359,6 +366,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------ host side
+static int64_t g_debug_extent_cap = 0;
+void gemm_debug_extent_cap(int64_t elements) { g_debug_extent_cap = elements > 0 ? elements : 0; }
+int64_t gemm_debug_extent_cap_value() { return g_debug_extent_cap; }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -452,6 +463,10 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
   p.route_batch_stride = route_batch_stride;
   p.route_base = route_base;
   p.wait_limit = wait_limit;
+  // extents for the debug build's index checks: last element the epilogue may touch, plus one
+  p.d_extent = (int64_t)(batch - 1) * bsd + (int64_t)(M - 1) * ldd + N;
+  p.route_extent = n_route > 0 ? route_base + (int64_t)(batch - 1) * route_batch_stride + (int64_t)(route_rows - 1) * ldd + N : 0;
+  if (g_debug_extent_cap > 0 && p.d_extent > g_debug_extent_cap) p.d_extent = g_debug_extent_cap;
   p.reduce = 0;
   p.n_static = 0;
   p.splits = 1;

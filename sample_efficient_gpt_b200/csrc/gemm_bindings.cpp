@@ -47,6 +47,14 @@ DeviceState& device_state(const c10::Device& dev) {
   return it->second;
 }
 
+}  // namespace
+
+// The per-device status word of the GEMM / attention kernels, for other binding files whose kernels report into it
+// (index checks of the debug build).
+int* package_status_ptr(const c10::Device& dev) { return device_state(dev).status.data_ptr<int>(); }
+
+namespace {
+
 void check_operand(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, " must be a CUDA bf16 tensor");
   TORCH_CHECK(t.dim() == 2 || t.dim() == 3, name, " must be 2-D or 3-D");
@@ -133,9 +141,13 @@ int64_t gemm_status(int64_t device_index) {
 }
 
 void gemm_reset_status(int64_t device_index) {
+  // raw memsets: the tensors may have been created under inference mode, where in-place tensor ops are refused later
+  c10::cuda::CUDAGuard guard((c10::DeviceIndex)device_index);
   auto& st = device_state(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
-  st.status.zero_();
-  for (auto& kv : st.workspaces) kv.second.flags.zero_();  // a kernel that gave up may have left parts announced
+  const cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+  cudaMemsetAsync(st.status.data_ptr(), 0, sizeof(int), stream);
+  for (auto& kv : st.workspaces)  // a kernel that gave up may have left parts announced
+    cudaMemsetAsync(kv.second.flags.data_ptr(), 0, (size_t)kv.second.flags.numel() * sizeof(int), stream);
 }
 
 // Causal GQA flash attention forward on the tcgen05 kernel: returns (o, lse).
@@ -202,5 +214,11 @@ void register_gemm(pybind11::module_& m) {
   m.def("fa_bwd", &fa_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("lse"),
         pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
   m.def("gemm_status", &gemm_status);
+  m.def("gemm_debug_extent_cap", [](int64_t n) { seg::gemm_debug_extent_cap(n); });
+#ifdef SEG_DEBUG_BOUNDS
+  m.attr("DEBUG_BOUNDS") = true;
+#else
+  m.attr("DEBUG_BOUNDS") = false;
+#endif
   m.def("gemm_reset_status", &gemm_reset_status);
 }

@@ -30,6 +30,7 @@
 
 #include <cstdlib>
 
+#include "bounds.cuh"
 #include "common.cuh"
 #include "gemm_pair_sched.h"
 #include "gemm_params.cuh"
@@ -294,6 +295,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (!owner) {
         // -------- part of a tile: the raw accumulator goes to the item's slot, then the flag of this warp is raised
         const int slot = pair_slot(sch, tl.ks, tl.t);
+        if (!SEG_IN_BOUNDS(p.status, 5, slot, 1, kPairMaxSlots)) { ok = false; break; }
         uint4* const my_slot = p.ws + ((size_t)(slot * 2 + (int)rank) * 8 + ep) * (4 * 8 * 32);
 #pragma unroll 1
         for (int ci = 0; ci < 4; ++ci) {
@@ -478,8 +480,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     f.x += p.beta * ccur[i].x; f.y += p.beta * ccur[i].y; f.z += p.beta * ccur[i].z; f.w += p.beta * ccur[i].w;
                   }
                   if (p.route_rows > 0) {
-                    store4<OutT>(rbase[i] + col + 4 * q, f);
-                  } else {
+                    const int reg = r / p.route_rows;
+                    const int64_t roff = p.route_base + (int64_t)tl.b * p.route_batch_stride + (int64_t)(r - reg * p.route_rows) * p.ldd + col + 4 * q;
+                    if (SEG_IN_BOUNDS(p.status, 3, reg < 8 ? roff : -1, 4, p.route_extent)) store4<OutT>(rbase[i] + col + 4 * q, f);
+                  } else if (SEG_IN_BOUNDS(p.status, 1, off, 4, p.d_extent)) {
                     store4<OutT>(D + off, f);
                     for (int d = 0; d < p.n_extra; ++d) store4<OutT>(reinterpret_cast<OutT*>(p.D_extra[d]) + off, f);
                   }
@@ -491,8 +495,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                       float val = fv[e];
                       if (C != nullptr) val += p.beta * to_f<OutT>(C[off + e]);
                       if (p.route_rows > 0) {
-                        rbase[i][col + 4 * q + e] = from_f<OutT>(val);
-                      } else {
+                        const int reg = r / p.route_rows;
+                        const int64_t roff = p.route_base + (int64_t)tl.b * p.route_batch_stride + (int64_t)(r - reg * p.route_rows) * p.ldd + col + 4 * q + e;
+                        if (SEG_IN_BOUNDS(p.status, 3, reg < 8 ? roff : -1, 1, p.route_extent)) rbase[i][col + 4 * q + e] = from_f<OutT>(val);
+                      } else if (SEG_IN_BOUNDS(p.status, 1, off + e, 1, p.d_extent)) {
                         D[off + e] = from_f<OutT>(val);
                         for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[off + e] = from_f<OutT>(val);
                       }
@@ -519,8 +525,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                   if (row < p.M && cc < ncols) {
                     const OutT val = from_f<OutT>(fv[e]);
                     const int64_t moff = boff + (int64_t)(col + cc) * p.ldd + row;
-                    D[moff] = val;
-                    for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+                    if (SEG_IN_BOUNDS(p.status, 4, moff, 1, p.d_extent)) {
+                      D[moff] = val;
+                      for (int d = 0; d < p.n_extra; ++d) reinterpret_cast<OutT*>(p.D_extra[d])[moff] = val;
+                    }
                   }
                 }
               }
@@ -607,6 +615,10 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   p.route_base = route_base;
   for (int i = 0; i < 8; ++i) p.D_route[i] = (n_route > 0) ? d_route[i < n_route ? i : n_route - 1] : nullptr;
   p.wait_limit = wait_limit;
+  // extents for the debug build's index checks: last element the epilogue may touch, plus one
+  p.d_extent = (int64_t)(batch - 1) * bsd + (int64_t)(M - 1) * ldd + N;
+  p.route_extent = n_route > 0 ? route_base + (int64_t)(batch - 1) * route_batch_stride + (int64_t)(route_rows - 1) * ldd + N : 0;
+  if (gemm_debug_extent_cap_value() > 0 && p.d_extent > gemm_debug_extent_cap_value()) p.d_extent = gemm_debug_extent_cap_value();
   p.reduce = 0;
   p.ws = reinterpret_cast<uint4*>(workspace);
   p.ws_flags = ws_flags;

@@ -33,6 +33,9 @@ struct GemmParams {
   int route_rows;  // 0: plain output
   int64_t route_batch_stride, route_base;
   long long wait_limit;  // cycles a wait may stand still before it gives up; 0: the defaults of sm100.cuh
+  // elements that D (and every extra destination) / every routed destination holds from its base: read by the index checks
+  // of the debug build only (bounds.cuh)
+  int64_t d_extent, route_extent;
   // pair kernel only
   int reduce;          // TMA epilogue: 1 = add the tile into D (cp.reduce.async.bulk ... add), 0 = store it
   int n_static, splits;  // schedule (gemm_pair_sched.h): tiles computed whole; ranges of the contraction for the others

@@ -82,7 +82,8 @@ constexpr int kCommMaxBlocks = 128;  // flag words per rank = kCommMaxBlocks * k
 // sq_out (optional, fp32 scalar): += sum of squares of the reduced slice this rank owns.
 void comm_allreduce_bucket(float* grads, void* const* wire_bufs, uint32_t* const* flags, void* mc_base, int64_t wire_off,
                            int64_t n, int rank, int world, uint32_t seq, int blocks, int* status, cudaStream_t st,
-                           float* sq_out = nullptr, long long wait_cycles = 0);
+                           float* sq_out = nullptr, long long wait_cycles = 0, int64_t wire_elems = 0);
+// wire_elems: bf16 elements every wire buffer holds (index checks of the debug build; 0: wire_off + n).
 // wait_cycles (both collectives): how long a block waits for a peer's flag before it gives up and sets *status to
 // 1000 + peer (0: about ten seconds).
 // bufs[p] + off_bytes holds `world` chunks of chunk_bytes (multiple of 16); chunk `rank` is valid on entry, all on exit.
@@ -107,7 +108,8 @@ void moe_slots(const int* idx, const int* block_off, int T, int E, int k, int ca
 // system-scope release (consumed by gemm_bf16's wait_flags).  done_counter: a zero-initialised device word.
 void moe_push(const void* x, const int* idx, const int* slot, const float* w, const int* totals, void* const* dst, int T, int d,
               int E, int k, int cap, int world, int rank, cudaStream_t st, uint32_t* const* flags = nullptr,
-              uint32_t* done_counter = nullptr, uint32_t seq = 0);
+              uint32_t* done_counter = nullptr, uint32_t seq = 0, int* status = nullptr);
+// status (optional): receives the code of the debug build's index checks (bounds.cuh).
 // out[t] = sum over kept assignments of w * src[owner](e_local, rank, slot) (w == nullptr: 1); with dots != nullptr also
 // dots[t, c] = <g[t], src2[owner] row> (0 for dropped assignments).  out is bf16 or fp32.
 void moe_pull(void* const* src, void* const* src2, const int* idx, const int* slot, const float* w, const void* g, void* out,
@@ -137,6 +139,10 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
 // impl: 1 = CTA-pair kernel (cta_group::2, 256-row tiles), 0 = one CTA per 128-row tile.  workspace / ws_flags / split_k:
 // the pair kernel's buffers for tiles cut along the contraction (sizes: gemm_pair_workspace_bytes / gemm_pair_flag_words) and
 // the switch for cutting.
+// Debug build only (no effect otherwise): every GEMM launched afterwards pretends that its output holds at most `elements`
+// elements (0: off), so that a test can watch the index checks refuse in-range stores - and only those - without any fault.
+void gemm_debug_extent_cap(int64_t elements);
+int64_t gemm_debug_extent_cap_value();
 size_t gemm_pair_workspace_bytes();
 size_t gemm_pair_flag_words();
 // d_route (optional): routed output - rows [r * route_rows, (r+1) * route_rows) of every batch entry go to d_route[r] (a buffer of

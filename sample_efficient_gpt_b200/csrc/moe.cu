@@ -20,6 +20,7 @@
 // overlapped mode, because the push kernel's last CTA releases a per-destination flag that the GEMM's producer acquires per
 // source region (gemm.cu).  None of the kernels here waits on anything.
 // The reference has no mixture-of-experts code; the specification is models/moe.py of this package.
+#include "bounds.cuh"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const __nv_bfloat16* __re
                                                      const int* __restrict__ slot, const float* __restrict__ w,
                                                      const int* __restrict__ totals, MoeBufs dst, int T, int d, int E, int k, int cap,
                                                      int e_local, int world, int rank, int n_row_blocks, MoeBufs flags,
-                                                     uint32_t* done_counter, uint32_t seq) {
+                                                     uint32_t* done_counter, uint32_t seq, int* status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vecs = d / 8;
   if ((int)blockIdx.x < n_row_blocks) {
@@ -155,6 +156,10 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const __nv_bfloat16* __re
         const int s = slot[(size_t)t * k + c];
         if (s >= 0) {
           const int e = idx[(size_t)t * k + c];
+          // expert and slot come from device tables: in the debug build both, and the row they address, are checked
+          if (!SEG_IN_BOUNDS(status, 21, e, 1, E) || !SEG_IN_BOUNDS(status, 21, s, 1, cap) ||
+              !SEG_IN_BOUNDS(status, 22, ((size_t)((e % e_local) * world + rank) * cap + s) * d, d, (size_t)e_local * world * cap * d))
+            continue;
           rows[c] = reinterpret_cast<__nv_bfloat16*>(dst.p[e / e_local]) + ((size_t)((e % e_local) * world + rank) * cap + s) * d;
           if (w != nullptr) ws[c] = w[(size_t)t * k + c];
         }
@@ -330,12 +335,12 @@ void moe_slots(const int* idx, const int* block_off, int T, int E, int k, int ca
 
 void moe_push(const void* x, const int* idx, const int* slot, const float* w, const int* totals, void* const* dst, int T, int d,
               int E, int k, int cap, int world, int rank, cudaStream_t st, uint32_t* const* flags, uint32_t* done_counter,
-              uint32_t seq) {
+              uint32_t seq, int* status) {
   const int n_row_blocks = (T + 7) / 8;
   const bool signal = flags != nullptr && done_counter != nullptr;
   moe_push_kernel<<<n_row_blocks + E * kMoeTailBlocks, 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), idx, slot, w, totals, make_bufs(dst, world), T, d, E, k, cap, E / world, world, rank,
-      n_row_blocks, make_bufs(signal ? reinterpret_cast<void* const*>(flags) : nullptr, world), signal ? done_counter : nullptr, seq);
+      n_row_blocks, make_bufs(signal ? reinterpret_cast<void* const*>(flags) : nullptr, world), signal ? done_counter : nullptr, seq, status);
 }
 
 void moe_pull(void* const* src, void* const* src2, const int* idx, const int* slot, const float* w, const void* g, void* out,

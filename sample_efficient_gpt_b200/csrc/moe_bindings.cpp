@@ -8,6 +8,8 @@
 
 #include "kernels.h"
 
+int* package_status_ptr(const c10::Device& dev);  // gemm_bindings.cpp
+
 namespace {
 
 using torch::Tensor;
@@ -82,7 +84,7 @@ void moe_push(const Tensor& x, const Tensor& idx, const Tensor& slot, const std:
   seg::moe_push(x.data_ptr(), idx.data_ptr<int>(), slot.data_ptr<int>(), w.has_value() ? w->data_ptr<float>() : nullptr,
                 totals.data_ptr<int>(), bufs, T, d, E, k, (int)cap, world, (int)rank, at::cuda::getCurrentCUDAStream().stream(),
                 signal ? reinterpret_cast<uint32_t* const*>(flags) : nullptr,
-                signal ? reinterpret_cast<uint32_t*>(done_counter->data_ptr<int>()) : nullptr, (uint32_t)seq);
+                signal ? reinterpret_cast<uint32_t*>(done_counter->data_ptr<int>()) : nullptr, (uint32_t)seq, package_status_ptr(x.device()));
 }
 
 // returns (out [T,d], dots [T,k] or empty)

@@ -29,7 +29,9 @@ def ext():
     global _EXT, _EXT_ERR
     if _EXT is None and _EXT_ERR is None:
         try:
-            _EXT = importlib.import_module("sample_efficient_gpt_b200._C")
+            # SEGPT_DEBUG_BOUNDS=1: the build whose kernels check every computed store index (csrc/bounds.cuh)
+            name = "_C_dbg" if os.environ.get("SEGPT_DEBUG_BOUNDS", "0") == "1" else "_C"
+            _EXT = importlib.import_module(f"sample_efficient_gpt_b200.{name}")
         except Exception as e:  # not built, or built for another torch
             _EXT_ERR = e
     return _EXT

@@ -6,6 +6,7 @@
   python -m sample_efficient_gpt_b200.ops.bench_ops --op linear_ce                    ([32768,1152] x [49152,1152])
   python -m sample_efficient_gpt_b200.ops.bench_ops --op elementwise                  (norms, SwiGLU, qkv post-processing, gate, AdamW, EMA)
   python -m sample_efficient_gpt_b200.ops.bench_ops --op decode                       (generation: eager vs CUDA-graph decode step)
+  python -m sample_efficient_gpt_b200.ops.bench_ops --op muon --layers 30                 (one NorMuonCWD step on the block matrices)
   python -m sample_efficient_gpt_b200.ops.bench_ops --op moe                          (router, dispatch, combine, router backward)
 Each line reports milliseconds, achieved TFLOP/s or GB/s, and the library call it replaces where there is one.
 """
@@ -187,7 +188,7 @@ def bench_attention(a):
 def bench_linear_ce(a):
     from sample_efficient_gpt_b200.ops.cross_entropy import linear_ce_fwd_bwd
 
-    T, d, V = 32768, 1152, 49152
+    T, d, V = a.tokens, 1152, 49152
     h = rnd(T, d, scale=1.0)
     w = rnd(V, d, scale=d**-0.5)
     tg = torch.randint(0, V, (T,), device="cuda")
@@ -201,6 +202,9 @@ def bench_linear_ce(a):
 
     fl = 3 * 2.0 * T * d * V / 1e9
     t_o = timeit(ours, a.iters)
+    if a.ours_only:  # profiling runs: no library or materialised-logits comparison (6 GB of fp32 logits)
+        print(json.dumps({"op": "linear_ce_fwd_bwd", "tokens": T, "ours_ms": t_o, "ours_tflops": fl / t_o}))
+        return
     ops._DISABLED.add("ce_gemm")  # same chunking and CE kernel, library GEMMs
     try:
         t_c = timeit(ours, a.iters)
@@ -209,6 +213,19 @@ def bench_linear_ce(a):
     t_l = timeit(lib, max(2, a.iters // 2))
     print(json.dumps({"op": "linear_ce_fwd_bwd", "ours_ms": t_o, "ours_tflops": fl / t_o, "with_library_gemms_ms": t_c,
                       "with_library_gemms_tflops": fl / t_c, "materialised_logits_ms": t_l}))
+
+
+def bench_muon(a):
+    """One NorMuonCWD step on the IMU-1 block matrices of ``--layers`` layers (momentum, Newton-Schulz, tail)."""
+    from sample_efficient_gpt_b200.optim import NorMuonCWD
+
+    shapes = [(1920, 1152), (1152, 1152), (6144, 1152), (1152, 3072)]
+    ps = [torch.nn.Parameter(torch.randn(r, c, device="cuda") * 0.02) for _ in range(a.layers) for (r, c) in shapes]
+    for p_ in ps:
+        p_.grad = torch.randn_like(p_) * 1e-3
+    opt = NorMuonCWD(ps, lr=0.02, momentum=0.95, weight_decay=0.1)
+    t = timeit(lambda: opt.step(), a.iters, flush=False)
+    print(json.dumps({"op": "normuon_cwd_step", "layers": a.layers, "matrices": len(ps), "ms": t}))
 
 
 def measured_hbm_gbs() -> tuple[float, str]:
@@ -334,7 +351,8 @@ def bench_decode(a):
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe", "decode"])
+    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe", "decode", "muon"])
+    p.add_argument("--layers", type=int, default=30, help="muon: layers whose four block matrices are stepped")
     p.add_argument("--m", type=int, default=8192)
     p.add_argument("--n", type=int, default=1920)
     p.add_argument("--k", type=int, default=1152)
@@ -344,11 +362,13 @@ def main():
     p.add_argument("--cols", type=int, default=3072)
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--tokens", type=int, default=32768, help="linear_ce: rows of the hidden-state matrix")
+    p.add_argument("--ours-only", action="store_true", help="linear_ce / muon: skip the comparison arms (profiling runs)")
     p.add_argument("--sustained", action="store_true", help="gemm: time about a second of back-to-back calls (power-capped rate) instead of flushed single calls")
     p.add_argument("--no-split-k", action="store_true", help="gemm: whole tiles only, no tile is cut along the contraction")
     p.add_argument("--shapes", default="", help="gemm: 'block' runs the IMU-1 block shapes (forward, data gradient, weight gradient)")
     a = p.parse_args()
-    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe, "decode": bench_decode}[a.op](a)
+    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe, "decode": bench_decode, "muon": bench_muon}[a.op](a)
 
 
 if __name__ == "__main__":

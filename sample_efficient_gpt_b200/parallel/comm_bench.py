@@ -136,8 +136,40 @@ def nccl_table(reps: int = 10, warmup: int = 5) -> list[dict]:
     return out
 
 
+def emulate_one_gpu(world: int, mb: int, blocks: int, reps: int) -> dict:
+    """The bucket kernel as rank 0 of ``world`` with every rank's wire buffer and flag array on this GPU and all flags set
+    in advance, so that no barrier waits: the kernel's own instruction and memory behaviour (what a profiler may look at
+    in a single process), without NVLink.  Not a bandwidth number."""
+    from sample_efficient_gpt_b200 import ops
+
+    ext = ops.ext()
+    n = mb * 1024 * 1024 // 4 // (8 * world) * (8 * world)
+    grads = torch.randn(n, device="cuda")
+    wires = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    flags = [torch.full((ext.COMM_MAX_BLOCKS * ext.COMM_MAX_RANKS,), 2**30, dtype=torch.int32, device="cuda") for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sq = torch.zeros(1, device="cuda")
+    run = lambda: ext.comm_allreduce_bucket(grads, [w.data_ptr() for w in wires], [f.data_ptr() for f in flags], 0, 0, 0, 1, blocks,  # noqa: E731
+                                            status, sq, 2_000_000, n)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    out = {"mode": "one GPU plays rank 0, peers' buffers local", "world": world, "mb": mb, "blocks": blocks, "ms": e0.elapsed_time(e1) / reps,
+           "status": int(status.item())}
+    print(json.dumps(out), flush=True)
+    return out
+
+
 def main(argv=None):
     p = argparse.ArgumentParser()
+    p.add_argument("--emulate-ranks", type=int, default=0, help="single process, one GPU: run the bucket kernel as rank 0 of N with local stand-ins for the peers (profiling)")
+    p.add_argument("--mb", type=int, default=32, help="--emulate-ranks: bucket size")
     p.add_argument("--min-mb", type=int, default=1)
     p.add_argument("--max-mb", type=int, default=512)
     p.add_argument("--reps", type=int, default=10)
@@ -148,6 +180,9 @@ def main(argv=None):
     p.add_argument("--out", default=None)
     a = p.parse_args(argv)
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    if a.emulate_ranks > 1:
+        emulate_one_gpu(a.emulate_ranks, a.mb, a.blocks, a.reps)
+        return
     dist.init_process_group("nccl")
     try:
         if a.nccl_table:

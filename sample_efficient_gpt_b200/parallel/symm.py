@@ -114,7 +114,7 @@ class SymmComm:
         self.stream.wait_event(ev)
         with torch.cuda.stream(self.stream):
             ops.ext().comm_allreduce_bucket(self.flat_grads[s:e], self.wire_ptrs, self.flag_ptrs, self.mc_ptr, s, self.rank,
-                                            self.seq, self.blocks, self.status, self.grad_sq)
+                                            self.seq, self.blocks, self.status, self.grad_sq, 0, self.wire.numel() // 2)
         ops._count()
         self.seq += 2
 
