@@ -41,9 +41,11 @@ struct CommPeers {
 };
 
 // All threads of the block call this.  Returns false when a peer did not show up in time.
+// Ordering: the block's stores happen before the CTA barrier, the flag is written after it with a system-scope release by
+// the threads that passed the barrier - release is cumulative, so a peer that acquires the flag sees every store of the
+// block.  (One release per peer instead of a system fence in each of the 512 threads: the fences were the larger part of
+// a small bucket's time.)
 __device__ __forceinline__ bool block_barrier(const CommPeers& pe, int rank, int world, uint32_t seq, int* status, long long limit) {
-  __threadfence_system();
-  __syncthreads();
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();

@@ -189,6 +189,15 @@ std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, co
   TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.dim() == 3 && lse.size(0) == B && lse.size(1) == H &&
                   lse.size(2) == S, "lse must be contiguous fp32 [B,H,S]");
   c10::cuda::CUDAGuard guard(q.device());
+  if (S % 128 != 0) {
+    // The kernel walks whole 128-row tiles.  A ragged sequence is extended with zero rows: causality hides the added keys
+    // from every real query, and an added query (q = 0, dO = 0, O = 0, lse = 0) has P = 1, dP = 0 and row sum 0, hence
+    // dS = 0 and P^T dO = 0: it adds nothing to dK or dV.
+    const int64_t pad = 128 - S % 128;
+    auto rows = [&](const Tensor& t) { return at::constant_pad_nd(t, {0, 0, 0, 0, 0, pad}, 0).contiguous(); };
+    auto [dq_p, dk_p, dv_p] = fa_bwd(rows(d_o), rows(q), rows(k), rows(v), rows(o), at::constant_pad_nd(lse, {0, pad}, 0).contiguous(), causal, prof);
+    return {dq_p.narrow(1, 0, S).contiguous(), dk_p.narrow(1, 0, S).contiguous(), dv_p.narrow(1, 0, S).contiguous()};
+  }
   Tensor dq = torch::empty_like(q), dk = torch::empty_like(k), dv = torch::empty_like(v);
   Tensor acc = torch::empty(q.sizes(), q.options().dtype(at::kFloat));
   Tensor dsum = torch::empty_like(lse), lse2 = torch::empty_like(lse);

@@ -1,12 +1,12 @@
 """Causal GQA attention on CUDA tensors: forward returning (O, ctx) and backward from ctx.
 
 Two implementations: this package's tcgen05 flash-attention kernels (``fa_fwd`` / ``fa_bwd`` in the extension; causal,
-head_dim 64; the backward needs a sequence that is a multiple of 128) and the library path: PyTorch's fused SDPA (flash / cuDNN backend, native GQA),
+head_dim 64, any sequence length: the backward extends a ragged sequence with zero rows up to its 128-row tiles) and the library path: PyTorch's fused SDPA (flash / cuDNN backend, native GQA),
 differentiated through a private autograd tape so that the caller needs no autograd graph of its own.
 ``SEGPT_ATTN_IMPL=native|library|auto``: ``auto`` (default) runs the native kernels wherever they apply - in training the
 tcgen05 forward + backward pair (inside the training step it is within a few percent of the library pair, which needs
 transposed copies of its operands and result), in evaluation and generation the forward - and the library elsewhere
-(head_dim other than 64, decoding against a cache, training sequences that are not a multiple of 128);
+(head_dim other than 64, decoding against a cache);
 ``native`` raises where ``auto`` would fall back because the kernels are missing; ``library`` forces the library pair.
 """
 
@@ -39,8 +39,7 @@ def _native_ok(q: Tensor, k: Tensor, v: Tensor, q_start: int, for_backward: bool
     if for_backward and not ops.has_kernel("fa_bwd"):
         return False  # the library backward needs the library forward's tape
     hd = q.size(-1)
-    seq_ok = (q.size(1) % 128 == 0) if for_backward else True  # the backward kernel needs whole 128-row tiles
-    return (q.dtype == torch.bfloat16 and hd == 64 and q_start == 0 and q.size(1) == k.size(1) and seq_ok
+    return (q.dtype == torch.bfloat16 and hd == 64 and q_start == 0 and q.size(1) == k.size(1)
             and q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
 
 

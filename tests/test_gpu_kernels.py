@@ -200,7 +200,8 @@ def test_native_attention_forward(B, S, H, Hkv):
     close(lse, lse_ref, 2e-2, name="LSE")
 
 
-@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 6, 2), (2, 1024, 3, 1), (1, 2048, 3, 1)])
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 6, 2), (2, 1024, 3, 1), (1, 2048, 3, 1), (2, 200, 4, 2), (1, 77, 2, 1),
+                                       (1, 1300, 2, 2)])
 def test_native_attention_backward(B, S, H, Hkv):
     """dq/dk/dv of the tcgen05 backward kernel against autograd of the fp32 statement of the same attention."""
     from sample_efficient_gpt_b200.ops import gemm as G
