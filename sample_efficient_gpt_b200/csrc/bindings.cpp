@@ -11,6 +11,8 @@
 
 #include "kernels.h"
 
+int* package_status_ptr(const c10::Device& dev);  // gemm_bindings.cpp
+
 namespace {
 
 using torch::Tensor;
@@ -184,6 +186,7 @@ std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, const OptTens
   c10::cuda::CUDAGuard guard(qkv.device());
   auto p = make_post(cos, sin, qgain, a1, a2, vs, B, S, H, Hkv, hd, qknorm);
   p.qkv_stride = qkv.stride(0);
+  p.status = package_status_ptr(qkv.device());
   if (pos.has_value()) {
     TORCH_CHECK(pos->is_cuda() && pos->scalar_type() == at::kInt && pos->numel() == 1, "pos must be a CUDA int32 scalar");
     p.pos = pos->data_ptr<int>();
@@ -222,6 +225,7 @@ std::tuple<Tensor, OptTensor, Tensor, Tensor, Tensor, Tensor> qkv_post_bwd(
     dqkv = torch::empty_strided(qkv.sizes(), qkv.strides(), qkv.options());
   }
   p.qkv_stride = qkv.stride(0);
+  p.status = package_status_ptr(qkv.device());
   OptTensor dv1;
   if (v1.has_value()) {
     if (dv1_acc.has_value()) {  // running sum over blocks, updated in place

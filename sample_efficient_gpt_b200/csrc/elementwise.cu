@@ -3,7 +3,8 @@
 //           da = df * b * (s + a s (1 - s)), db = df * a * s,  s = sigmoid(a)
 //   gate  : g[t,h,:] = 2 sigmoid(z[t,h]) * o[t,h,:]                   (transformer/attention.py:249-255)
 //           do = 2 s dg ;  dz = 2 s (1 - s) sum_d dg * o
-// Pure streaming kernels: 4 elements per thread per access, every tensor touched once.
+// Pure streaming kernels: 4 elements per thread per access, every tensor touched once.  Index divisions run in 32 bits
+// whenever the item count allows (a 64-bit division costs more instructions than the rest of an item).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -15,7 +16,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ u
   const int fv = F / VEC;
   const int64_t total = rows * fv;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / fv;
+    const int64_t r = total <= 0x7fffffff ? (int64_t)((uint32_t)i / (uint32_t)fv) : i / fv;
     const int c = (int)(i - r * fv) * VEC;
     float a[8], b[8], o[8];
     if (VEC == 8) {
@@ -47,7 +48,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const T* __restrict__ d
   const int fv = F / VEC;
   const int64_t total = rows * fv;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / fv;
+    const int64_t r = total <= 0x7fffffff ? (int64_t)((uint32_t)i / (uint32_t)fv) : i / fv;
     const int c = (int)(i - r * fv) * VEC;
     float a[8], b[8], g[8], da[8], db[8];
     if (VEC == 8) {
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ o, 
   const int64_t total = n_heads_total * TPH;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t head = i / TPH;
-    const int64_t tok = head / H;
+    const int64_t tok = total <= 0x7fffffff ? (int64_t)((uint32_t)head / (uint32_t)H) : head / H;
     const float s = 2.f * sigmoidf_(to_f<T>(z[tok * z_stride + (head - tok * H)]));
     float v[8];
     load8<T>(o + i * 8, v);
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dg,
   for (int64_t it = 0; it < rounds; ++it, i += stride) {
     const bool live = i < total;
     const int64_t head = live ? i / TPH : 0;
-    const int64_t tok = head / H;
+    const int64_t tok = total <= 0x7fffffff ? (int64_t)((uint32_t)head / (uint32_t)H) : head / H;
     const int h = (int)(head - tok * H);
     float sg = 0.f, dot = 0.f;
     if (live) {

@@ -134,6 +134,21 @@ Tensor gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, st
   return d;
 }
 
+// (u, f) = (x w^T, silu(u[:, :F]) * u[:, F:]) in one launch; w = [F gate rows | F up rows].
+std::tuple<Tensor, Tensor> gemm_swiglu(const Tensor& x, const Tensor& w) {
+  check_operand(x, "x");
+  check_operand(w, "w");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1) && w.size(0) % 256 == 0, "x [M, K], w [2F, K] with F a multiple of 128");
+  const int M = (int)x.size(0), K = (int)x.size(1), F = (int)(w.size(0) / 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor u = torch::empty({M, 2 * F}, x.options()), f = torch::empty({M, F}, x.options());
+  auto& st = device_state(x.device());
+  const int rc = seg::gemm_swiglu_pair(x.data_ptr(), w.data_ptr(), u.data_ptr(), f.data_ptr(), M, F, K, x.stride(0), w.stride(0), u.stride(0),
+                                       f.stride(0), st.status.data_ptr<int>(), st.sm_count, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "gemm_swiglu launch failed with code ", rc);
+  return {u, f};
+}
+
 // Host read of the status word (synchronises): 0 = every wait completed.
 int64_t gemm_status(int64_t device_index) {
   auto& st = device_state(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
@@ -219,6 +234,7 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("region_rows") = 0, pybind11::arg("route_ptrs") = std::vector<int64_t>(), pybind11::arg("route_rows") = 0,
         pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0,
         pybind11::arg("impl") = 1, pybind11::arg("split_k") = true, pybind11::arg("wait_limit") = 0);
+  m.def("gemm_swiglu", &gemm_swiglu, pybind11::arg("x"), pybind11::arg("w"));
   m.def("fa_fwd", &fa_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
   m.def("fa_bwd", &fa_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("lse"),
         pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);

@@ -42,11 +42,11 @@ namespace seg {
 using namespace sm100;
 
 constexpr int kPairThreads = 320;
-constexpr int kEpiGeneric = 0, kEpiTma = 1, kEpiTmaC = 2;
+constexpr int kEpiGeneric = 0, kEpiTma = 1, kEpiTmaC = 2, kEpiSwiglu = 3;
 // The addend variant keeps two 4 KB tiles per epilogue warp (each receives a box of C, is overwritten with the result and
-// stored), paid for with one stage of the ring.
-__host__ __device__ constexpr int pair_stages(int epi) { return epi == kEpiTmaC ? 5 : 6; }
-__host__ __device__ constexpr int pair_staging_bytes(int epi) { return epi == kEpiTmaC ? 8 * 8192 : 8 * 4096; }
+// stored), paid for with one stage of the ring; so does the SwiGLU variant (gate and up columns leave side by side).
+__host__ __device__ constexpr int pair_stages(int epi) { return (epi == kEpiTmaC || epi == kEpiSwiglu) ? 5 : 6; }
+__host__ __device__ constexpr int pair_staging_bytes(int epi) { return (epi == kEpiTmaC || epi == kEpiSwiglu) ? 8 * 8192 : 8 * 4096; }
 constexpr int kPairABytes = 128 * kPairK * 2;
 constexpr int kPairBBytes = 128 * kPairK * 2;
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
@@ -124,7 +124,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
     if (EPI != kEpiGeneric) prefetch_tensormap(&map_d);
-    if (EPI == kEpiTmaC) prefetch_tensormap(&map_c);
+    if (EPI == kEpiTmaC || EPI == kEpiSwiglu) prefetch_tensormap(&map_c);
   }
   if (warp == 0) {
     __syncwarp();
@@ -147,7 +147,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       for (int item = pair; item < sch.n_items && ok; item += n_pairs) {
         const PairItem tl = pair_item(sch, item);
         const int a_row0 = tl.m * kPairM + (int)rank * 128;
-        const int b_row0 = tl.n * kPairN + (int)rank * (tl.nt >> 1);
+        // SwiGLU variant: tile n covers hidden units [128 n, 128 n + 128); the leader's half of B holds their gate rows,
+        // the peer's half their up rows (F rows further down), so accumulator column c + 128 is the partner of column c
+        const int b_row0 = EPI == kEpiSwiglu ? (int)rank * p.swiglu_f + tl.n * 128 : tl.n * kPairN + (int)rank * (tl.nt >> 1);
         const int b_boxes = p.b_box_rows == 64 ? ((tl.nt >> 1) + 63) >> 6 : 128 / p.b_box_rows;  // boxes of this CTA's B half
         if (!A_MN && p.wait_flags != nullptr && a_row0 < p.M) {
           const int r0 = a_row0 / p.region_rows;
@@ -356,6 +358,57 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               }
             }
             if (!ok) break;
+          }
+        } else if (EPI == kEpiSwiglu) {
+          if (row0 < p.M) {
+            // This warp: gate columns [64 half, 64 half + 64) of the tile and their up partners 128 columns further.  Both
+            // leave as bf16 (tile 0 -> gate block of D, tile 1 -> up block of D); f = silu(gate) * up is formed from the
+            // rounded values, exactly what a separate pass over D would compute, and follows through tile 0.
+            const int hcol = tl.n * 128 + half * 64;
+            uint32_t fpk[32];
+            if (lane == 0) bulk_wait_group_read0();  // the previous item's stores have left both tiles
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              uint32_t g[32], u[32];
+              tmem_ld_32x32(tmem_acc + half * 64 + c * 32, g);
+              tmem_ld_32x32(tmem_acc + 128 + half * 64 + c * 32, u);
+              tmem_ld_wait_regs(g);
+              tmem_ld_wait_regs(u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t gw[4], uw[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __nv_bfloat162 gh = __floats2bfloat162_rn(__uint_as_float(g[8 * j + 2 * e]), __uint_as_float(g[8 * j + 2 * e + 1]));
+                  const __nv_bfloat162 uh = __floats2bfloat162_rn(__uint_as_float(u[8 * j + 2 * e]), __uint_as_float(u[8 * j + 2 * e + 1]));
+                  gw[e] = *reinterpret_cast<const uint32_t*>(&gh);
+                  uw[e] = *reinterpret_cast<const uint32_t*>(&uh);
+                  const float2 a = __bfloat1622float2(gh), b = __bfloat1622float2(uh);
+                  const __nv_bfloat162 fh = __floats2bfloat162_rn(a.x * sigmoidf_(a.x) * b.x, a.y * sigmoidf_(a.y) * b.y);
+                  fpk[c * 16 + j * 4 + e] = *reinterpret_cast<const uint32_t*>(&fh);
+                }
+                row_slots[(c * 4 + j) ^ (lane & 7)] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+                reinterpret_cast<uint4*>(stage_raw + 4096 + lane * 128)[(c * 4 + j) ^ (lane & 7)] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+              }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&map_d, stage_u32, hcol, row0, tl.b);
+              tma_store_3d(&map_d, stage_u32 + 4096, p.swiglu_f + hcol, row0, tl.b);
+              bulk_commit_group();
+              bulk_wait_group_read0();
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) row_slots[j ^ (lane & 7)] = make_uint4(fpk[4 * j], fpk[4 * j + 1], fpk[4 * j + 2], fpk[4 * j + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&map_c, stage_u32, hcol, row0, tl.b);
+              bulk_commit_group();
+            }
           }
         } else if (EPI == kEpiTma) {
           if (row0 < p.M) {
@@ -620,6 +673,7 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   p.route_extent = n_route > 0 ? route_base + (int64_t)(batch - 1) * route_batch_stride + (int64_t)(route_rows - 1) * ldd + N : 0;
   if (gemm_debug_extent_cap_value() > 0 && p.d_extent > gemm_debug_extent_cap_value()) p.d_extent = gemm_debug_extent_cap_value();
   p.reduce = 0;
+  p.swiglu_f = 0;
   p.ws = reinterpret_cast<uint4*>(workspace);
   p.ws_flags = ws_flags;
   p.b_box_rows = b_box_env;
@@ -663,6 +717,48 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   if (a_mn_major && b_mn_major) return SEG_PAIR(true, true);
   return SEG_PAIR(true, false);
 #undef SEG_PAIR
+}
+
+// u[:, :F] | u[:, F:] = x W^T (W = [gate rows | up rows], [2F, K]) and f = silu(u[:, :F]) * u[:, F:] in one launch.
+int gemm_swiglu_pair(const void* X, const void* W, void* U, void* Fout, int M, int F, int K, int64_t ldx, int64_t ldw, int64_t ldu,
+                     int64_t ldf, int* status, int sm_count, cudaStream_t st, long long wait_limit) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if (F % 128 != 0 || K % 8 != 0) return -7;
+  for (const void* ptr : {X, W, (const void*)U, (const void*)Fout})
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return -8;
+  if (ldx % 8 != 0 || ldw % 8 != 0 || ldu % 8 != 0 || ldf % 8 != 0) return -8;
+  CUtensorMap ma, mb, md, mc;
+  int r = make_tensor_map_3d(&ma, X, false, (uint64_t)K, (uint64_t)M, 1, (uint64_t)ldx, (uint64_t)M * ldx, 64, 128);
+  if (r != 0) return 100 + r;
+  r = make_tensor_map_3d(&mb, W, false, (uint64_t)K, (uint64_t)2 * F, 1, (uint64_t)ldw, (uint64_t)2 * F * ldw, 64, 64);
+  if (r != 0) return 200 + r;
+  r = make_tensor_map_3d(&md, U, false, (uint64_t)2 * F, (uint64_t)M, 1, (uint64_t)ldu, (uint64_t)M * ldu, 64, 32);
+  if (r != 0) return 300 + r;
+  r = make_tensor_map_3d(&mc, Fout, false, (uint64_t)F, (uint64_t)M, 1, (uint64_t)ldf, (uint64_t)M * ldf, 64, 32);
+  if (r != 0) return 400 + r;
+  GemmParams p;
+  p.M = M; p.N = 2 * F; p.K = K; p.batch = 1;
+  p.alpha = 1.f; p.beta = 0.f;
+  p.C = nullptr; p.D = U; p.ldd = ldu; p.batch_stride_d = (int64_t)M * ldu;
+  p.status = status;
+  p.symmetric = 0;
+  p.n_extra = 0;
+  for (int i = 0; i < 7; ++i) p.D_extra[i] = nullptr;
+  p.wait_flags = nullptr; p.wait_seq = 0; p.region_rows = 1;
+  p.route_rows = 0; p.route_batch_stride = 0; p.route_base = 0;
+  for (int i = 0; i < 8; ++i) p.D_route[i] = nullptr;
+  p.wait_limit = wait_limit;
+  p.d_extent = (int64_t)(M - 1) * ldu + 2 * F;
+  p.route_extent = 0;
+  p.reduce = 0;
+  p.ws = nullptr; p.ws_flags = nullptr;
+  p.b_box_rows = 64;
+  p.epi_backoff_ns = 0;
+  p.swiglu_f = F;
+  pair_choose_split(M, 2 * F, K, 1, 0, sm_count / 2, false, p.n_static, p.splits);  // whole tiles only
+  const PairSched sched = make_pair_sched(M, 2 * F, K, 1, 0, p.n_static, p.splits);
+  const int pairs = sched.n_items < sm_count / 2 ? sched.n_items : sm_count / 2;
+  return launch_pair<false, false, __nv_bfloat16, kEpiSwiglu>(ma, mb, md, mc, p, pairs, st);
 }
 
 }  // namespace seg

@@ -43,6 +43,7 @@ struct GemmParams {
   int epi_backoff_ns;    // sleep between the epilogue warps' polls of the accumulator barrier (0: none)
   uint4* ws;             // workspace slots for the parts of tiles that are cut along the contraction
   uint32_t* ws_flags;    // one word per (slot, rank, epilogue warp), zero between launches
+  int swiglu_f;          // SwiGLU epilogue: hidden width F (B holds F gate rows, then F up rows); 0 otherwise
 };
 
 // Gives up after half the limit of the barrier waits: the roles that wait (through the ring) for what this producer loads

@@ -37,7 +37,13 @@ struct QkvPostParams {
   int64_t qkv_stride;   // row stride (elements) of qkv and dqkv: (H + 2 Hkv) * hd, or more when the projection is wider
   const int* pos;       // optional device scalar added to every token's position (decode: S == 1, position = cache length)
   bool dv1_accumulate = false;  // backward: add the value-residual gradient to dv1_out instead of overwriting it
+  int* status = nullptr;        // device word for the bounded waits of the shared-memory variant (nullptr: that variant is not used)
 };
+// Shared-memory variants (qkv_post_tile.cu; bf16, head_dim 64, S a multiple of the token tile).  They return false / 0 when the
+// call is not theirs and nothing was launched.
+bool qkv_post_fwd_tile(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st);
+int qkv_post_bwd_tile(const void* dq, const void* dk, const void* dv, const void* qkv, const void* v1, void* dqkv, float* dv1_out,
+                      float* partial, int partial_rows, const QkvPostParams& p, bool bf16, cudaStream_t st);
 void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st);
 // dv_is_f32: dv is fp32 (first block, after the v1 gradients were added); dv1_out fp32 [T,Hkv,hd] or nullptr;
 // scalars: fp32[4] = {dqgain, dalpha1, dalpha2, dvscale}; partial: scratch fp32 [qkv_post_bwd_grid(...), 4].
@@ -139,6 +145,11 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
 // impl: 1 = CTA-pair kernel (cta_group::2, 256-row tiles), 0 = one CTA per 128-row tile.  workspace / ws_flags / split_k:
 // the pair kernel's buffers for tiles cut along the contraction (sizes: gemm_pair_workspace_bytes / gemm_pair_flag_words) and
 // the switch for cutting.
+// Up projection of a SwiGLU feed-forward with the activation in the epilogue (CTA-pair kernel): U [M, 2F] = X W^T for
+// W = [F gate rows | F up rows] and Fout [M, F] = silu(U[:, :F]) * U[:, F:], formed from the bf16-rounded U.  bf16, row-major,
+// F a multiple of 128, K a multiple of 8, 16-byte aligned bases and row strides.
+int gemm_swiglu_pair(const void* X, const void* W, void* U, void* Fout, int M, int F, int K, int64_t ldx, int64_t ldw, int64_t ldu,
+                     int64_t ldf, int* status, int sm_count, cudaStream_t st, long long wait_limit = 0);
 // Debug build only (no effect otherwise): every GEMM launched afterwards pretends that its output holds at most `elements`
 // elements (0: off), so that a test can watch the index checks refuse in-range stores - and only those - without any fault.
 void gemm_debug_extent_cap(int64_t elements);

@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(256) muon_apply_kernel(const __nv_bfloat16* __
   float* p = params[mat];
   __nv_bfloat16* sh = shadows ? shadows[mat] : nullptr;
   for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < numel; i += (int64_t)gridDim.x * blockDim.x * 4) {
-    const int row = (int)(i / C), col = (int)(i - (int64_t)row * C);
+    const int row = numel <= 0x7fffffff ? (int)((uint32_t)i / (uint32_t)C) : (int)(i / C), col = (int)(i - (int64_t)row * C);
     const float4 vv = load4<__nv_bfloat16>(vp + i);
     float4 pv = *reinterpret_cast<float4*>(p + i);
     float m0, m1, m2, m3;

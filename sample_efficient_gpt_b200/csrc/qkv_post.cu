@@ -3,8 +3,8 @@
 //   q and k (eps 1e-6, q times a learnable scalar), value residual v' = s*c*(a1*v + a2*v1), c = rsqrt(a1^2+a2^2+1e-8).
 // Reference math: transformer/rope.py:36-56, transformer/attention.py:51-63 and 222-228.
 // Layouts: qkv [T, (H+2Hkv)*hd]; q [T,H,hd]; k, v, v1 [T,Hkv,hd] (token-major, what the attention kernel reads).
-// Work item = 8 rotary pairs of one (token, head slot): a thread loads x[8j..8j+8) and x[hd/2+8j..] with 16-byte
-// accesses, hd/16 neighbouring lanes share a head and combine their sums of squares with shuffles.  The backward
+// Work item = 8 rotary pairs of up to six head slots of one token: a thread loads x[8j..8j+8) and x[hd/2+8j..] of each
+// with 16-byte accesses, hd/16 neighbouring lanes share a head and combine their sums of squares with shuffles.  The backward
 // recomputes rotation and norms from qkv (the forward saves nothing extra) and reduces the four scalar gradients
 // deterministically: per-CTA partials, then a single-CTA finalize.
 #include "common.cuh"
@@ -27,14 +27,50 @@ __device__ __forceinline__ float group_sum(float v) {
   return v;
 }
 
+// Decomposition of a work-item index: item = ((token * ng) + group) * LPH + sub.  A thread serves head slots group,
+// group + ng, group + 2 ng, ... of its token, so the rotation table row (64 bytes per thread) and the index arithmetic are
+// paid once per kSlotsPerItem heads instead of once per head: that, not DRAM, bounded these kernels.
+constexpr int kSlotsPerItem = 6;
+constexpr int kSlotBatch = 3;     // forward: slots whose loads are issued together before any of them is used
+constexpr int kSlotBatchBwd = 2;  // backward (twice the registers per slot)
+__host__ __device__ inline int qkv_post_groups(int nslots) { return (nslots + kSlotsPerItem - 1) / kSlotsPerItem; }
+
+struct PostItem {
+  int sub, grp, s;
+  int64_t t;
+};
+template <int LPH>
+__device__ __forceinline__ PostItem post_item(int64_t idx, bool live, int64_t total, int ng, int S, int pos_off) {
+  PostItem it;
+  if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values are slow
+    const uint32_t i32 = live ? (uint32_t)idx : 0u;
+    it.sub = (int)(i32 % LPH);
+    const uint32_t sg = i32 / LPH;
+    it.grp = (int)(sg % (uint32_t)ng);
+    const uint32_t t32 = sg / (uint32_t)ng;
+    it.s = (int)(t32 % (uint32_t)S) + pos_off;
+    it.t = t32;
+  } else {
+    const int64_t i64 = live ? idx : 0;
+    it.sub = (int)(i64 % LPH);
+    const int64_t sg = i64 / LPH;
+    it.grp = (int)(sg % ng);
+    it.t = sg / ng;
+    it.s = (int)(it.t % S) + pos_off;
+  }
+  return it;
+}
+
 template <typename T, int HD>
-__global__ void __launch_bounds__(kPostThreads, 4) qkv_post_fwd_kernel(const T* __restrict__ qkv, const T* __restrict__ v1,
+__global__ void __launch_bounds__(kPostThreads, 2) qkv_post_fwd_kernel(const T* __restrict__ qkv, const T* __restrict__ v1,
                                                                   T* __restrict__ q, T* __restrict__ k, T* __restrict__ v,
                                                                   QkvPostParams p) {
   constexpr int HALF = HD / 2;
   constexpr int LPH = HALF / 8;  // lanes per head
-  const int nslots = p.H + 2 * p.Hkv;
-  const int64_t total = (int64_t)p.B * p.S * nslots * LPH;
+  const int nslots = p.H + 2 * p.Hkv, nrot = p.H + p.Hkv;
+  const int ng = qkv_post_groups(nslots);
+  const int iters = (nslots + ng - 1) / ng;
+  const int64_t total = (int64_t)p.B * p.S * ng * LPH;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t rounds = (total + stride - 1) / stride;
   const float a1 = *p.alpha1, a2 = *p.alpha2, vs = *p.vscale;
@@ -42,84 +78,74 @@ __global__ void __launch_bounds__(kPostThreads, 4) qkv_post_fwd_kernel(const T* 
   const float qg = *p.qgain;
   const int pos_off = p.pos != nullptr ? *p.pos : 0;
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  for (int64_t it = 0; it < rounds; ++it, idx += stride) {
-    const bool live = idx < total;
-    int sub, slot, s;
-    int64_t t;
-    if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values dominate otherwise
-      const uint32_t i32 = live ? (uint32_t)idx : 0u;
-      sub = (int)(i32 % LPH);
-      const uint32_t sg = i32 / LPH;
-      slot = (int)(sg % (uint32_t)nslots);
-      const uint32_t t32 = sg / (uint32_t)nslots;
-      s = (int)(t32 % (uint32_t)p.S) + pos_off;
-      t = t32;
-    } else {
-      sub = (int)(idx % LPH);
-      const int64_t sg = live ? idx / LPH : 0;
-      slot = (int)(sg % nslots);
-      t = sg / nslots;
-      s = (int)(t % p.S) + pos_off;
-    }
-    float x1[8], x2[8];
-    if (live) {
-      const T* src = qkv + (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
-      load8<T>(src, x1);
-      load8<T>(src + HALF, x2);
-    }
-    if (slot < p.H + p.Hkv) {
-      float ss = 0.f;
-      if (live) {
-        float cs[8], sn[8];
-        load8<float>(p.cos + (size_t)s * HALF + sub * 8, cs);
-        load8<float>(p.sin + (size_t)s * HALF + sub * 8, sn);
+  for (int64_t round = 0; round < rounds; ++round, idx += stride) {
+    const bool live = idx < total;  // the LPH lanes of a head are live together (total and stride are multiples of LPH)
+    if (!live) continue;
+    const PostItem it = post_item<LPH>(idx, live, total, ng, p.S, pos_off);
+    float cs[8], sn[8];
+    load8<float>(p.cos + (size_t)it.s * HALF + it.sub * 8, cs);
+    load8<float>(p.sin + (size_t)it.s * HALF + it.sub * 8, sn);
+    const T* row = qkv + (size_t)it.t * p.qkv_stride + it.sub * 8;
+    for (int i0 = 0; i0 < iters; i0 += kSlotBatch) {
+      float x1[kSlotBatch][8], x2[kSlotBatch][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float r1 = x1[j] * cs[j] - x2[j] * sn[j], r2 = x1[j] * sn[j] + x2[j] * cs[j];
-          x1[j] = r1;
-          x2[j] = r2;
-          ss += r1 * r1 + r2 * r2;
+      for (int b = 0; b < kSlotBatch; ++b) {
+        const int slot = it.grp + (i0 + b) * ng;
+        if (i0 + b < iters && slot < nslots) {
+          load8<T>(row + (size_t)slot * HD, x1[b]);
+          load8<T>(row + (size_t)slot * HD + HALF, x2[b]);
         }
       }
-      float mul = 1.f;
-      if (p.qknorm) {
-        ss = group_sum<LPH>(ss);
-        mul = rsqrtf(ss / HD + kQkEps);
-        if (slot < p.H) mul *= qg;
-      }
-      if (live) {
-        T* dst = (slot < p.H) ? q + ((size_t)t * p.H + slot) * HD : k + ((size_t)t * p.Hkv + (slot - p.H)) * HD;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          x1[j] *= mul;
-          x2[j] *= mul;
-        }
-        store8<T>(dst + sub * 8, x1);
-        store8<T>(dst + HALF + sub * 8, x2);
-      }
-    } else {
-      if (live) {
-        const size_t off = ((size_t)t * p.Hkv + (slot - p.H - p.Hkv)) * HD + sub * 8;
-        float w1[8], w2[8];
-        if (v1 != nullptr) {
-          load8<T>(v1 + off, w1);
-          load8<T>(v1 + off + HALF, w2);
-        }
+      for (int b = 0; b < kSlotBatch; ++b) {
+        const int slot = it.grp + (i0 + b) * ng;
+        if (i0 + b >= iters || slot >= nslots) continue;
+        if (slot < nrot) {
+          float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float u1 = v1 ? w1[j] : x1[j], u2 = v1 ? w2[j] : x2[j];
-          x1[j] = vs * c * (a1 * x1[j] + a2 * u1);
-          x2[j] = vs * c * (a1 * x2[j] + a2 * u2);
+          for (int j = 0; j < 8; ++j) {
+            const float r1 = x1[b][j] * cs[j] - x2[b][j] * sn[j], r2 = x1[b][j] * sn[j] + x2[b][j] * cs[j];
+            x1[b][j] = r1;
+            x2[b][j] = r2;
+            ss += r1 * r1 + r2 * r2;
+          }
+          float mul = 1.f;
+          if (p.qknorm) {
+            ss = group_sum<LPH>(ss);
+            mul = rsqrtf(ss / HD + kQkEps);
+            if (slot < p.H) mul *= qg;
+          }
+          T* dst = (slot < p.H) ? q + ((size_t)it.t * p.H + slot) * HD : k + ((size_t)it.t * p.Hkv + (slot - p.H)) * HD;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            x1[b][j] *= mul;
+            x2[b][j] *= mul;
+          }
+          store8<T>(dst + it.sub * 8, x1[b]);
+          store8<T>(dst + HALF + it.sub * 8, x2[b]);
+        } else {
+          const size_t off = ((size_t)it.t * p.Hkv + (slot - nrot)) * HD + it.sub * 8;
+          float w1[8], w2[8];
+          if (v1 != nullptr) {
+            load8<T>(v1 + off, w1);
+            load8<T>(v1 + off + HALF, w2);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float u1 = v1 ? w1[j] : x1[b][j], u2 = v1 ? w2[j] : x2[b][j];
+            x1[b][j] = vs * c * (a1 * x1[b][j] + a2 * u1);
+            x2[b][j] = vs * c * (a1 * x2[b][j] + a2 * u2);
+          }
+          store8<T>(v + off, x1[b]);
+          store8<T>(v + off + HALF, x2[b]);
         }
-        store8<T>(v + off, x1);
-        store8<T>(v + off + HALF, x2);
       }
     }
   }
 }
 
 template <typename T, typename DVT, int HD>
-__global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __restrict__ dq, const T* __restrict__ dk,
+__global__ void __launch_bounds__(kPostThreads, 2) qkv_post_bwd_kernel(const T* __restrict__ dq, const T* __restrict__ dk,
                                                                   const DVT* __restrict__ dv, const T* __restrict__ qkv,
                                                                   const T* __restrict__ v1, T* __restrict__ dqkv,
                                                                   float* __restrict__ dv1_out, float* __restrict__ partial,
@@ -127,122 +153,121 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_bwd_kernel(const T* __r
   constexpr int HALF = HD / 2;
   constexpr int LPH = HALF / 8;
   __shared__ float red[32];
-  const int nslots = p.H + 2 * p.Hkv;
-  const int64_t total = (int64_t)p.B * p.S * nslots * LPH;
+  const int nslots = p.H + 2 * p.Hkv, nrot = p.H + p.Hkv;
+  const int ng = qkv_post_groups(nslots);
+  const int iters = (nslots + ng - 1) / ng;
+  const int64_t total = (int64_t)p.B * p.S * ng * LPH;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t rounds = (total + stride - 1) / stride;
   const float a1 = *p.alpha1, a2 = *p.alpha2, vs = *p.vscale;
   const float c = rsqrtf(a1 * a1 + a2 * a2 + kMixEps);
   const float qg = *p.qgain;
   const int pos_off = p.pos != nullptr ? *p.pos : 0;
+  const float kself = vs * c * (v1 ? a1 : (a1 + a2));
+  const float kother = vs * c * a2;
   float acc_qg = 0.f, acc_dvU = 0.f, acc_dvv = 0.f, acc_dvv1 = 0.f;
   int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  for (int64_t it = 0; it < rounds; ++it, idx += stride) {
+  for (int64_t round = 0; round < rounds; ++round, idx += stride) {
     const bool live = idx < total;
-    int sub, slot, s;
-    int64_t t;
-    if (total <= 0x7fffffffLL) {  // 32-bit index arithmetic (uniform branch): 64-bit divisions by run-time values dominate otherwise
-      const uint32_t i32 = live ? (uint32_t)idx : 0u;
-      sub = (int)(i32 % LPH);
-      const uint32_t sg = i32 / LPH;
-      slot = (int)(sg % (uint32_t)nslots);
-      const uint32_t t32 = sg / (uint32_t)nslots;
-      s = (int)(t32 % (uint32_t)p.S) + pos_off;
-      t = t32;
-    } else {
-      sub = (int)(idx % LPH);
-      const int64_t sg = live ? idx / LPH : 0;
-      slot = (int)(sg % nslots);
-      t = sg / nslots;
-      s = (int)(t % p.S) + pos_off;
-    }
-    const size_t row_off = (size_t)t * p.qkv_stride + (size_t)slot * HD + sub * 8;
-    float x1[8], x2[8];
-    if (live) {
-      load8<T>(qkv + row_off, x1);
-      load8<T>(qkv + row_off + HALF, x2);
-    }
-    if (slot < p.H + p.Hkv) {
-      const bool is_q = slot < p.H;
-      float g1[8], g2[8], cs[8], sn[8];
-      float ss = 0.f, dot = 0.f;
-      if (live) {
-        const T* g = is_q ? dq + ((size_t)t * p.H + slot) * HD + sub * 8 : dk + ((size_t)t * p.Hkv + (slot - p.H)) * HD + sub * 8;
-        load8<T>(g, g1);
-        load8<T>(g + HALF, g2);
-        load8<float>(p.cos + (size_t)s * HALF + sub * 8, cs);
-        load8<float>(p.sin + (size_t)s * HALF + sub * 8, sn);
+    if (!live) continue;
+    const PostItem it = post_item<LPH>(idx, live, total, ng, p.S, pos_off);
+    float cs[8], sn[8];
+    load8<float>(p.cos + (size_t)it.s * HALF + it.sub * 8, cs);
+    load8<float>(p.sin + (size_t)it.s * HALF + it.sub * 8, sn);
+    const size_t row0 = (size_t)it.t * p.qkv_stride + it.sub * 8;
+    for (int i0 = 0; i0 < iters; i0 += kSlotBatchBwd) {
+      float x1[kSlotBatchBwd][8], x2[kSlotBatchBwd][8], g1[kSlotBatchBwd][8], g2[kSlotBatchBwd][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float r1 = x1[j] * cs[j] - x2[j] * sn[j], r2 = x1[j] * sn[j] + x2[j] * cs[j];
-          x1[j] = r1;
-          x2[j] = r2;
-          ss += r1 * r1 + r2 * r2;
-          dot += r1 * g1[j] + r2 * g2[j];
+      for (int b = 0; b < kSlotBatchBwd; ++b) {
+        const int slot = it.grp + (i0 + b) * ng;
+        if (i0 + b < iters && slot < nslots) {
+          load8<T>(qkv + row0 + (size_t)slot * HD, x1[b]);
+          load8<T>(qkv + row0 + (size_t)slot * HD + HALF, x2[b]);
+          if (slot < nrot) {
+            const T* g = slot < p.H ? dq + ((size_t)it.t * p.H + slot) * HD + it.sub * 8
+                                    : dk + ((size_t)it.t * p.Hkv + (slot - p.H)) * HD + it.sub * 8;
+            load8<T>(g, g1[b]);
+            load8<T>(g + HALF, g2[b]);
+          } else {
+            const size_t off = ((size_t)it.t * p.Hkv + (slot - nrot)) * HD + it.sub * 8;
+            load8<DVT>(dv + off, g1[b]);
+            load8<DVT>(dv + off + HALF, g2[b]);
+          }
         }
       }
-      if (p.qknorm) {
-        ss = group_sum<LPH>(ss);
-        dot = group_sum<LPH>(dot);
-        const float r = rsqrtf(ss / HD + kQkEps);
-        const float gamma = is_q ? qg : 1.f;
-        if (live && is_q && sub == 0) acc_qg += r * dot;
-        const float ka = gamma * r, kb = gamma * r * r * r * dot / HD;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          g1[j] = ka * g1[j] - kb * x1[j];
-          g2[j] = ka * g2[j] - kb * x2[j];
-        }
-      }
-      if (live) {
-        float o1[8], o2[8];
+      for (int b = 0; b < kSlotBatchBwd; ++b) {
+        const int slot = it.grp + (i0 + b) * ng;
+        if (i0 + b >= iters || slot >= nslots) continue;
+        const size_t row_off = row0 + (size_t)slot * HD;
+        if (slot < nrot) {
+          const bool is_q = slot < p.H;
+          float ss = 0.f, dot = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {  // transpose of the rotation
-          o1[j] = g1[j] * cs[j] + g2[j] * sn[j];
-          o2[j] = -g1[j] * sn[j] + g2[j] * cs[j];
-        }
-        store8<T>(dqkv + row_off, o1);
-        store8<T>(dqkv + row_off + HALF, o2);
-      }
-    } else {
-      if (live) {
-        const size_t off = ((size_t)t * p.Hkv + (slot - p.H - p.Hkv)) * HD + sub * 8;
-        const float kself = vs * c * (v1 ? a1 : (a1 + a2));
-        const float kother = vs * c * a2;
-        float d1[8], d2[8], w1[8], w2[8];
-        load8<DVT>(dv + off, d1);
-        load8<DVT>(dv + off + HALF, d2);
-        if (v1 != nullptr) {
-          load8<T>(v1 + off, w1);
-          load8<T>(v1 + off + HALF, w2);
-        }
-        float o1[8], o2[8], e1[8], e2[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float u1 = v1 ? w1[j] : x1[j], u2 = v1 ? w2[j] : x2[j];
-          acc_dvU += d1[j] * (a1 * x1[j] + a2 * u1) + d2[j] * (a1 * x2[j] + a2 * u2);
-          acc_dvv += d1[j] * x1[j] + d2[j] * x2[j];
-          acc_dvv1 += d1[j] * u1 + d2[j] * u2;
-          o1[j] = kself * d1[j];
-          o2[j] = kself * d2[j];
-          e1[j] = kother * d1[j];
-          e2[j] = kother * d2[j];
-        }
-        store8<T>(dqkv + row_off, o1);
-        store8<T>(dqkv + row_off + HALF, o2);
-        if (dv1_out != nullptr) {
-          if (p.dv1_accumulate) {  // the gradient of the first block's values gathers over all later blocks
-            float b1[8], b2[8];
-            load8<float>(dv1_out + off, b1);
-            load8<float>(dv1_out + off + HALF, b2);
+          for (int j = 0; j < 8; ++j) {
+            const float r1 = x1[b][j] * cs[j] - x2[b][j] * sn[j], r2 = x1[b][j] * sn[j] + x2[b][j] * cs[j];
+            x1[b][j] = r1;
+            x2[b][j] = r2;
+            ss += r1 * r1 + r2 * r2;
+            dot += r1 * g1[b][j] + r2 * g2[b][j];
+          }
+          if (p.qknorm) {
+            ss = group_sum<LPH>(ss);
+            dot = group_sum<LPH>(dot);
+            const float r = rsqrtf(ss / HD + kQkEps);
+            const float gamma = is_q ? qg : 1.f;
+            if (is_q && it.sub == 0) acc_qg += r * dot;
+            const float ka = gamma * r, kb = gamma * r * r * r * dot / HD;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              e1[j] += b1[j];
-              e2[j] += b2[j];
+              g1[b][j] = ka * g1[b][j] - kb * x1[b][j];
+              g2[b][j] = ka * g2[b][j] - kb * x2[b][j];
             }
           }
-          store8<float>(dv1_out + off, e1);
-          store8<float>(dv1_out + off + HALF, e2);
+          float o1[8], o2[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {  // transpose of the rotation
+            o1[j] = g1[b][j] * cs[j] + g2[b][j] * sn[j];
+            o2[j] = -g1[b][j] * sn[j] + g2[b][j] * cs[j];
+          }
+          store8<T>(dqkv + row_off, o1);
+          store8<T>(dqkv + row_off + HALF, o2);
+        } else {
+          const size_t off = ((size_t)it.t * p.Hkv + (slot - nrot)) * HD + it.sub * 8;
+          float w1[8], w2[8];
+          if (v1 != nullptr) {
+            load8<T>(v1 + off, w1);
+            load8<T>(v1 + off + HALF, w2);
+          }
+          float o1[8], o2[8], e1[8], e2[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float d1 = g1[b][j], d2 = g2[b][j];
+            const float u1 = v1 ? w1[j] : x1[b][j], u2 = v1 ? w2[j] : x2[b][j];
+            acc_dvU += d1 * (a1 * x1[b][j] + a2 * u1) + d2 * (a1 * x2[b][j] + a2 * u2);
+            acc_dvv += d1 * x1[b][j] + d2 * x2[b][j];
+            acc_dvv1 += d1 * u1 + d2 * u2;
+            o1[j] = kself * d1;
+            o2[j] = kself * d2;
+            e1[j] = kother * d1;
+            e2[j] = kother * d2;
+          }
+          store8<T>(dqkv + row_off, o1);
+          store8<T>(dqkv + row_off + HALF, o2);
+          if (dv1_out != nullptr) {
+            if (p.dv1_accumulate) {  // the gradient of the first block's values gathers over all later blocks
+              float b1[8], b2[8];
+              load8<float>(dv1_out + off, b1);
+              load8<float>(dv1_out + off + HALF, b2);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                e1[j] += b1[j];
+                e2[j] += b2[j];
+              }
+            }
+            store8<float>(dv1_out + off, e1);
+            store8<float>(dv1_out + off + HALF, e2);
+          }
         }
       }
     }
@@ -280,12 +305,13 @@ __global__ void __launch_bounds__(256) qkv_post_finalize(const float* __restrict
 }
 
 int qkv_post_bwd_grid(int64_t T, int nslots, int hd) {
-  const int64_t items = T * nslots * (hd / 16);
+  const int64_t items = T * qkv_post_groups(nslots) * (hd / 16);
   int64_t g = (items + kPostThreads - 1) / kPostThreads;
   return (int)(g < kQkvPostMaxGrid ? (g > 0 ? g : 1) : kQkvPostMaxGrid);
 }
 
 void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, const QkvPostParams& p, bool bf16, cudaStream_t st) {
+  if (qkv_post_fwd_tile(qkv, v1, q, k, v, p, bf16, st)) return;
   const int grid = qkv_post_bwd_grid((int64_t)p.B * p.S, p.H + 2 * p.Hkv, p.hd);
 #define SEG_POST(TY, HD) qkv_post_fwd_kernel<TY, HD><<<grid, kPostThreads, 0, st>>>((const TY*)qkv, (const TY*)v1, (TY*)q, (TY*)k, (TY*)v, p)
   if (bf16) { if (p.hd == 64) SEG_POST(__nv_bfloat16, 64); else if (p.hd == 128) SEG_POST(__nv_bfloat16, 128); else SEG_POST(__nv_bfloat16, 32); }
@@ -296,6 +322,13 @@ void qkv_post_fwd(const void* qkv, const void* v1, void* q, void* k, void* v, co
 void qkv_post_bwd(const void* dq, const void* dk, const void* dv, bool dv_is_f32, const void* qkv, const void* v1, void* dqkv,
                   float* dv1_out, float* scalars, float* partial, const QkvPostParams& p, bool bf16, cudaStream_t st) {
   const int grid = qkv_post_bwd_grid((int64_t)p.B * p.S, p.H + 2 * p.Hkv, p.hd);
+  if (!dv_is_f32) {
+    const int rows = qkv_post_bwd_tile(dq, dk, dv, qkv, v1, dqkv, dv1_out, partial, grid, p, bf16, st);
+    if (rows > 0) {
+      qkv_post_finalize<<<1, 256, 0, st>>>(partial, rows, scalars, p);
+      return;
+    }
+  }
 #define SEG_POSTB(TY, DV, HD)                                                                                                      \
   qkv_post_bwd_kernel<TY, DV, HD><<<grid, kPostThreads, 0, st>>>((const TY*)dq, (const TY*)dk, (const DV*)dv, (const TY*)qkv,       \
                                                                  (const TY*)v1, (TY*)dqkv, dv1_out, partial, p)

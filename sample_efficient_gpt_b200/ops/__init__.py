@@ -164,6 +164,19 @@ def swiglu_bwd(df, u):
     return ref.swiglu_bwd(df, u)
 
 
+def up_swiglu(x: Tensor, w: Tensor):
+    """(u, f) of a SwiGLU feed-forward's first half: u = x w^T for w = [F gate rows | F up rows], f = silu(u[:, :F]) * u[:, F:]
+    (transformer/core.py:86-89 of the reference).  On CUDA one launch of the tcgen05 GEMM whose epilogue stores u and forms
+    f from the rounded tile while it is still on chip (``SEGPT_FUSE_SWIGLU=0``: GEMM, then the element-wise kernel;
+    both give the same bits)."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.size(0) % 256 == 0
+            and os.environ.get("SEGPT_FUSE_SWIGLU", "1") != "0" and has_kernel("gemm_swiglu") and _native_gemm(x, w)):
+        _count()
+        return ext().gemm_swiglu(x, w)
+    u = matmul_nt(x, w)
+    return u, swiglu_fwd(u)
+
+
 # ----------------------------------------------------------------------------- GEMMs
 def _native_gemm(*tensors) -> bool:
     """The block projections (and their gradients) run on this package's tcgen05 GEMM (CTA pairs, csrc/gemm_pair.cu);

@@ -160,8 +160,7 @@ class FusedEngine:
             m, u = self.moe.forward(i, n2, train, record=want_kurt or not train)  # u: what the expert backward needs
             f = None
         else:
-            u = ops.matmul_nt(n2, self._w(blk.ffn.up.linear.weight))
-            f = ops.swiglu_fwd(u)
+            u, f = ops.up_swiglu(n2, self._w(blk.ffn.up.linear.weight))
             m = ops.matmul_nt(f, self._w(blk.ffn.down.linear.weight))
         saved = (x, n1, rstd1, qkv, z, q, k, v, o, lse, g, y, n2, rstd2, u, f)
         return y, m, v, kurt, saved

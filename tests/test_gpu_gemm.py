@@ -145,3 +145,26 @@ def test_pair_store_reduce_and_split_contraction():
     # generic epilogue (addend, bf16) on a long contraction that is cut between pairs
     a, b, c = _rand(256, 8192), _rand(300, 8192), _rand(256, 300)
     _check(G.gemm(a, b, c=c, alpha=0.5, beta=2.0, impl=1), 0.5 * (a.float() @ b.float().t()) + 2.0 * c.float(), "nt addend, cut contraction")
+
+
+@pytest.mark.parametrize("M,F,K", [(512, 128, 64), (1000, 384, 1152), (4096, 3072, 1152), (77, 256, 200)])
+def test_gemm_swiglu_epilogue(M, F, K, gemm_impl):
+    """Up projection with the SwiGLU activation in the GEMM's epilogue: u against the fp32 product, f against the fp32
+    statement of silu(gate) * up on the rounded u, and both bit-identical to GEMM + element-wise kernel."""
+    if gemm_impl == 0:
+        pytest.skip("the fused epilogue exists on the CTA-pair kernel only")
+    G = _g()
+    torch.manual_seed(M + F)
+    x = (torch.randn(M, K, device=DEV) * 0.7).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device=DEV) * (1.5 / K**0.5)).to(torch.bfloat16)
+    u, f = ops.ext().gemm_swiglu(x, w)
+    torch.cuda.synchronize()
+    assert G.status() == 0
+    u_ref = x.float() @ w.float().T
+    assert (u.float() - u_ref).abs().max().item() <= 2e-2 * u_ref.abs().max().item()
+    ur = u.float()
+    f_ref = torch.nn.functional.silu(ur[:, :F]) * ur[:, F:]
+    assert (f.float() - f_ref).abs().max().item() <= 1e-2 * f_ref.abs().max().item() + 1e-3
+    u2 = G.gemm(x, w, impl=1, split_k=False)  # same summation order as the fused launch: whole tiles
+    f2 = ops.swiglu_fwd(u2)
+    assert torch.equal(u, u2) and torch.equal(f, f2)

@@ -118,6 +118,49 @@ def test_qkv_post(hd, H, Hkv, bf16, qknorm):
                 close(run, before + outr[1], tol, name="dv1 accumulated")
 
 
+@pytest.mark.parametrize("B,S,extra", [(3, 72, 0), (4, 640, 0), (2, 328, 24), (1, 8, 0)])
+@pytest.mark.parametrize("qknorm", [True, False])
+def test_qkv_post_shared_memory_variant(B, S, extra, qknorm):
+    """bf16, head_dim 64, S a multiple of 8: token rows are staged through shared memory with bulk copies (several tiles
+    per CTA, a ragged last tile, and qkv / dqkv as the leading columns of a wider projection output)."""
+    from sample_efficient_gpt_b200.models.rope import rope_tables
+    from sample_efficient_gpt_b200.ops import gemm as G
+
+    torch.manual_seed(4)
+    H, Hkv, hd = 18, 6, 64
+    n = (H + 2 * Hkv) * hd
+    cos, sin = rope_tables(1024, 10000.0, hd, DEV)
+    wide = torch.randn(B * S, n + extra, device=DEV).to(torch.bfloat16)
+    qkv = wide[:, :n]
+    v1 = torch.randn(B, S, Hkv, hd, device=DEV).to(torch.bfloat16)
+    sc = [torch.tensor([v], device=DEV) for v in (1.3, 0.8, 0.5, 1.1)]
+    args = (cos, sin, *sc, B, S, H, Hkv, hd, qknorm)
+    for v1_ in (v1, None):
+        q, k, v = _ext().qkv_post_fwd(qkv, v1_, *args)
+        torch.cuda.synchronize()
+        assert G.status() == 0
+        qr, kr, vr = ref.qkv_post_fwd(qkv.float(), None if v1_ is None else v1_.float(), *args)
+        close(q, qr, 4e-2, name="q"); close(k, kr, 4e-2, name="k"); close(v, vr, 4e-2, name="v")
+        dq, dk, dv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+        dwide = torch.full((B * S, n + extra), 7.0, device=DEV).to(torch.bfloat16)
+        out = _ext().qkv_post_bwd(dq, dk, dv, qkv, v1_, *args, dwide[:, :n])
+        torch.cuda.synchronize()
+        assert G.status() == 0
+        outr = ref.qkv_post_bwd(dq.float(), dk.float(), dv.float(), qkv.float(), None if v1_ is None else v1_.float(), *args)
+        close(out[0], outr[0], 8e-2, name="dqkv")
+        if extra:
+            assert bool((dwide[:, n:] == 7.0).all()), "columns beside dqkv must stay untouched"
+        for i, nm in zip(range(2, 6), ("dqgain", "da1", "da2", "dvscale")):
+            close(out[i], outr[i], 0.5, 2e-3, name=nm)
+        if v1_ is not None:
+            close(out[1], outr[1], 4e-2, name="dv1")
+            run = torch.randn(B, S, Hkv, hd, device=DEV)
+            before = run.clone()
+            out2 = _ext().qkv_post_bwd(dq, dk, dv, qkv, v1_, *args, None, run)
+            assert out2[1].data_ptr() == run.data_ptr()
+            close(run, before + outr[1], 4e-2, name="dv1 accumulated")
+
+
 def test_ce_chunk():
     torch.manual_seed(3)
     rows, V = 300, 49152
