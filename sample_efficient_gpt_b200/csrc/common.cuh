@@ -109,5 +109,11 @@ template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16*
 // ex2 + rcp on the special-function unit (within 2 ulp of the divided form): four instructions, which matters where the
 // activation runs inside a GEMM epilogue next to the warp that issues the MMAs
 __device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// Gradient of f = silu(a) * b: shared by the element-wise kernel and the GEMM epilogue that does the same on chip.
+__device__ __forceinline__ void swiglu_grad(float a, float b, float df, float& da, float& db) {
+  const float s = sigmoidf_(a);
+  da = df * b * (s + a * s * (1.f - s));
+  db = df * a * s;
+}
 
 }  // namespace seg

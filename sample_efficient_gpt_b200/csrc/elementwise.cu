@@ -36,12 +36,6 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ u
   }
 }
 
-__device__ __forceinline__ void swiglu_grad(float a, float b, float df, float& da, float& db) {
-  const float s = sigmoidf_(a);
-  da = df * b * (s + a * s * (1.f - s));
-  db = df * a * s;
-}
-
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const T* __restrict__ df, const T* __restrict__ u, T* __restrict__ du,
                                                        int64_t rows, int F) {

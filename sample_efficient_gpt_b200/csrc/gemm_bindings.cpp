@@ -149,6 +149,23 @@ std::tuple<Tensor, Tensor> gemm_swiglu(const Tensor& x, const Tensor& w) {
   return {u, f};
 }
 
+// du = gradient of u = (gate | up) given dy [M, K], the down projection's weight w [K, F] and u [M, 2F].
+Tensor gemm_swiglu_bwd(const Tensor& dy, const Tensor& w, const Tensor& u) {
+  check_operand(dy, "dy");
+  check_operand(w, "w");
+  check_operand(u, "u");
+  TORCH_CHECK(dy.dim() == 2 && w.dim() == 2 && u.dim() == 2 && dy.size(1) == w.size(0) && u.size(0) == dy.size(0) && u.size(1) == 2 * w.size(1) &&
+                  w.size(1) % 256 == 0, "dy [M, K], w [K, F], u [M, 2F] with F a multiple of 256");
+  const int M = (int)dy.size(0), K = (int)dy.size(1), F = (int)w.size(1);
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor du = torch::empty({M, 2 * F}, dy.options());
+  auto& st = device_state(dy.device());
+  const int rc = seg::gemm_swiglu_bwd_pair(dy.data_ptr(), w.data_ptr(), u.data_ptr(), du.data_ptr(), M, F, K, dy.stride(0), w.stride(0), u.stride(0),
+                                           du.stride(0), st.status.data_ptr<int>(), st.sm_count, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "gemm_swiglu_bwd launch failed with code ", rc);
+  return du;
+}
+
 // Host read of the status word (synchronises): 0 = every wait completed.
 int64_t gemm_status(int64_t device_index) {
   auto& st = device_state(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
@@ -235,6 +252,7 @@ void register_gemm(pybind11::module_& m) {
         pybind11::arg("route_batch_stride") = 0, pybind11::arg("route_base") = 0, pybind11::arg("route_ld") = 0,
         pybind11::arg("impl") = 1, pybind11::arg("split_k") = true, pybind11::arg("wait_limit") = 0);
   m.def("gemm_swiglu", &gemm_swiglu, pybind11::arg("x"), pybind11::arg("w"));
+  m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd, pybind11::arg("dy"), pybind11::arg("w"), pybind11::arg("u"));
   m.def("fa_fwd", &fa_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);
   m.def("fa_bwd", &fa_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("lse"),
         pybind11::arg("causal"), pybind11::arg("prof") = std::nullopt);

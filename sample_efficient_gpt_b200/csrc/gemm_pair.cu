@@ -42,11 +42,11 @@ namespace seg {
 using namespace sm100;
 
 constexpr int kPairThreads = 320;
-constexpr int kEpiGeneric = 0, kEpiTma = 1, kEpiTmaC = 2, kEpiSwiglu = 3;
+constexpr int kEpiGeneric = 0, kEpiTma = 1, kEpiTmaC = 2, kEpiSwiglu = 3, kEpiSwigluBwd = 4;
 // The addend variant keeps two 4 KB tiles per epilogue warp (each receives a box of C, is overwritten with the result and
-// stored), paid for with one stage of the ring; so does the SwiGLU variant (gate and up columns leave side by side).
-__host__ __device__ constexpr int pair_stages(int epi) { return (epi == kEpiTmaC || epi == kEpiSwiglu) ? 5 : 6; }
-__host__ __device__ constexpr int pair_staging_bytes(int epi) { return (epi == kEpiTmaC || epi == kEpiSwiglu) ? 8 * 8192 : 8 * 4096; }
+// stored), paid for with one stage of the ring; so do the SwiGLU variants (gate and up columns travel side by side).
+__host__ __device__ constexpr int pair_stages(int epi) { return epi >= kEpiTmaC ? 5 : 6; }
+__host__ __device__ constexpr int pair_staging_bytes(int epi) { return epi >= kEpiTmaC ? 8 * 8192 : 8 * 4096; }
 constexpr int kPairABytes = 128 * kPairK * 2;
 constexpr int kPairBBytes = 128 * kPairK * 2;
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
@@ -124,7 +124,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
     if (EPI != kEpiGeneric) prefetch_tensormap(&map_d);
-    if (EPI == kEpiTmaC || EPI == kEpiSwiglu) prefetch_tensormap(&map_c);
+    if (EPI >= kEpiTmaC) prefetch_tensormap(&map_c);
   }
   if (warp == 0) {
     __syncwarp();
@@ -286,6 +286,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         __syncwarp();
       }
+      if (EPI == kEpiSwigluBwd && row0 < p.M) {
+        // gate and up values of this warp's first 64 columns are on their way before the accumulator is complete
+        if (lane == 0) {
+          bulk_wait_group_read0();  // the previous item's stores have left the staging tiles
+          const int col = tl.n * kPairN + half * 128;
+          mbar_expect_tx(smem_u32(&c_bar[ep * 2]), 4096);
+          tma_load_3d(stage_u32, &map_c, smem_u32(&c_bar[ep * 2]), col, row0, tl.b);
+          mbar_expect_tx(smem_u32(&c_bar[ep * 2 + 1]), 4096);
+          tma_load_3d(stage_u32 + 4096, &map_c, smem_u32(&c_bar[ep * 2 + 1]), p.swiglu_f + col, row0, tl.b);
+        }
+        __syncwarp();
+      }
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, ab, 6, p.epi_backoff_ns)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * kPairN;
@@ -409,6 +421,69 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tma_store_3d(&map_c, stage_u32, hcol, row0, tl.b);
               bulk_commit_group();
             }
+          }
+        } else if (EPI == kEpiSwigluBwd) {
+          if (row0 < p.M) {
+            // The accumulator is df = dy W (gradient of f = silu(gate) * up), rounded to bf16 as a stored df would be.  Per
+            // 64 columns: gate and up arrive in tiles 0 and 1, are replaced by their gradients and leave for the gate and up
+            // blocks of the output; the second 64 columns reuse the tiles once the first stores have read them.
+#pragma unroll 1
+            for (int k = 0; k < 2; ++k) {
+              const int c0g = half * 128 + k * 64;
+              const int col = tl.n * kPairN + c0g;
+              if (k == 1) {
+                if (lane == 0) {
+                  bulk_wait_group_read0();
+                  mbar_expect_tx(smem_u32(&c_bar[ep * 2]), 4096);
+                  tma_load_3d(stage_u32, &map_c, smem_u32(&c_bar[ep * 2]), col, row0, tl.b);
+                  mbar_expect_tx(smem_u32(&c_bar[ep * 2 + 1]), 4096);
+                  tma_load_3d(stage_u32 + 4096, &map_c, smem_u32(&c_bar[ep * 2 + 1]), p.swiglu_f + col, row0, tl.b);
+                }
+                __syncwarp();
+              }
+              if (!mbar_wait(smem_u32(&c_bar[ep * 2]), c_phase & 1u, ab, 8) || !mbar_wait(smem_u32(&c_bar[ep * 2 + 1]), (c_phase >> 1) & 1u, ab, 8)) {
+                ok = false;
+                break;
+              }
+              c_phase ^= 3u;
+              uint4* ga = reinterpret_cast<uint4*>(stage_raw + lane * 128);
+              uint4* ua = reinterpret_cast<uint4*>(stage_raw + 4096 + lane * 128);
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_acc + c0g + c * 32, v);
+                tmem_ld_wait_regs(v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int slot = (c * 4 + j) ^ (lane & 7);
+                  const uint4 gq = ga[slot], uq = ua[slot];
+                  const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
+                  uint32_t aw[4], bw[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 d = __bfloat1622float2(__floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[e]));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[e]));
+                    float da0, db0, da1, db1;
+                    swiglu_grad(a.x, b.x, d.x, da0, db0);
+                    swiglu_grad(a.y, b.y, d.y, da1, db1);
+                    const __nv_bfloat162 ah = __floats2bfloat162_rn(da0, da1), bh = __floats2bfloat162_rn(db0, db1);
+                    aw[e] = *reinterpret_cast<const uint32_t*>(&ah);
+                    bw[e] = *reinterpret_cast<const uint32_t*>(&bh);
+                  }
+                  ga[slot] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+                  ua[slot] = make_uint4(bw[0], bw[1], bw[2], bw[3]);
+                }
+              }
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&map_d, stage_u32, col, row0, tl.b);
+                tma_store_3d(&map_d, stage_u32 + 4096, p.swiglu_f + col, row0, tl.b);
+                bulk_commit_group();
+              }
+            }
+            if (!ok) break;
           }
         } else if (EPI == kEpiTma) {
           if (row0 < p.M) {
@@ -759,6 +834,49 @@ int gemm_swiglu_pair(const void* X, const void* W, void* U, void* Fout, int M, i
   const PairSched sched = make_pair_sched(M, 2 * F, K, 1, 0, p.n_static, p.splits);
   const int pairs = sched.n_items < sm_count / 2 ? sched.n_items : sm_count / 2;
   return launch_pair<false, false, __nv_bfloat16, kEpiSwiglu>(ma, mb, md, mc, p, pairs, st);
+}
+
+// DU [M, 2F] = gradient of (gate | up) for f = silu(gate) * up, given dY [M, K], W [K, F] (df = dY W never reaches memory)
+// and U [M, 2F] = (gate | up).
+int gemm_swiglu_bwd_pair(const void* dY, const void* W, const void* U, void* DU, int M, int F, int K, int64_t ldy, int64_t ldw,
+                         int64_t ldu, int64_t lddu, int* status, int sm_count, cudaStream_t st, long long wait_limit) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if (F % 256 != 0 || K % 8 != 0) return -7;
+  for (const void* ptr : {dY, W, U, (const void*)DU})
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return -8;
+  if (ldy % 8 != 0 || ldw % 8 != 0 || ldu % 8 != 0 || lddu % 8 != 0) return -8;
+  CUtensorMap ma, mb, md, mc;
+  int r = make_tensor_map_3d(&ma, dY, false, (uint64_t)K, (uint64_t)M, 1, (uint64_t)ldy, (uint64_t)M * ldy, 64, 128);
+  if (r != 0) return 100 + r;
+  r = make_tensor_map_3d(&mb, W, false, (uint64_t)F, (uint64_t)K, 1, (uint64_t)ldw, (uint64_t)K * ldw, 64, 64);  // memory [K, F]
+  if (r != 0) return 200 + r;
+  r = make_tensor_map_3d(&md, DU, false, (uint64_t)2 * F, (uint64_t)M, 1, (uint64_t)lddu, (uint64_t)M * lddu, 64, 32);
+  if (r != 0) return 300 + r;
+  r = make_tensor_map_3d(&mc, U, false, (uint64_t)2 * F, (uint64_t)M, 1, (uint64_t)ldu, (uint64_t)M * ldu, 64, 32);
+  if (r != 0) return 400 + r;
+  GemmParams p;
+  p.M = M; p.N = F; p.K = K; p.batch = 1;
+  p.alpha = 1.f; p.beta = 0.f;
+  p.C = U; p.D = DU; p.ldd = lddu; p.batch_stride_d = (int64_t)M * lddu;
+  p.status = status;
+  p.symmetric = 0;
+  p.n_extra = 0;
+  for (int i = 0; i < 7; ++i) p.D_extra[i] = nullptr;
+  p.wait_flags = nullptr; p.wait_seq = 0; p.region_rows = 1;
+  p.route_rows = 0; p.route_batch_stride = 0; p.route_base = 0;
+  for (int i = 0; i < 8; ++i) p.D_route[i] = nullptr;
+  p.wait_limit = wait_limit;
+  p.d_extent = (int64_t)(M - 1) * lddu + 2 * F;
+  p.route_extent = 0;
+  p.reduce = 0;
+  p.ws = nullptr; p.ws_flags = nullptr;
+  p.b_box_rows = 64;
+  p.epi_backoff_ns = 0;
+  p.swiglu_f = F;
+  pair_choose_split(M, F, K, 1, 0, sm_count / 2, false, p.n_static, p.splits);  // whole tiles only
+  const PairSched sched = make_pair_sched(M, F, K, 1, 0, p.n_static, p.splits);
+  const int pairs = sched.n_items < sm_count / 2 ? sched.n_items : sm_count / 2;
+  return launch_pair<false, true, __nv_bfloat16, kEpiSwigluBwd>(ma, mb, md, mc, p, pairs, st);
 }
 
 }  // namespace seg

@@ -150,6 +150,11 @@ int gemm_bf16(const void* A, const void* B, const void* C, void* D, int M, int N
 // F a multiple of 128, K a multiple of 8, 16-byte aligned bases and row strides.
 int gemm_swiglu_pair(const void* X, const void* W, void* U, void* Fout, int M, int F, int K, int64_t ldx, int64_t ldw, int64_t ldu,
                      int64_t ldf, int* status, int sm_count, cudaStream_t st, long long wait_limit = 0);
+// Data gradient of the down projection with the SwiGLU backward in the epilogue: DU [M, 2F] = (d gate | d up) from dY [M, K],
+// W [K, F] (row-major: the down projection's weight), U [M, 2F] = (gate | up); df = dY W is rounded to bf16 on chip, as a
+// stored df would be, and never written.  bf16, F a multiple of 256.
+int gemm_swiglu_bwd_pair(const void* dY, const void* W, const void* U, void* DU, int M, int F, int K, int64_t ldy, int64_t ldw,
+                         int64_t ldu, int64_t lddu, int* status, int sm_count, cudaStream_t st, long long wait_limit = 0);
 // Debug build only (no effect otherwise): every GEMM launched afterwards pretends that its output holds at most `elements`
 // elements (0: off), so that a test can watch the index checks refuse in-range stores - and only those - without any fault.
 void gemm_debug_extent_cap(int64_t elements);

@@ -177,6 +177,19 @@ def up_swiglu(x: Tensor, w: Tensor):
     return u, swiglu_fwd(u)
 
 
+def down_dgrad_swiglu(dy: Tensor, w_down: Tensor, u: Tensor) -> Tensor:
+    """Gradient of u = (gate | up) [M, 2F] of a SwiGLU feed-forward from the gradient dy [M, d] of its output and the down
+    projection's weight w_down [d, F]: du = swiglu_bwd(dy @ w_down, u).  On CUDA one launch: the GEMM's epilogue takes df
+    (rounded to bf16, as a stored df would be) straight from the accumulator, so df never reaches memory
+    (``SEGPT_FUSE_SWIGLU=0``: GEMM, then the element-wise kernel; both give the same bits)."""
+    if (dy.is_cuda and dy.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16 and u.dtype == torch.bfloat16 and dy.dim() == 2
+            and w_down.size(1) % 256 == 0 and os.environ.get("SEGPT_FUSE_SWIGLU", "1") != "0" and has_kernel("gemm_swiglu_bwd")
+            and _native_gemm(dy, w_down) and u.is_contiguous()):
+        _count()
+        return ext().gemm_swiglu_bwd(dy, w_down, u)
+    return swiglu_bwd(matmul_nn(dy, w_down), u)
+
+
 # ----------------------------------------------------------------------------- GEMMs
 def _native_gemm(*tensors) -> bool:
     """The block projections (and their gradients) run on this package's tcgen05 GEMM (CTA pairs, csrc/gemm_pair.cu);

@@ -109,9 +109,30 @@ class FusedEngine:
                             opt.lowp_shadows[p] = self.shadows[p]
 
     def ensure_grads(self):
-        for p in self.model.parameters():
-            if p.requires_grad and p.grad is None:
+        """fp32 gradients for every parameter.  When none exists yet (single-process runs; DDP installs its own views before)
+        they are carved out of one flat buffer, 256-byte aligned, so that the global gradient norm is one reduction
+        (``flat_grads``) instead of one per tensor."""
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        if params and all(p.grad is None for p in params) and getattr(self, "flat_grads", None) is None:
+            offs, total = [], 0
+            for p in params:
+                offs.append(total)
+                total += (p.numel() + 63) // 64 * 64
+            self.flat_grads = torch.zeros(total, dtype=torch.float32, device=params[0].device)
+            self._flat_views = {}
+            for p, o in zip(params, offs):
+                p.grad = self._flat_views[p] = self.flat_grads[o : o + p.numel()].view_as(p)
+            return
+        for p in params:
+            if p.grad is None:
                 p.grad = torch.zeros_like(p, dtype=torch.float32)
+
+    def flat_grad_norm(self) -> Tensor | None:
+        """Global gradient norm from the flat buffer; None when some gradient no longer lives there."""
+        flat, views = getattr(self, "flat_grads", None), getattr(self, "_flat_views", None)
+        if flat is None or any(p.grad is not v for p, v in views.items()):
+            return None
+        return torch.linalg.vector_norm(flat)
 
     def _dqkvz_buffer(self, T: int, n_ext: int, like: Tensor) -> Tensor:
         """Gradient buffer of the fused qkv+gate projection, shared by all blocks (the kernels of a step run in stream order);
@@ -178,9 +199,8 @@ class FusedEngine:
             dn2 = self.moe.backward(i, dres_lp, n2, u, self._loss_coef, self._first_accum)
         else:
             w_down, w_up = blk.ffn.down.linear.weight, blk.ffn.up.linear.weight
-            df = ops.matmul_nn(dres_lp, self._w(w_down))
+            du = ops.down_dgrad_swiglu(dres_lp, self._w(w_down), u)
             self._wgrad(w_down, dres_lp, f)
-            du = ops.swiglu_bwd(df, u)
             dn2 = ops.matmul_nn(du, self._w(w_up))
             self._wgrad(w_up, du, n2)
         dy, dy_lp, dgain2 = ops.add_rmsnorm_bwd(dn2, dres, y, blk.ln2.gain, rstd2, scale, self.lp)

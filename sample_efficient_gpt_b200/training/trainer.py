@@ -541,6 +541,8 @@ class Trainer:
                 if self.ddp is not None and ga == 1:
                     local = [p.grad for n, p in self.model.named_parameters() if p.grad is not None and p not in self.ddp.param_bucket]
                     gnorm = self.ddp.reduced_grad_norm(local)  # partial sums from inside the reduction kernels
+                if gnorm is None and self.engine is not None and self.ddp is None:
+                    gnorm = self.engine.flat_grad_norm()  # one reduction over the engine's flat gradient buffer
                 if gnorm is None:
                     gnorm = grad_norm([p.grad for p in params])
             update_ratios = [opt.step() for opt in self.optimizers]

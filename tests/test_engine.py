@@ -48,6 +48,13 @@ def test_engine_gradients_match_autograd(kw):
         assert torch.allclose(p.grad, 2 * want[n], rtol=2e-3, atol=1e-6 + 2e-4 * float(want[n].abs().max())), n
     ev = eng.forward_loss(ids, tg)
     assert float(ev.loss) == pytest.approx(float(loss), rel=1e-5)
+    # the gradients are views of one flat buffer: the global norm is a single reduction over it
+    from sample_efficient_gpt_b200.optim.clip import grad_norm
+
+    flat_norm = eng.flat_grad_norm()
+    assert flat_norm is not None and float(flat_norm) == pytest.approx(float(grad_norm([p.grad for p in m.parameters()])), rel=2e-4)
+    next(m.parameters()).grad = torch.zeros_like(next(m.parameters()))  # a gradient that left the buffer: no shortcut
+    assert eng.flat_grad_norm() is None
 
 
 def test_engine_fused_gate_projection_matches_autograd():

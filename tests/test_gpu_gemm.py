@@ -168,3 +168,26 @@ def test_gemm_swiglu_epilogue(M, F, K, gemm_impl):
     u2 = G.gemm(x, w, impl=1, split_k=False)  # same summation order as the fused launch: whole tiles
     f2 = ops.swiglu_fwd(u2)
     assert torch.equal(u, u2) and torch.equal(f, f2)
+
+
+@pytest.mark.parametrize("M,F,K", [(512, 256, 64), (1000, 512, 1152), (4096, 3072, 1152), (77, 256, 200)])
+def test_gemm_swiglu_backward_epilogue(M, F, K, gemm_impl):
+    """Data gradient of the down projection with the SwiGLU backward in the GEMM's epilogue, against the fp32 statement and
+    bit for bit against GEMM + element-wise kernel."""
+    if gemm_impl == 0:
+        pytest.skip("the fused epilogue exists on the CTA-pair kernel only")
+    G = _g()
+    torch.manual_seed(M + F + 1)
+    dy = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(K, F, device=DEV) * (1.5 / K**0.5)).to(torch.bfloat16)
+    u = torch.randn(M, 2 * F, device=DEV).to(torch.bfloat16)
+    du = ops.ext().gemm_swiglu_bwd(dy, w, u)
+    torch.cuda.synchronize()
+    assert G.status() == 0
+    df = (dy.float() @ w.float()).to(torch.bfloat16).float()
+    a, b = u.float()[:, :F], u.float()[:, F:]
+    s = torch.sigmoid(a)
+    want = torch.cat([df * b * (s + a * s * (1 - s)), df * a * s], dim=1)
+    assert (du.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
+    df2 = G.gemm(dy, w, b_mn=True, impl=1, split_k=False)  # same summation order as the fused launch: whole tiles
+    assert torch.equal(du, ops.swiglu_bwd(df2, u))
