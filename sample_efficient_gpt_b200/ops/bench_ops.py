@@ -349,9 +349,39 @@ def bench_decode(a):
         print(json.dumps(row))
 
 
+def bench_swiglu_gemm(a):
+    """The feed-forward's two fused launches against GEMM + element-wise kernel: up projection with SwiGLU in the epilogue,
+    and the down projection's data gradient with the SwiGLU backward in the epilogue (IMU-1 shapes: d 1152, F 3072)."""
+    from sample_efficient_gpt_b200.ops import gemm as G
+
+    T, d, F = a.tokens, a.k, a.cols
+    x, dy = rnd(T, d), rnd(T, d)
+    w_up, w_down = rnd(2 * F, d, scale=0.03), rnd(d, F, scale=0.03)
+    u = rnd(T, 2 * F, scale=1.0)
+    df = G.gemm(dy, w_down, b_mn=True)
+    ext = ops.ext()
+    t = (lambda fn: time_sustained(fn)) if a.sustained else (lambda fn: timeit(fn, a.iters))
+    rows = [
+        ("up projection + swiglu, fused", lambda: ext.gemm_swiglu(x, w_up), 2.0 * T * 2 * F * d),
+    ]
+    if not a.ours_only:
+        rows += [("up projection (GEMM alone)", lambda: G.gemm(x, w_up), 2.0 * T * 2 * F * d),
+                 ("swiglu_fwd kernel", lambda: ops.swiglu_fwd(u), 0.0)]
+    rows.append(("down dgrad + swiglu backward, fused", lambda: ext.gemm_swiglu_bwd(dy, w_down, u), 2.0 * T * F * d))
+    if not a.ours_only:
+        rows += [("down dgrad (GEMM alone)", lambda: G.gemm(dy, w_down, b_mn=True), 2.0 * T * F * d),
+                 ("swiglu_bwd kernel", lambda: ops.swiglu_bwd(df, u), 0.0)]
+    for name, fn, flops in rows:
+        ms = t(fn)
+        print(json.dumps({"op": name, "tokens": T, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1) if flops else None,
+                          "mode": "sustained" if a.sustained else "flushed single calls"}))
+    torch.cuda.synchronize()
+    assert G.status() == 0
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe", "decode", "muon"])
+    p.add_argument("--op", required=True, choices=["gemm", "ns", "attention", "linear_ce", "elementwise", "moe", "decode", "muon", "swiglu_gemm"])
     p.add_argument("--layers", type=int, default=30, help="muon: layers whose four block matrices are stepped")
     p.add_argument("--m", type=int, default=8192)
     p.add_argument("--n", type=int, default=1920)
@@ -362,13 +392,13 @@ def main():
     p.add_argument("--cols", type=int, default=3072)
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--iters", type=int, default=10)
-    p.add_argument("--tokens", type=int, default=32768, help="linear_ce: rows of the hidden-state matrix")
+    p.add_argument("--tokens", type=int, default=32768, help="linear_ce / swiglu_gemm: rows of the hidden-state matrix")
     p.add_argument("--ours-only", action="store_true", help="linear_ce / muon: skip the comparison arms (profiling runs)")
     p.add_argument("--sustained", action="store_true", help="gemm: time about a second of back-to-back calls (power-capped rate) instead of flushed single calls")
     p.add_argument("--no-split-k", action="store_true", help="gemm: whole tiles only, no tile is cut along the contraction")
     p.add_argument("--shapes", default="", help="gemm: 'block' runs the IMU-1 block shapes (forward, data gradient, weight gradient)")
     a = p.parse_args()
-    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe, "decode": bench_decode, "muon": bench_muon}[a.op](a)
+    {"gemm": bench_gemm, "ns": bench_ns, "attention": bench_attention, "linear_ce": bench_linear_ce, "elementwise": bench_elementwise, "moe": bench_moe, "decode": bench_decode, "muon": bench_muon, "swiglu_gemm": bench_swiglu_gemm}[a.op](a)
 
 
 if __name__ == "__main__":
