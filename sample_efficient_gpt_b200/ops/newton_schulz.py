@@ -1,7 +1,7 @@
 """Newton-Schulz chain on the tcgen05 GEMM.
 
 Per iteration and for a whole batch of same-shape matrices: the Gram matrix ``A`` computes only the tiles on or above
-the diagonal and mirrors them; ``B = b A + c A A`` is computed in full, because with the addend fetched by TMA the
+the diagonal and mirrors them when its contraction is long (>= 2048), and all tiles otherwise; ``B = b A + c A A`` is computed in full, because with the addend fetched by TMA the
 plain epilogue is faster than the mirrored one on this short contraction; the update ``a X + B X`` (wide X) or
 ``a X + X B`` (tall X) reads its operands in place (K-major and MN-major tiles), so tall matrices are never
 transposed: for ``R > C`` the chain runs on ``X^T`` implicitly with ``A = X^T X``.  Every product accumulates in fp32
@@ -20,6 +20,10 @@ import os
 from sample_efficient_gpt_b200.ops import gemm as G
 
 _SYM_B = os.environ.get("SEGPT_NS_SYMMETRIC_B", "0") == "1"  # mirrored instead of full computation of b A + c A A
+# The Gram matrix is mirrored (upper-triangle tiles only) when its contraction is at least this long: the mirrored epilogue
+# is slower than the TMA store and hides only behind a long mainloop (30 matrices, chain of 5: 1152 x 1152 runs 1.95 ms
+# mirrored and 1.56 ms in full; 1152 x 3072 2.71 against 2.78 ms; 6144 x 1152 4.06 against 4.71 ms).
+_SYM_A_MIN_K = int(os.environ.get("SEGPT_NS_SYMMETRIC_A_MIN_K", "2048"))
 
 
 def ns_iterations(X: Tensor, Y: Tensor, coeffs, final_extra_dst=None) -> Tensor:
@@ -45,10 +49,11 @@ def ns_iterations(X: Tensor, Y: Tensor, coeffs, final_extra_dst=None) -> Tensor:
         last = len(coeffs) - 1
         pushed = False
         for it, (a, b, c) in enumerate(coeffs):
+            sym_a = max(R, C) >= _SYM_A_MIN_K
             if tall:
-                G.gemm(X, X, out=A, a_mn=True, b_mn=True, symmetric=True)  # X^T X
+                G.gemm(X, X, out=A, a_mn=True, b_mn=True, symmetric=sym_a)  # X^T X
             else:
-                G.gemm(X, X, out=A, symmetric=True)  # X X^T
+                G.gemm(X, X, out=A, symmetric=sym_a)  # X X^T
             G.gemm(A, A, c=A, out=B, alpha=c, beta=b, symmetric=_SYM_B)
             extra = final_extra_dst(Y) if (it == last and final_extra_dst is not None) else None
             pushed = pushed or bool(extra)
