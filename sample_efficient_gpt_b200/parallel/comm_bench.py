@@ -166,6 +166,57 @@ def emulate_one_gpu(world: int, mb: int, blocks: int, reps: int) -> dict:
     return out
 
 
+def gemm_allgather(rows: int, cols: int, total: int, reps: int, warmup: int) -> dict:
+    """The last GEMM of a sharded Newton-Schulz chain: each rank computes ``a X + B X`` for its share of ``total`` matrices
+    ([rows, rows] x [rows, cols]) and the epilogue stores every tile into all ranks' buffers (``extra_dst`` = the peers'
+    copies), followed by the device barrier.  Timed against the same GEMM with a local output only, and against that GEMM
+    followed by ``all_gather_into_tensor``; roofline = max(FLOPs at the measured cuBLAS rate, bytes that leave this GPU
+    over NVLink at 770 GB/s)."""
+    from sample_efficient_gpt_b200.ops import gemm as G
+    from sample_efficient_gpt_b200.parallel.symm import SymmComm
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    comm = SymmComm.create(dev)
+    per = (total + world - 1) // world
+    buf = comm.symm_zeros((world * per, rows, cols), torch.bfloat16)
+    mine = buf[rank * per : (rank + 1) * per]
+    local = torch.empty_like(mine)
+    gathered = torch.empty_like(buf)
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    Bm = (torch.randn(per, rows, rows, device=dev, generator=g) * 0.03).to(torch.bfloat16)
+    X = (torch.randn(per, rows, cols, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    peers = comm.peer_addresses(mine)
+
+    def fused():
+        G.gemm(Bm, X, c=X, out=mine, b_mn=True, alpha=1.0, beta=0.7, extra_dst=peers)
+        comm.barrier()
+
+    def local_only():
+        G.gemm(Bm, X, c=X, out=local, b_mn=True, alpha=1.0, beta=0.7)
+
+    def gemm_then_nccl():
+        G.gemm(Bm, X, c=X, out=local, b_mn=True, alpha=1.0, beta=0.7)
+        dist.all_gather_into_tensor(gathered.view(-1), local.view(-1))
+
+    out = {"world": world, "matrices_per_rank": per, "shape": [rows, cols]}
+    for name, fn in (("gemm_local_only", local_only), ("gemm_epilogue_allgather", fused), ("gemm_then_nccl_allgather", gemm_then_nccl)):
+        out[name + "_ms"] = _time_ms(fn, reps, warmup, flush)
+    torch.cuda.synchronize()
+    comm.check()
+    assert G.status() == 0
+    flops = per * 2.0 * rows * rows * cols
+    link_bytes = (world - 1) * per * rows * cols * 2
+    out["flops_ms_at_1390_tflops"] = flops / 1389.6e12 * 1e3
+    out["link_ms_at_770_gbs"] = link_bytes / 770e9 * 1e3
+    out["roofline_ms"] = max(out["flops_ms_at_1390_tflops"], out["link_ms_at_770_gbs"])
+    out["fused_over_roofline"] = out["gemm_epilogue_allgather_ms"] / out["roofline_ms"] if out["roofline_ms"] > 0 else None
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    return out
+
+
 def main(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--emulate-ranks", type=int, default=0, help="single process, one GPU: run the bucket kernel as rank 0 of N with local stand-ins for the peers (profiling)")
@@ -177,6 +228,10 @@ def main(argv=None):
     p.add_argument("--backends", default="nccl_bf16,nccl_fp32,p2p,multimem")
     p.add_argument("--blocks", type=int, default=128, help="CTAs of the NVLink kernels (training uses 32 to leave SMs to the backward pass)")
     p.add_argument("--nccl-table", action="store_true")
+    p.add_argument("--gemm-allgather", action="store_true", help="time the GEMM whose epilogue stores its tiles into every rank's buffer (sharded Newton-Schulz)")
+    p.add_argument("--rows", type=int, default=1152)
+    p.add_argument("--cols", type=int, default=3072)
+    p.add_argument("--matrices", type=int, default=30)
     p.add_argument("--out", default=None)
     a = p.parse_args(argv)
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
@@ -185,7 +240,9 @@ def main(argv=None):
         return
     dist.init_process_group("nccl")
     try:
-        if a.nccl_table:
+        if a.gemm_allgather:
+            rows = [gemm_allgather(a.rows, a.cols, a.matrices, a.reps, a.warmup)]
+        elif a.nccl_table:
             rows = nccl_table()
         else:
             sizes, mb = [], a.min_mb

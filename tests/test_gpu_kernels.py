@@ -269,6 +269,9 @@ def test_native_attention_backward(B, S, H, Hkv):
     close(dq, qf.grad, 3e-2, 3e-2, name="dQ")
     close(dk, kf.grad, 3e-2, 3e-2, name="dK")
     close(dv, vf.grad, 3e-2, 3e-2, name="dV")
+    for got, want, nm in ((dq, qf.grad, "dQ"), (dk, kf.grad, "dK"), (dv, vf.grad, "dV")):  # relative L2: bf16 rounding level
+        rel = float((got.float() - want).norm() / want.norm())
+        assert rel < 1.5e-2, f"{nm}: relative L2 error {rel}"
 
 
 def test_native_attention_stage_timers():
