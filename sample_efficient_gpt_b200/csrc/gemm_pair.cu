@@ -86,10 +86,17 @@ __device__ __forceinline__ bool wait_slot_flag(uint32_t* flag, const AbortState&
   }
 }
 
+// Tensor maps of the further destinations of the TMA-store epilogues (peer-mapped copies of D on other ranks): every output
+// tile leaves once per destination from the same staging tile, which makes the epilogue the all-gather of the result.
+struct PairExtraMaps {
+  CUtensorMap m[7];
+};
+
 template <bool A_MN, bool B_MN, typename OutT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_c, GemmParams p) {
+                 const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_c,
+                 const __grid_constant__ PairExtraMaps extra, GemmParams p) {
   constexpr int kStages = pair_stages(EPI);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -365,6 +372,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 __syncwarp();
                 if (lane == 0) {
                   tma_store_3d(&map_d, stage_u32 + k * 4096, tl.n * kPairN + half * 128 + k * 64, row0, tl.b);
+                  for (int d = 0; d < p.n_extra; ++d) tma_store_3d(&extra.m[d], stage_u32 + k * 4096, tl.n * kPairN + half * 128 + k * 64, row0, tl.b);
                   bulk_commit_group();
                 }
               }
@@ -536,6 +544,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tma_reduce_add_3d(&map_d, stage_u32, col_store, row0, tl.b);
                   else
                     tma_store_3d(&map_d, stage_u32, col_store, row0, tl.b);
+                  for (int d = 0; d < p.n_extra; ++d) tma_store_3d(&extra.m[d], stage_u32, col_store, row0, tl.b);
                   bulk_commit_group();
                 }
               }
@@ -690,14 +699,16 @@ size_t gemm_pair_flag_words() { return (size_t)kPairMaxSlots * 16; }
 
 template <bool A_MN, bool B_MN, typename OutT, int EPI>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const CUtensorMap& mc, const GemmParams& p, int pairs,
-                       cudaStream_t st) {
+                       cudaStream_t st, const PairExtraMaps* extra = nullptr) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, OutT, EPI>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_total(EPI)) != cudaSuccess) return -2;
     configured = true;
   }
-  kern<<<2 * pairs, kPairThreads, pair_smem_total(EPI), st>>>(ma, mb, md, mc, p);
+  PairExtraMaps ex;
+  for (int i = 0; i < 7; ++i) ex.m[i] = (extra != nullptr) ? extra->m[i] : md;  // unused slots hold a valid map
+  kern<<<2 * pairs, kPairThreads, pair_smem_total(EPI), st>>>(ma, mb, md, mc, ex, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -767,7 +778,9 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
   const size_t esz = out_f32 ? 4 : 2;
   const bool accumulate = C != nullptr && C == D && beta == 1.0f && out_f32;
   const bool aligned = (reinterpret_cast<uintptr_t>(D) % 16 == 0) && ((ldd * esz) % 16 == 0) && (batch == 1 || (bsd * esz) % 16 == 0);
-  const bool plain = n_route == 0 && n_extra <= 0 && !symmetric && aligned && D != nullptr;
+  bool extra_ok = true;  // further destinations go through the TMA epilogues when they are laid out and aligned like D
+  for (int i = 0; i < p.n_extra; ++i) extra_ok = extra_ok && (reinterpret_cast<uintptr_t>(p.D_extra[i]) % 16 == 0);
+  const bool plain = n_route == 0 && extra_ok && !(p.n_extra > 0 && accumulate) && !symmetric && aligned && D != nullptr;
   const bool tma_epi = plain && (C == nullptr || accumulate);
   const bool tma_c_epi = plain && !tma_epi && !out_f32 && (reinterpret_cast<uintptr_t>(C) % 16 == 0);
   md = ma;  // placeholders when unused
@@ -781,10 +794,20 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
     r = make_tensor_map_3d(&mc, C, false, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldd, (uint64_t)bsd, 64, 32);
     if (r != 0) return 400 + r;
   }
+  PairExtraMaps extra_maps;
+  const bool with_extra = (tma_epi || tma_c_epi) && p.n_extra > 0;
+  if (with_extra) {
+    for (int i = 0; i < 7; ++i) {
+      r = make_tensor_map_3d(&extra_maps.m[i], i < p.n_extra ? p.D_extra[i] : D, out_f32, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldd,
+                             (uint64_t)bsd, out_f32 ? 32 : 64, 32);
+      if (r != 0) return 500 + r;
+    }
+  }
+  const PairExtraMaps* extra_ptr = with_extra ? &extra_maps : nullptr;
 #define SEG_PAIR(AM, BM_)                                                                                             \
-  (tma_c_epi ? launch_pair<AM, BM_, __nv_bfloat16, kEpiTmaC>(ma, mb, md, mc, p, pairs, st)                            \
-   : tma_epi ? (out_f32 ? launch_pair<AM, BM_, float, kEpiTma>(ma, mb, md, mc, p, pairs, st)                          \
-                        : launch_pair<AM, BM_, __nv_bfloat16, kEpiTma>(ma, mb, md, mc, p, pairs, st))                 \
+  (tma_c_epi ? launch_pair<AM, BM_, __nv_bfloat16, kEpiTmaC>(ma, mb, md, mc, p, pairs, st, extra_ptr)                 \
+   : tma_epi ? (out_f32 ? launch_pair<AM, BM_, float, kEpiTma>(ma, mb, md, mc, p, pairs, st, extra_ptr)               \
+                        : launch_pair<AM, BM_, __nv_bfloat16, kEpiTma>(ma, mb, md, mc, p, pairs, st, extra_ptr))      \
              : (out_f32 ? launch_pair<AM, BM_, float, kEpiGeneric>(ma, mb, md, mc, p, pairs, st)                      \
                         : launch_pair<AM, BM_, __nv_bfloat16, kEpiGeneric>(ma, mb, md, mc, p, pairs, st)))
   if (!a_mn_major && !b_mn_major) return SEG_PAIR(false, false);
