@@ -191,3 +191,30 @@ def test_gemm_swiglu_backward_epilogue(M, F, K, gemm_impl):
     assert (du.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
     df2 = G.gemm(dy, w, b_mn=True, impl=1, split_k=False)  # same summation order as the fused launch: whole tiles
     assert torch.equal(du, ops.swiglu_bwd(df2, u))
+
+
+@pytest.mark.parametrize("n_extra", [1, 3, 7])
+@pytest.mark.parametrize("with_c", [True, False])
+def test_gemm_extra_destinations(n_extra, with_c, gemm_impl):
+    """Every output tile is stored to all further destinations as well (on several GPUs these are the peers' buffers: the
+    all-gather of the sharded Newton-Schulz result); here they are local buffers, ragged shape, with and without addend,
+    and once with a destination that is not 16-byte aligned (falls back to the register-store epilogue)."""
+    G = _g()
+    torch.manual_seed(n_extra)
+    nb, M, N, K = 3, 328, 712, 264
+    a = (torch.randn(nb, M, K, device=DEV) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(nb, N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    c = torch.randn(nb, M, N, device=DEV).to(torch.bfloat16) if with_c else None
+    want = a.float() @ b.float().transpose(1, 2) + (0.5 * c.float() if with_c else 0.0)
+    for misalign in (False, True):
+        out = torch.empty(nb, M, N, device=DEV, dtype=torch.bfloat16)
+        pool = torch.full((n_extra, nb * M * N + 8), 7.0, device=DEV, dtype=torch.bfloat16)
+        off = 4 if misalign else 0  # 8 bytes off a 16-byte boundary
+        extras = [pool[i, off : off + nb * M * N].view(nb, M, N) for i in range(n_extra)]
+        if misalign:
+            assert extras[0].data_ptr() % 16 == 8
+        G.gemm(a, b, c=c, out=out, beta=0.5 if with_c else 0.0, extra_dst=[e.data_ptr() for e in extras])
+        _check(out, want, f"out extra={n_extra} misalign={misalign}")
+        for i, e in enumerate(extras):
+            assert torch.equal(e, out), f"destination {i} differs from the main output"
+            assert bool((pool[i, :off] == 7.0).all()) and bool((pool[i, off + nb * M * N :] == 7.0).all()), "stores outside the destination"
