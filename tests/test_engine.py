@@ -127,3 +127,20 @@ def test_reference_op_backward_formulas_against_autograd():
     got = ref.attention_bwd(do, q.detach(), k.detach(), v.detach(), o.detach(), lse.detach())
     for a, b in zip(got, want):
         assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_feed_forward_ops_fall_back_to_their_statements_on_cpu():
+    """``ops.up_swiglu`` / ``ops.down_dgrad_swiglu`` (one fused launch each on CUDA) are GEMM + SwiGLU statements elsewhere."""
+    from sample_efficient_gpt_b200 import ops
+
+    torch.manual_seed(0)
+    T, d, F = 37, 24, 16
+    x, w_up, w_down = torch.randn(T, d), torch.randn(2 * F, d) * 0.2, torch.randn(d, F) * 0.2
+    u, f = ops.up_swiglu(x, w_up)
+    assert torch.allclose(u, x @ w_up.T, atol=1e-5)
+    assert torch.allclose(f, torch.nn.functional.silu(u[:, :F]) * u[:, F:], atol=1e-5)
+    dy = torch.randn(T, d)
+    du = ops.down_dgrad_swiglu(dy, w_down, u)
+    ur = u.clone().requires_grad_(True)
+    (torch.nn.functional.silu(ur[:, :F]) * ur[:, F:]).backward(dy @ w_down)
+    assert torch.allclose(du, ur.grad, atol=1e-5)
