@@ -245,8 +245,8 @@ class EngineDecoder:
             g = ops.gate_fwd(o, z) if at.gating else o.reshape(B, H * hd)
             a = ops.matmul_nt(g, eng._w(at.out.linear.weight))
             y, n2, _, _ = ops.add_rmsnorm_fwd(x, a, blk.ln2.gain, scale, blk.ln2.eps, lp, False)
-            u = ops.matmul_nt(n2, eng._w(blk.ffn.up.linear.weight))
-            m = ops.matmul_nt(ops.swiglu_fwd(u), eng._w(blk.ffn.down.linear.weight))
+            _, f = ops.up_swiglu(n2, eng._w(blk.ffn.up.linear.weight))
+            m = ops.matmul_nt(f, eng._w(blk.ffn.down.linear.weight))
             res, delta = y, m
         return self._final(res, delta)
 

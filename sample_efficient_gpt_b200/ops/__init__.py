@@ -191,10 +191,17 @@ def down_dgrad_swiglu(dy: Tensor, w_down: Tensor, u: Tensor) -> Tensor:
 
 
 # ----------------------------------------------------------------------------- GEMMs
+_NATIVE_GEMM_MIN_ROWS = int(os.environ.get("SEGPT_NATIVE_GEMM_MIN_ROWS", "128"))
+
+
 def _native_gemm(*tensors) -> bool:
     """The block projections (and their gradients) run on this package's tcgen05 GEMM (CTA pairs, csrc/gemm_pair.cu);
     ``SEGPT_BLOCK_GEMM=library`` sends them to the library GEMM instead (comparison runs)."""
     if os.environ.get("SEGPT_BLOCK_GEMM", "native") != "native":
+        return False
+    # Products with a handful of rows (the one-token decode step: rows = batch) are matrix-vector work: a 256 x 256 tile
+    # kernel keeps a dozen CTA pairs busy on them, the library's small-row kernels run the decode step 1.6x faster.
+    if tensors[0].dim() == 2 and tensors[0].size(0) < _NATIVE_GEMM_MIN_ROWS:
         return False
     from sample_efficient_gpt_b200.ops import gemm as G
 
