@@ -12,12 +12,18 @@
 //
 // Roles (320 threads per CTA): warp 0 TMA producer (both CTAs), warp 1 MMA issuer (leader only), warps 2-9 epilogue
 // (both CTAs, each on its own 128 accumulator rows; two accumulators of 256 columns so that a tile's epilogue overlaps
-// the next tile's mainloop).  Two epilogues:
-//   EPI_TMA     : plain outputs.  tcgen05.ld -> registers -> 128-byte-swizzled staging tile -> TMA store, or TMA
-//                 reduce-add for fp32 outputs that accumulate into themselves (weight gradients).
-//   EPI_TMA_C   : bf16 outputs with an addend: boxes of C are fetched by TMA into the warp's staging tiles ahead of the
-//                 accumulator, the result overwrites them in place and is stored by TMA.
-//   EPI_GENERIC : symmetric (mirrored) outputs, extra destinations in peer memory, routed outputs, fp32 addends.
+// the next tile's mainloop).  Epilogues:
+//   EPI_TMA        : plain outputs.  tcgen05.ld -> registers -> 128-byte-swizzled staging tile -> TMA store, or TMA
+//                    reduce-add for fp32 outputs that accumulate into themselves (weight gradients).
+//   EPI_TMA_C      : bf16 outputs with an addend: boxes of C are fetched by TMA into the warp's staging tiles ahead of
+//                    the accumulator, the result overwrites them in place and is stored by TMA.
+//                    Both TMA epilogues store every staging tile once more per further destination (tensor maps of
+//                    the peers' copies of D: the all-gather of a result that is sharded over ranks).
+//   EPI_SWIGLU     : up projection of a SwiGLU feed-forward: gate and up columns of the same hidden units sit 128
+//                    accumulator columns apart; u = (gate | up) and f = silu(gate) * up leave from the same tile.
+//   EPI_SWIGLU_BWD : data gradient of the down projection: the accumulator is df, gate and up arrive by TMA, their
+//                    gradients replace them in the staging tiles and leave by TMA; df is never stored.
+//   EPI_GENERIC    : symmetric (mirrored) outputs, routed outputs, fp32 addends, destinations that are not 16-byte aligned.
 // Schedule (gemm_pair_sched.h): whole tiles dealt round-robin to the pairs; the tiles of the last, partly filled wave (or
 // all of them when there are fewer tiles than pairs) are cut into ranges of the contraction whose raw accumulators meet
 // in a workspace and are summed in a fixed order by the item of the last range, which also runs the epilogue.
@@ -817,7 +823,8 @@ int gemm_bf16_pair(const void* A, const void* B, const void* C, void* D, int M, 
 #undef SEG_PAIR
 }
 
-// u[:, :F] | u[:, F:] = x W^T (W = [gate rows | up rows], [2F, K]) and f = silu(u[:, :F]) * u[:, F:] in one launch.
+// u[:, :F] | u[:, F:] = x W^T (W = [gate rows | up rows], [2F, K]) and f = silu(u[:, :F]) * u[:, F:] in one launch
+// (the feed-forward of transformer/core.py:86-89 of the reference up to its down projection).
 int gemm_swiglu_pair(const void* X, const void* W, void* U, void* Fout, int M, int F, int K, int64_t ldx, int64_t ldw, int64_t ldu,
                      int64_t ldf, int* status, int sm_count, cudaStream_t st, long long wait_limit) {
   if (M <= 0 || F <= 0 || K <= 0) return 0;

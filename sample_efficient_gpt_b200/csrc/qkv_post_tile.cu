@@ -1,4 +1,5 @@
-// qkv post-processing (see qkv_post.cu for the math) staged through shared memory with bulk asynchronous copies.
+// qkv post-processing (same math as qkv_post.cu; reference: transformer/rope.py:36-56, transformer/attention.py:51-63 and
+// 222-228) staged through shared memory with bulk asynchronous copies.
 //
 // Why: a rotary pair is (x[j], x[j + hd/2]), so a thread that owns pairs reads two 16-byte pieces 64 bytes apart, and a
 // warp's request touches eight 128-byte lines, half of each.  The L1 data pipe processes one line per wavefront, and
