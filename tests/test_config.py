@@ -75,3 +75,23 @@ def test_cli_resolve(tmp_path):
     assert cfg.optim.lr == 0.001 and cfg.optim.seesaw_steps == (10, 20)
     assert cfg.optim.cosine_steps == cfg.trainer.max_steps
     assert cfg.data.train_path == "a" and str(cfg.trainer.save_dir).endswith(run_name) and "lr=0.00" in run_name
+
+
+def test_loss_parity_compare_reports_window_differences(tmp_path):
+    """``loss_parity.py --compare``: per-step and 50-step-window differences of two recorded loss curves."""
+    import importlib.util
+    import json
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("loss_parity", Path(__file__).resolve().parents[1] / "loss_parity.py")
+    lp = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(lp)
+    a = [5.0 - 0.01 * i for i in range(200)]
+    b = [x + (0.02 if i >= 100 else 0.0) for i, x in enumerate(a)]
+    for name, losses in (("a.json", a), ("b.json", b)):
+        (tmp_path / name).write_text(json.dumps({"impl": "ours", "steps": 100, "losses": losses}))
+    out = lp.compare(str(tmp_path / "a.json"), str(tmp_path / "b.json"))
+    assert out["micro_steps"] == 200
+    assert abs(out["max_abs_diff"] - 0.02) < 1e-5 and abs(out["max_abs_diff_of_50_step_means"] - 0.02) < 1e-5
+    assert abs(out["mean_abs_diff"] - 0.01) < 1e-5
+    assert len(out["windows"]) == 4 and abs(out["windows"][0][0] - out["windows"][0][1]) < 1e-5
