@@ -185,3 +185,16 @@ def test_dataset_tokeniser_parquet_jsonl_txt(tmp_path, monkeypatch):
     assert np.load(out / "c_train.npy").tolist() == [3, 4, 0, 5, 6, 0]
     ratios = proc.compression_ratios(txt)
     assert ratios["c_val.txt"] == pytest.approx(7 / 5)
+
+
+def test_tokenizer_bench_runs_and_native_trainer_matches_python(tmp_path):
+    """The CPU benchmark of the native tools on a 1 MB synthetic corpus: both BPE trainers must learn the same merges."""
+    import json
+    import subprocess
+    import sys
+
+    r = subprocess.run([sys.executable, "-m", "sample_efficient_gpt_b200.tokenizer.bench_tokenizer", "--mb", "1", "--vocab-size", "320",
+                        "--threads", "2", "--python-mb", "1"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["bpe_same_merges"] is True and out["bpe_merges"] == 64 and out["distinct_pretokens"] > 1000
