@@ -41,6 +41,8 @@ def find_chunk_boundaries(file: BinaryIO, desired_num_chunks: int, split_special
 
 
 def pre_tokenize(splitter: Splitter, filepath: str, num_processes: int = 1, special_token: str = "<|endoftext|>") -> dict[str, int]:
+    if num_processes > 1 and hasattr(splitter, "count_file"):
+        return splitter.count_file(str(filepath), num_processes)  # native threads, one dict at the end
     with Path(filepath).open("rb") as fh:
         bounds = find_chunk_boundaries(fh, num_processes * 4, special_token.encode())
     spans = list(zip(bounds[:-1], bounds[1:]))
