@@ -4,6 +4,8 @@
 
   * pre-tokenisation: the C++ scanner (``Splitter.seek_and_split``, one and several threads) against ``regex.findall`` with
     the same pattern plus a Python ``Counter`` (what the reference's pure-Python path does, tokenizer/pretokenization.py);
+  * encoding with the learned vocabulary: the Python merge loop with its cache against the native encoder
+    (``tokenizer/csrc/segtok.cpp::Encoder``), one thread and several; the ids must be identical;
   * BPE training on the resulting pre-token counts: the C++ incremental trainer (the stand-in for the reference's Rust
     ``rustbpe``) against the Python merge loop (``train_merges_python``: the reference's optimised loop with the sort
     heuristic, tokenizer/train_bpe.py:168 there).  Both must produce the same merges.
@@ -104,6 +106,32 @@ def main():
     out["bpe_python_s"] = round(t2 - t1, 3)
     out["bpe_speedup"] = round((t2 - t1) / max(t1 - t0, 1e-9), 1)
     out["bpe_same_merges"] = native_merges == py_merges
+
+    # encoding with the learned vocabulary: Python merge loop with its per-pre-token cache, the native encoder, and the
+    # native encoder on several threads (documents of the same corpus; the Python path is timed on a slice)
+    from sample_efficient_gpt_b200.tokenizer.tokenizer import Tokenizer
+
+    vocab = {i: bytes([i]) for i in range(256)}
+    vocab[256] = b"<|endoftext|>"
+    for k, (l, r) in enumerate(native_merges):
+        vocab[257 + k] = l + r
+    docs = [d + "<|endoftext|>" for d in text.split("<|endoftext|>") if d]
+    py_tok = Tokenizer(vocab, native_merges, ["<|endoftext|>"], use_native=False)
+    na_tok = Tokenizer(vocab, native_merges, ["<|endoftext|>"])
+    py_docs = docs[: max(1, len(docs) // 4)]
+    t0 = time.monotonic()
+    py_ids = [py_tok.encode(d) for d in py_docs]
+    t1 = time.monotonic()
+    na_ids = [na_tok.encode(d) for d in docs]
+    t2 = time.monotonic()
+    na_batch = na_tok.encode_batch(docs, threads=a.threads)
+    t3 = time.monotonic()
+    nb = lambda ds: sum(len(d.encode("utf-8")) for d in ds)  # noqa: E731
+    out["encode_python_mb_s"] = round(nb(py_docs) / (t1 - t0) / 2**20, 2)
+    out["encode_native_mb_s"] = round(nb(docs) / (t2 - t1) / 2**20, 2)
+    out[f"encode_native_{a.threads}_threads_mb_s"] = round(nb(docs) / (t3 - t2) / 2**20, 2)
+    out["encode_same_ids"] = na_ids[: len(py_ids)] == py_ids and na_batch == na_ids
+    out["bytes_per_token"] = round(nb(docs) / max(1, sum(len(x) for x in na_ids)), 3)
     print(json.dumps(out))
 
 

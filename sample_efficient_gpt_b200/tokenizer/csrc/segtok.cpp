@@ -30,6 +30,7 @@
 #include <string>
 #include <string_view>
 #include <thread>
+#include <tuple>
 #include <unordered_map>
 #include <vector>
 
@@ -624,6 +625,104 @@ class BpeTrainer {
   std::vector<std::string> token_bytes_;
 };
 
+// ------------------------------------------------------------------------------------------------ BPE encoder
+// Encodes text with a given vocabulary: byte -> id table, merges as (left id, right id, new id, rank).  A pre-token is
+// merged lowest-rank-first, every occurrence of the chosen pair left to right per round (the statement of
+// tokenizer/tokenizer.py:104-351 of the reference); an optional second stage of merges runs over the whole piece, across
+// pre-token boundaries.  Pieces must not contain special tokens (the caller splits on them).
+class Encoder {
+ public:
+  using Merge = std::tuple<uint32_t, uint32_t, uint32_t, uint32_t>;
+  Encoder(std::vector<uint32_t> lut256, const std::vector<Merge>& first, const std::vector<Merge>& second) : lut_(std::move(lut256)) {
+    if (lut_.size() != 256) throw py::value_error("the byte table needs 256 entries");
+    for (const auto& m : first) first_[mk(std::get<0>(m), std::get<1>(m))] = {std::get<3>(m), std::get<2>(m)};
+    for (const auto& m : second) second_[mk(std::get<0>(m), std::get<1>(m))] = {std::get<3>(m), std::get<2>(m)};
+  }
+
+  // Holds the GIL: the instance's pre-token cache is shared by all callers.
+  std::vector<uint32_t> encode_ordinary(const std::string& text) { return encode_with(text, cache_); }
+
+  // Many pieces at once on native threads; every thread keeps its own pre-token cache.
+  std::vector<std::vector<uint32_t>> encode_batch(const std::vector<std::string>& texts, int threads) const {
+    std::vector<std::vector<uint32_t>> out(texts.size());
+    py::gil_scoped_release nogil;
+    const unsigned nt = (unsigned)std::max(1, std::min<int>(threads, 64));
+    std::atomic<size_t> next{0};
+    auto work = [&]() {
+      Cache cache;
+      for (size_t i = next.fetch_add(1); i < texts.size(); i = next.fetch_add(1)) out[i] = encode_with(texts[i], cache);
+    };
+    std::vector<std::thread> th;
+    for (unsigned t = 1; t < nt; ++t) th.emplace_back(work);
+    work();
+    for (auto& x : th) x.join();
+    return out;
+  }
+
+ private:
+  struct RankId {
+    uint32_t rank, id;
+  };
+  using Table = std::unordered_map<Pair, RankId, PairHash>;
+  using Cache = std::unordered_map<std::string, std::vector<uint32_t>>;
+
+  static void merge_by_rank(std::vector<uint32_t>& ids, const Table& table) {
+    std::vector<uint32_t> out;
+    while (ids.size() >= 2) {
+      uint32_t best = UINT32_MAX, new_id = 0;
+      Pair best_pair = 0;
+      for (size_t i = 0; i + 1 < ids.size(); ++i) {
+        const auto it = table.find(mk(ids[i], ids[i + 1]));
+        if (it != table.end() && it->second.rank < best) {
+          best = it->second.rank;
+          new_id = it->second.id;
+          best_pair = it->first;
+        }
+      }
+      if (best == UINT32_MAX) break;
+      out.clear();
+      for (size_t i = 0; i < ids.size();) {
+        if (i + 1 < ids.size() && mk(ids[i], ids[i + 1]) == best_pair) {
+          out.push_back(new_id);
+          i += 2;
+        } else {
+          out.push_back(ids[i]);
+          i += 1;
+        }
+      }
+      ids.swap(out);
+    }
+  }
+
+  std::vector<uint32_t> encode_with(const std::string& text, Cache& cache) const {
+    std::vector<uint32_t> all;
+    const uint8_t* s = (const uint8_t*)text.data();
+    const size_t n = text.size();
+    size_t i = 0;
+    std::string key;
+    while (i < n) {
+      const size_t j = match_at(s, i, n);
+      key.assign((const char*)s + i, j - i);
+      auto it = cache.find(key);
+      if (it == cache.end()) {
+        std::vector<uint32_t> ids(key.size());
+        for (size_t k = 0; k < key.size(); ++k) ids[k] = lut_[(uint8_t)key[k]];
+        merge_by_rank(ids, first_);
+        if (cache.size() >= (size_t)2000000) cache.clear();
+        it = cache.emplace(key, std::move(ids)).first;
+      }
+      all.insert(all.end(), it->second.begin(), it->second.end());
+      i = j;
+    }
+    if (!second_.empty()) merge_by_rank(all, second_);
+    return all;
+  }
+
+  std::vector<uint32_t> lut_;
+  Table first_, second_;
+  Cache cache_;
+};
+
 }  // namespace
 
 PYBIND11_MODULE(_segtok, m) {
@@ -642,4 +741,9 @@ PYBIND11_MODULE(_segtok, m) {
       .def("get_pattern", &BpeTrainer::get_pattern)
       .def("get_mergeable_ranks", &BpeTrainer::get_mergeable_ranks)
       .def("encode", &BpeTrainer::encode, py::arg("text"));
+  py::class_<Encoder>(m, "Encoder")
+      .def(py::init<std::vector<uint32_t>, const std::vector<Encoder::Merge>&, const std::vector<Encoder::Merge>&>(), py::arg("lut256"),
+           py::arg("merges"), py::arg("second_stage") = std::vector<Encoder::Merge>())
+      .def("encode_ordinary", &Encoder::encode_ordinary, py::arg("text"))
+      .def("encode_batch", &Encoder::encode_batch, py::arg("texts"), py::arg("threads") = 8);
 }

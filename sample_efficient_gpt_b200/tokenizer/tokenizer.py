@@ -48,7 +48,7 @@ def merge_by_rank(ids: list[int], ranks: dict[tuple[int, int], int], merge_map: 
 
 class Tokenizer:
     def __init__(self, vocab: dict[int, bytes], merges: list[tuple[bytes, bytes]], special_tokens: list[str] | None = None,
-                 superbpe_transition_idx: int | None = None):
+                 superbpe_transition_idx: int | None = None, use_native: bool = True):
         from sample_efficient_gpt_b200.tokenizer.fastsplit import Splitter
 
         self.special_tokens = special_tokens or []
@@ -66,6 +66,17 @@ class Tokenizer:
         self.merge_map, self.bpe_ranks = self._init_merge_map(merges, 0)
         self.merge_map_superbpe, self.bpe_ranks_superbpe = self._init_merge_map(second, len(merges))
         self._cached = lru_cache(maxsize=2_000_000)(self._encode_bytes)
+        # native encoder (tokenizer/csrc/segtok.cpp::Encoder): same merges, same order; the Python statements below stay as
+        # the fallback and as its oracle (``use_native=False``)
+        self.use_native = use_native
+        self._native = None
+        if use_native:
+            from sample_efficient_gpt_b200.tokenizer.fastsplit import _mod
+
+            if hasattr(_mod, "Encoder"):
+                as_rows = lambda mm, rk: [(l, r, mm[(l, r)], rk[(l, r)]) for (l, r) in sorted(rk, key=rk.get)]  # noqa: E731
+                self._native = _mod.Encoder(self.lut256, as_rows(self.merge_map, self.bpe_ranks),
+                                            as_rows(self.merge_map_superbpe, self.bpe_ranks_superbpe))
 
     def _init_merge_map(self, merges, base_rank):
         merge_map, ranks = {}, {}
@@ -94,6 +105,9 @@ class Tokenizer:
             if piece in self.special_tokens:
                 out.append(self.byte2int[piece.encode()])
                 continue
+            if self._native is not None:
+                out.extend(self._native.encode_ordinary(piece))
+                continue
             ids: list[int] = []
             for tok in self._scanner.pretokens(piece):
                 ids.extend(self._cached(tok.encode("utf-8")))
@@ -102,11 +116,39 @@ class Tokenizer:
             out.extend(ids)
         return out
 
+    def encode_batch(self, texts: list[str], threads: int = 8) -> list[list[int]]:
+        """Many documents at once; with the native encoder the ordinary pieces of all of them are encoded on native threads."""
+        if self._native is None:
+            return [self.encode(t) for t in texts]
+        plans, pieces = [], []
+        for text in texts:
+            plan = []
+            for piece in self._split.split(text):
+                if not piece:
+                    continue
+                if piece in self.special_tokens:
+                    plan.append(self.byte2int[piece.encode()])
+                else:
+                    plan.append(None)
+                    pieces.append(piece)
+            plans.append(plan)
+        encoded = iter(self._native.encode_batch(pieces, threads))
+        outs = []
+        for plan in plans:
+            ids: list[int] = []
+            for item in plan:
+                if item is None:
+                    ids.extend(next(encoded))
+                else:
+                    ids.append(item)
+            outs.append(ids)
+        return outs
+
     def encode_iterable(self, iterable):
         for line in iterable:
             yield from self.encode(line)
 
-    def encode_file(self, filepath, chunk_size: int = 1024 * 1024) -> list[int]:
+    def encode_file(self, filepath, chunk_size: int = 1024 * 1024, threads: int = 8) -> list[int]:
         from sample_efficient_gpt_b200.tokenizer.pretokenization import find_chunk_boundaries
 
         path = Path(filepath)
@@ -114,9 +156,15 @@ class Tokenizer:
         with path.open("rb") as f:
             bounds = find_chunk_boundaries(f, n_chunks, b" ")
             tokens: list[int] = []
-            for s, e in zip(bounds[:-1], bounds[1:]):
-                f.seek(s)
-                tokens.extend(self.encode(f.read(e - s).decode("utf-8", errors="ignore")))
+            spans = list(zip(bounds[:-1], bounds[1:]))
+            group = 64 if self._native is not None else 1  # chunks encoded together on native threads
+            for g0 in range(0, len(spans), group):
+                texts = []
+                for s, e in spans[g0 : g0 + group]:
+                    f.seek(s)
+                    texts.append(f.read(e - s).decode("utf-8", errors="ignore"))
+                for ids in self.encode_batch(texts, threads=threads):
+                    tokens.extend(ids)
         return tokens
 
     def decode(self, ids) -> str:

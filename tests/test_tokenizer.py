@@ -198,3 +198,31 @@ def test_tokenizer_bench_runs_and_native_trainer_matches_python(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     out = json.loads(r.stdout.strip().splitlines()[-1])
     assert out["bpe_same_merges"] is True and out["bpe_merges"] == 64 and out["distinct_pretokens"] > 1000
+    assert out["encode_same_ids"] is True
+
+
+def test_native_encoder_matches_the_python_statements(tmp_path):
+    """tokenizer/csrc/segtok.cpp::Encoder against ``merge_by_rank`` + cache in Python: one-stage and two-stage (superbpe)
+    vocabularies, special tokens in the text, random unicode, and the batch API on several threads."""
+    import random
+
+    rnd = random.Random(3)
+    alphabet = list("abcdefghij  \n.,'0123456789") + ["é", "ü", "あ", "語", "😀", "it's", " don't", "<|endoftext|>"]
+    texts = ["".join(rnd.choice(alphabet) for _ in range(rnd.randint(1, 400))) for _ in range(60)] + [CORPUS, "", " ", "<|endoftext|>"]
+    bpe = BPE(["<|endoftext|>"], vocab_size=420, save_dir=tmp_path / "tok")
+    bpe.train_from_counts(Splitter("<|endoftext|>").split(CORPUS * 20 + "".join(texts)))
+    first = len(bpe.merges_tuples)
+    py1 = Tokenizer(bpe.vocab, bpe.merges_tuples, ["<|endoftext|>"], use_native=False)
+    na1 = Tokenizer(bpe.vocab, bpe.merges_tuples, ["<|endoftext|>"])
+    assert na1._native is not None and py1._native is None
+    docs = [py1.encode(d) for d in (CORPUS * 3 + "".join(texts)).split("<|endoftext|>")]
+    bpe.resume_train(docs, vocab_size=470, superbpe=True)
+    py2 = Tokenizer(bpe.vocab, bpe.merges_tuples, ["<|endoftext|>"], superbpe_transition_idx=first, use_native=False)
+    na2 = Tokenizer(bpe.vocab, bpe.merges_tuples, ["<|endoftext|>"], superbpe_transition_idx=first)
+    for t in texts:
+        assert na1.encode(t) == py1.encode(t), t
+        assert na2.encode(t) == py2.encode(t), t
+        assert na2.decode(na2.encode(t)) == t
+    assert na1.encode_batch(texts, threads=4) == [py1.encode(t) for t in texts]
+    assert na2.encode_batch(texts, threads=3) == [py2.encode(t) for t in texts]
+    assert py1.encode_batch(texts[:5]) == [py1.encode(t) for t in texts[:5]]
