@@ -179,7 +179,8 @@ def up_swiglu(x: Tensor, w: Tensor):
 
 def down_dgrad_swiglu(dy: Tensor, w_down: Tensor, u: Tensor) -> Tensor:
     """Gradient of u = (gate | up) [M, 2F] of a SwiGLU feed-forward from the gradient dy [M, d] of its output and the down
-    projection's weight w_down [d, F]: du = swiglu_bwd(dy @ w_down, u).  On CUDA one launch: the GEMM's epilogue takes df
+    projection's weight w_down [d, F]: du = swiglu_bwd(dy @ w_down, u) (what autograd derives for transformer/core.py:86-89 of
+    the reference).  On CUDA one launch: the GEMM's epilogue takes df
     (rounded to bf16, as a stored df would be) straight from the accumulator, so df never reaches memory
     (``SEGPT_FUSE_SWIGLU=0``: GEMM, then the element-wise kernel; both give the same bits)."""
     if (dy.is_cuda and dy.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16 and u.dtype == torch.bfloat16 and dy.dim() == 2

@@ -169,7 +169,8 @@ def emulate_one_gpu(world: int, mb: int, blocks: int, reps: int) -> dict:
 def gemm_allgather(rows: int, cols: int, total: int, reps: int, warmup: int) -> dict:
     """The last GEMM of a sharded Newton-Schulz chain: each rank computes ``a X + B X`` for its share of ``total`` matrices
     ([rows, rows] x [rows, cols]) and the epilogue stores every tile into all ranks' buffers (``extra_dst`` = the peers'
-    copies), followed by the device barrier.  Timed against the same GEMM with a local output only, and against that GEMM
+    copies), followed by the device barrier (the reference leaves its matrix ownership commented out,
+    training/optimizers/normuon_cwd.py:60-62, and every rank orthogonalises every matrix).  Timed against the same GEMM with a local output only, and against that GEMM
     followed by ``all_gather_into_tensor``; roofline = max(FLOPs at the measured cuBLAS rate, bytes that leave this GPU
     over NVLink at 770 GB/s)."""
     from sample_efficient_gpt_b200.ops import gemm as G
